@@ -1,0 +1,105 @@
+/* b200q - B200 (sm_100a) quantized GEMV/GEMM over raw GGUF blocks: C ABI.
+ *
+ * Drop-in boundary for the integer GEMV/GEMM path of the sycl-infer engine's
+ * backend-operator interface.  Every entry point names the reference interface
+ * it replaces (paths inside the reference project).  All pointers are DEVICE
+ * pointers unless a parameter says "host"; the caller owns every buffer; the
+ * library allocates nothing, keeps no state beyond a thread-local error string,
+ * and never falls back to the CPU: an unsupported request is an error.
+ *
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ * stream).  Calls only enqueue work; they do not synchronize.
+ *
+ * Activation layout (the one the reference's quantizer writes,
+ * src/backend/cpu/kernels/xq.cpp:1-5): group-major, token t, 32-value group g:
+ *   x8[(g*TB + t)*32 + i]          int8 codes
+ *   xmeta[2*(g*TB + t)]            fp32 scale (already rounded through f16), [+1] = 0
+ *   xsumq[2*(g*TB + t) + {0,1}]    sums of codes 0..15 and 16..31
+ * Weight layout: raw GGUF blocks, row r at w + r * row_bytes(type, K).
+ */
+#ifndef B200Q_H
+#define B200Q_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200Q_VERSION 1
+
+/* ggml type ids (src/model/gguf.h:8-32) */
+enum { B200Q_Q8_0 = 8, B200Q_Q4_K = 12, B200Q_Q5_K = 13, B200Q_Q6_K = 14, B200Q_IQ4_XS = 23 };
+
+/* Status codes.  Mirrors the reference C ABI's convention of an integer status
+ * plus a thread-local message (include/sycl_infer/sycl_infer.h:54-59). */
+enum {
+    B200Q_OK = 0,
+    B200Q_EINVAL = 1,      /* bad argument: shape, alignment, null pointer */
+    B200Q_EUNSUPPORTED = 2, /* type or size this library has no kernel for */
+    B200Q_ECUDA = 3,        /* a CUDA runtime call failed */
+    B200Q_ETIMEOUT = 4      /* a bounded device-side wait ran out (see b200q_device_status) */
+};
+
+#define B200Q_MAX_SEGS 8
+
+/* One GEMV output segment: field for field the reference's cpu_gemv_seg
+ * (src/backend/cpu/cpu_types.h:68-86) / gemv_seg (src/backend/gpu/kernels/kernels.h:44-81)
+ * without the repacked-store members this path never reads. */
+typedef struct b200q_seg {
+    const void * w;         /* raw GGUF blocks [n_rows][K], 16-byte aligned */
+    uint32_t type;          /* ggml type of w */
+    int32_t K;              /* input length, multiple of 256 */
+    int32_t n_rows;         /* output rows */
+    const float * x;        /* fp32 activations, row stride x_stride (fused-quantize entry points) */
+    int32_t x_stride;
+    const float * act_up;   /* non-null: the activation is silu(x) * act_up (same stride as x) */
+    float * out;            /* out[t*out_stride + row] */
+    int32_t out_stride;
+    const float * residual; /* optional, same indexing as out; may alias out */
+    float alpha;            /* out = alpha * dot (+ residual) */
+    const int8_t * x8;      /* quantized activation views (see header comment) */
+    const float * xmeta;
+    const int32_t * xsumq;
+} b200q_seg;
+
+const char * b200q_last_error(void);
+int b200q_version(void);
+/* bytes of one weight row; 0 for an unsupported type.  quant_row_bytes, src/common/quant.h:1177-1198 */
+size_t b200q_row_bytes(uint32_t type, int64_t K);
+
+/* compute_backend::xq (src/backend/backend.h:104-105) = cpu_xq (src/backend/cpu/kernels/xq.cpp:10-50).
+ * `up` non-null quantizes silu(x)*up.  x8 must be 16-byte aligned. */
+int b200q_xq(void * stream, const float * x, const float * up, int x_stride, int up_stride, int8_t * x8,
+             float * xmeta, int32_t * xsumq, int TB, int K);
+
+/* compute_backend::i8_gemv (src/backend/backend.h:113) = cpu_i8_gemv (src/backend/cpu/kernels/i8.cpp:498-516),
+ * extended to the n_segs segments of one call that share a quantized activation
+ * (seg_plan::call_t, src/engine/engine_types.h:46-61): one launch for q|k|v or gate|up. */
+int b200q_i8_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs);
+
+/* compute_backend::i8_gemm (src/backend/backend.h:114) = cpu_i8_gemm (src/backend/cpu/kernels/i8.cpp:518-546):
+ * TB tokens, out[t*out_stride + row]. */
+int b200q_i8_gemm(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB);
+
+/* Quantize the call's activation (segs[0].x / act_up, TB tokens) into the caller's
+ * x8/xmeta/xsumq scratch and run every segment: the analogue of the reference's fused
+ * decode launch i8_grp_quant_gemv_launch (src/backend/gpu/kernels/kernels.h:216-219).
+ * The segments' x8/xmeta/xsumq fields are ignored; the scratch arguments are used. */
+int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
+                     int32_t * xsumq);
+
+/* Parity instrument: the exact int32 per-group dot products the reference forms inside
+ * q4k/q5k/q6k_i8_block (src/backend/cpu/kernels/i8.cpp:57,117,149) for token t.
+ * wd[row*D + j], D = K/32 (K/16 for Q6_K: raw codes 0..63, 16-value scale groups).
+ * Uses the same device unpack + dp4a code as the GEMV kernels. */
+int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int n_rows, const int8_t * x8, int TB,
+                        int t, int32_t * wd);
+
+/* compute_backend::synchronize (src/backend/backend.h:123): blocks until the stream drained. */
+int b200q_synchronize(void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

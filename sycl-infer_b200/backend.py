@@ -1,0 +1,145 @@
+"""Host-side mirror of the reference engine's backend-operator interface for the
+integer GEMV/GEMM path.
+
+`cuda_backend` carries the same operator names, argument order and meaning as the
+reference's `compute_backend` (src/backend/backend.h:33-124 of the reference) for the
+operators on this path - `xq`, `i8_gemv`, `i8_gemm`, `gemv_group`, `synchronize` - and
+`gemv_seg` mirrors its segment descriptor (src/backend/gpu/kernels/kernels.h:44-81).
+Like the reference's backends it is one device + one in-order queue (a CUDA stream),
+owns no memory, and raises (RuntimeError subclass) instead of falling back when an
+operator is not available.  Buffers are torch CUDA tensors (device memory plumbing
+only); every operator goes through the C ABI of libb200q.so.
+"""
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .capi import MAX_SEGS, Seg, load_lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda, "device tensor expected"
+    return t.data_ptr()
+
+
+@dataclass
+class gemv_seg:
+    """One GEMV output segment (reference: gemv_seg / cpu_gemv_seg)."""
+    w: object = None            # uint8 tensor: raw GGUF blocks [n_rows][K]
+    type: int = 0               # ggml type id
+    K: int = 0
+    n_rows: int = 0
+    x: object = None            # fp32 activations (fused-quantize operators)
+    x_stride: int = 0
+    act_up: object = None       # non-None: activation is silu(x)*act_up
+    out: object = None          # fp32, out[t*out_stride + row]
+    out_stride: int = 0
+    residual: object = None
+    alpha: float = 1.0
+    x8: object = None           # int8 codes, group-major
+    xmeta: object = None        # fp32 (scale, 0) pairs
+    xsumq: object = None        # int32 pairs of 16-value sums
+    i8: bool = True
+
+    def to_c(self):
+        return Seg(_ptr(self.w), self.type, self.K, self.n_rows, _ptr(self.x), self.x_stride, _ptr(self.act_up),
+                   _ptr(self.out), self.out_stride or self.n_rows, _ptr(self.residual), self.alpha, _ptr(self.x8),
+                   _ptr(self.xmeta), _ptr(self.xsumq))
+
+
+def _pack(segs):
+    if isinstance(segs, gemv_seg):
+        segs = [segs]
+    if not 1 <= len(segs) <= MAX_SEGS:
+        raise ValueError(f"a call holds 1..{MAX_SEGS} segments")
+    arr = (Seg * len(segs))(*[s.to_c() for s in segs])
+    return arr, len(segs)
+
+
+class cuda_backend:
+    """One B200 + one stream.  Mirrors compute_backend for the int8 GEMV/GEMM path."""
+
+    def __init__(self, device=0, stream: Optional[torch.cuda.Stream] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("cuda_backend needs a CUDA device; this library has no CPU path")
+        self.lib = load_lib()
+        self.device = torch.device("cuda", device)
+        self._stream = stream
+
+    def name(self):
+        return "b200q-cuda"
+
+    def is_cpu(self):
+        return False
+
+    def kind(self):
+        return "gpu"
+
+    @property
+    def stream(self):
+        return self._stream if self._stream is not None else torch.cuda.current_stream(self.device)
+
+    def _s(self):
+        return C.c_void_p(self.stream.cuda_stream)
+
+    # compute_backend::xq (backend.h:104-105): x8/xmeta/xsumq are caller-owned outputs
+    def xq(self, x, up, x_stride, up_stride, x8, xmeta, xsumq, info, TB, K):
+        del info  # the reference's host quantizer ignores it as well (xq.cpp:12)
+        self.lib.check(self.lib.xq(self._s(), _ptr(x), _ptr(up), x_stride, up_stride, _ptr(x8), _ptr(xmeta),
+                                   _ptr(xsumq), TB, K))
+
+    # compute_backend::i8_gemv (backend.h:113); a list runs the segments of one call in one launch
+    def i8_gemv(self, s):
+        arr, n = _pack(s)
+        self.lib.check(self.lib.i8_gemv(self._s(), arr, n))
+
+    # compute_backend::i8_gemm (backend.h:114)
+    def i8_gemm(self, s, TB):
+        arr, n = _pack(s)
+        self.lib.check(self.lib.i8_gemm(self._s(), arr, n, TB))
+
+    # compute_backend::gemv_group (backend.h:61-62): every segment of one type-group of a
+    # call, activation given as fp32.  Here the group is quantized into the scratch the
+    # segments carry (x8/xmeta/xsumq, engine-owned as in src/engine/graph.cpp:218-220)
+    # and run on the integer path; total_rows/nsb/n_tok_blocks are implied by the
+    # segments and accepted for signature parity.
+    def gemv_group(self, type, segs, n_segs, total_rows, TB, nsb=0, n_tok_blocks=0):
+        segs = list(segs)[:n_segs]
+        if any(s.type != type for s in segs):
+            raise ValueError("gemv_group: every segment must have the group's type")
+        if total_rows != sum(s.n_rows for s in segs):
+            raise ValueError("gemv_group: total_rows does not match the segments")
+        self.quant_gemv(segs, TB)
+
+    # fused decode launch (reference: i8_grp_quant_gemv_launch, kernels.h:216-219)
+    def quant_gemv(self, segs, TB=1):
+        arr, n = _pack(segs)
+        s0 = segs[0] if not isinstance(segs, gemv_seg) else segs
+        self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
+
+    # parity instrument (no reference operator: the reference never exposes these sums)
+    def i8_block_dots(self, w, type, K, n_rows, x8, TB, t, wd):
+        self.lib.check(self.lib.i8_block_dots(self._s(), _ptr(w), type, K, n_rows, _ptr(x8), TB, t, _ptr(wd)))
+
+    # compute_backend::synchronize (backend.h:123): must truly block
+    def synchronize(self):
+        self.lib.check(self.lib.synchronize(self._s()))
+
+
+def make_cuda_backend(device=0, stream=None):
+    """Counterpart of make_gpu_backend(queue&) (backend.h:126)."""
+    return cuda_backend(device, stream)
+
+
+def alloc_act(TB, K, device="cuda"):
+    """Caller-owned quantized-activation scratch of one call (x8, xmeta, xsumq)."""
+    G = K // 32
+    return (torch.empty(G * TB * 32, dtype=torch.int8, device=device),
+            torch.empty(G * TB * 2, dtype=torch.float32, device=device),
+            torch.empty(G * TB * 2, dtype=torch.int32, device=device))

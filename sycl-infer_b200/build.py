@@ -1,0 +1,55 @@
+"""In-tree build of libb200q.so with nvcc for sm_100a (no JIT cache, no torch headers)."""
+import hashlib
+import os
+import shutil
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libb200q.so")
+STAMP = os.path.join(HERE, "build", "libb200q.stamp")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: the CUDA toolkit is required to build libb200q.so")
+
+
+def sources():
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _digest():
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    inc = os.path.join(HERE, "..", "include", "b200q.h")
+    for f in sorted(os.listdir(CSRC)):
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(f.encode() + fh.read())
+    with open(inc, "rb") as fh:
+        h.update(fh.read())
+    return h.hexdigest()
+
+
+def build_native(force=False, verbose=False, extra=()):
+    """Compile every .cu under csrc/ into libb200q.so; skipped when sources are unchanged."""
+    dig = _digest()
+    if not force and os.path.exists(LIB) and os.path.exists(STAMP) and open(STAMP).read() == dig:
+        return LIB
+    os.makedirs(os.path.dirname(STAMP), exist_ok=True)
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", LIB, *sources()]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.run(cmd, check=True)
+    with open(STAMP, "w") as fh:
+        fh.write(dig)
+    return LIB
+
+
+if __name__ == "__main__":
+    import sys
+    build_native(force="--force" in sys.argv, verbose=True,
+                 extra=["-Xptxas", "-v"] if "--ptxas" in sys.argv else [])

@@ -1,0 +1,73 @@
+"""ctypes binding of libb200q.so (the C ABI declared in include/b200q.h).
+
+There is no fallback: if the library is missing or fails to load, importing code gets
+an exception that says how to build it.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200q.so")
+
+_vp = C.c_void_p
+OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT = 0, 1, 2, 3, 4
+MAX_SEGS = 8
+
+
+class B200QError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"b200q status {code}: {msg}")
+        self.code = code
+
+
+class Seg(C.Structure):
+    """struct b200q_seg, field for field."""
+    _fields_ = [("w", _vp), ("type", C.c_uint32), ("K", C.c_int32), ("n_rows", C.c_int32), ("x", _vp),
+                ("x_stride", C.c_int32), ("act_up", _vp), ("out", _vp), ("out_stride", C.c_int32),
+                ("residual", _vp), ("alpha", C.c_float), ("x8", _vp), ("xmeta", _vp), ("xsumq", _vp)]
+
+
+_SIGS = {
+    "b200q_last_error": (C.c_char_p, []),
+    "b200q_version": (C.c_int, []),
+    "b200q_row_bytes": (C.c_size_t, [C.c_uint32, C.c_int64]),
+    "b200q_xq": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, C.c_int, C.c_int]),
+    "b200q_i8_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
+    "b200q_i8_gemm": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int]),
+    "b200q_quant_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_i8_block_dots": (C.c_int, [_vp, _vp, C.c_uint32, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]),
+    "b200q_synchronize": (C.c_int, [_vp]),
+}
+
+
+class Lib:
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise ImportError(f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; "
+                              "g.build()'` (needs nvcc); there is no CPU fallback")
+        self.path = path
+        self.dll = C.CDLL(path)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(self.dll, name)
+            fn.restype = res
+            fn.argtypes = args
+
+    def last_error(self):
+        return self.dll.b200q_last_error().decode()
+
+    def check(self, rc):
+        if rc != OK:
+            raise B200QError(rc, self.last_error())
+
+    def __getattr__(self, name):
+        return getattr(self.dll, "b200q_" + name)
+
+
+_lib = None
+
+
+def load_lib():
+    global _lib
+    if _lib is None:
+        _lib = Lib()
+    return _lib

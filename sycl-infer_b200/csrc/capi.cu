@@ -1,0 +1,208 @@
+// C ABI of the library: argument validation, error reporting, kernel dispatch.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "launch.h"
+
+namespace b200q {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char * fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char * what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return B200Q_ECUDA;
+}
+
+static bool type_ok(uint32_t t) {
+    return t == kQ4_K || t == kQ5_K || t == kQ6_K || t == kQ8_0 || t == kIQ4_XS;
+}
+
+static inline bool aligned(const void * p, size_t a) {
+    return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+// Validate the segments of one call and flatten them for the kernels.  A call shares
+// one quantized activation, so every segment must have the same K.
+static int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
+                      const int32_t * xsumq, CallDev & c) {
+    if (!segs || n_segs < 1 || n_segs > B200Q_MAX_SEGS) {
+        set_error("n_segs must be 1..%d (got %d)", B200Q_MAX_SEGS, n_segs);
+        return B200Q_EINVAL;
+    }
+    if (TB < 1) {
+        set_error("TB must be >= 1 (got %d)", TB);
+        return B200Q_EINVAL;
+    }
+    memset(&c, 0, sizeof(c));
+    c.K = segs[0].K;
+    c.TB = TB;
+    c.n_segs = n_segs;
+    c.x8 = x8 ? x8 : segs[0].x8;
+    c.xmeta = xmeta ? xmeta : segs[0].xmeta;
+    c.xsumq = xsumq ? xsumq : segs[0].xsumq;
+    if (c.K < 256 || (c.K & 255)) {
+        set_error("K must be a positive multiple of 256 (got %d)", c.K);
+        return B200Q_EINVAL;
+    }
+    if (!c.x8 || !c.xmeta || !c.xsumq) {
+        set_error("quantized activation views x8/xmeta/xsumq must be non-null");
+        return B200Q_EINVAL;
+    }
+    if (!aligned(c.x8, 16) || !aligned(c.xmeta, 8) || !aligned(c.xsumq, 8)) {
+        set_error("x8 must be 16-byte aligned, xmeta and xsumq 8-byte aligned");
+        return B200Q_EINVAL;
+    }
+    int rows = 0;
+    for (int i = 0; i < n_segs; i++) {
+        const b200q_seg & s = segs[i];
+        if (!type_ok(s.type)) {
+            set_error("segment %d: unsupported ggml type %u (supported: Q8_0=8 Q4_K=12 Q5_K=13 Q6_K=14 IQ4_XS=23)",
+                      i, s.type);
+            return B200Q_EUNSUPPORTED;
+        }
+        if (s.K != c.K) {
+            set_error("segment %d: K=%d differs from the call's K=%d", i, s.K, c.K);
+            return B200Q_EINVAL;
+        }
+        if (!x8 && (s.x8 != c.x8 || s.xmeta != c.xmeta || s.xsumq != c.xsumq)) {
+            set_error("segment %d: segments of one call must share x8/xmeta/xsumq", i);
+            return B200Q_EINVAL;
+        }
+        if (s.n_rows < 1 || !s.w || !s.out) {
+            set_error("segment %d: n_rows must be >= 1 and w/out non-null", i);
+            return B200Q_EINVAL;
+        }
+        if (!aligned(s.w, 16)) {
+            set_error("segment %d: weight pointer must be 16-byte aligned", i);
+            return B200Q_EINVAL;
+        }
+        if (s.out_stride < s.n_rows && TB > 1) {
+            set_error("segment %d: out_stride %d < n_rows %d", i, s.out_stride, s.n_rows);
+            return B200Q_EINVAL;
+        }
+        if (rows > INT32_MAX - s.n_rows) {
+            set_error("too many rows in one call");
+            return B200Q_EINVAL;
+        }
+        rows += s.n_rows;
+        SegDev & d = c.seg[i];
+        d.w = static_cast<const uint8_t *>(s.w);
+        d.out = s.out;
+        d.residual = s.residual;
+        d.alpha = s.alpha;
+        d.type = (int32_t)s.type;
+        d.n_rows = s.n_rows;
+        d.out_stride = s.out_stride;
+        d.row_end = rows;
+    }
+    c.total_rows = rows;
+    return B200Q_OK;
+}
+
+} // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+const char * b200q_last_error(void) {
+    return g_err;
+}
+
+int b200q_version(void) {
+    return B200Q_VERSION;
+}
+
+size_t b200q_row_bytes(uint32_t type, int64_t K) {
+    return type_ok(type) && K > 0 ? (size_t)(K / 256) * (size_t)sb_bytes(type) : 0;
+}
+
+int b200q_xq(void * stream, const float * x, const float * up, int x_stride, int up_stride, int8_t * x8,
+             float * xmeta, int32_t * xsumq, int TB, int K) {
+    if (!x || !x8 || !xmeta || !xsumq) {
+        set_error("b200q_xq: x, x8, xmeta, xsumq must be non-null");
+        return B200Q_EINVAL;
+    }
+    if (TB < 1 || K < 32 || (K & 31)) {
+        set_error("b200q_xq: TB >= 1 and K a positive multiple of 32 required (TB=%d K=%d)", TB, K);
+        return B200Q_EINVAL;
+    }
+    if (x_stride < K || (up && up_stride < K)) {
+        set_error("b200q_xq: row strides must be >= K");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, x, up, x_stride, up_stride, x8, xmeta, xsumq, TB, K, false));
+    return B200Q_OK;
+}
+
+int b200q_i8_gemm(void * stream, const b200q_seg * segs, int n_segs, int TB) {
+    CallDev c;
+    const int rc = build_call(segs, n_segs, TB, nullptr, nullptr, nullptr, c);
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    B200Q_CUDA_OK(launch_gemv_rows((cudaStream_t)stream, c, false));
+    return B200Q_OK;
+}
+
+int b200q_i8_gemv(void * stream, const b200q_seg * segs, int n_segs) {
+    return b200q_i8_gemm(stream, segs, n_segs, 1);
+}
+
+int b200q_quant_gemv(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
+                     int32_t * xsumq) {
+    if (!x8 || !xmeta || !xsumq) {
+        set_error("b200q_quant_gemv: scratch x8/xmeta/xsumq must be non-null");
+        return B200Q_EINVAL;
+    }
+    CallDev c;
+    const int rc = build_call(segs, n_segs, TB, x8, xmeta, xsumq, c);
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    const b200q_seg & s0 = segs[0];
+    if (!s0.x || s0.x_stride < s0.K) {
+        set_error("b200q_quant_gemv: segs[0].x must be non-null with x_stride >= K");
+        return B200Q_EINVAL;
+    }
+    for (int i = 1; i < n_segs; i++) {
+        if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
+            set_error("b200q_quant_gemv: segment %d does not share the call's activation", i);
+            return B200Q_EINVAL;
+        }
+    }
+    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
+                            s0.K, true));
+    B200Q_CUDA_OK(launch_gemv_rows((cudaStream_t)stream, c, true));
+    return B200Q_OK;
+}
+
+int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int n_rows, const int8_t * x8, int TB,
+                        int t, int32_t * wd) {
+    if (!w || !x8 || !wd || !type_ok(type)) {
+        set_error("b200q_i8_block_dots: null pointer or unsupported type %u", type);
+        return type_ok(type) ? B200Q_EINVAL : B200Q_EUNSUPPORTED;
+    }
+    if (K < 256 || (K & 255) || n_rows < 1 || TB < 1 || t < 0 || t >= TB || !aligned(w, 16) || !aligned(x8, 16)) {
+        set_error("b200q_i8_block_dots: bad shape or alignment (K=%d n_rows=%d TB=%d t=%d)", K, n_rows, TB, t);
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(
+        launch_block_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows, x8, TB, t, wd));
+    return B200Q_OK;
+}
+
+int b200q_synchronize(void * stream) {
+    B200Q_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200Q_OK;
+}
+
+} // extern "C"

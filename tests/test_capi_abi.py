@@ -1,0 +1,61 @@
+"""The C-ABI library loads and exports every entry point include/b200q.h declares.
+No compute call is made here (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    src = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200q_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_the_path():
+    syms = declared_symbols()
+    for need in ("b200q_xq", "b200q_i8_gemv", "b200q_i8_gemm", "b200q_quant_gemv", "b200q_i8_block_dots",
+                 "b200q_synchronize", "b200q_last_error"):
+        assert need in syms
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg.load_lib()
+    for s in declared_symbols():
+        assert hasattr(lib.dll, s), f"{s} declared in include/b200q.h but not exported"
+    assert lib.dll.b200q_version() == 1
+
+
+def test_row_bytes_table(pkg, po):
+    # quant_row_bytes of the reference (src/common/quant.h:1177-1198; tests/model/test_quant_synth.cpp:106-111)
+    lib = pkg.load_lib()
+    for t, per256 in ((12, 144), (13, 176), (14, 210), (8, 272), (23, 136)):
+        assert lib.dll.b200q_row_bytes(t, 4096) == per256 * 16 == po.row_bytes(t, 4096)
+    assert lib.dll.b200q_row_bytes(2, 4096) == 0
+
+
+def test_argument_errors_need_no_gpu(pkg):
+    """Validation happens before any CUDA call and reports through status + last_error."""
+    from sycl_infer_b200.capi import Seg, EINVAL, EUNSUPPORTED
+    lib = pkg.load_lib()
+    seg = (Seg * 1)(Seg(0x1000, 12, 300, 4, None, 0, None, 0x2000, 4, None, 1.0, 0x3000, 0x4000, 0x5000))
+    assert lib.dll.b200q_i8_gemv(None, seg, 1) == EINVAL and "multiple of 256" in lib.last_error()
+    seg[0].K = 512
+    seg[0].type = 2
+    assert lib.dll.b200q_i8_gemv(None, seg, 1) == EUNSUPPORTED and "unsupported ggml type" in lib.last_error()
+    seg[0].type = 12
+    seg[0].w = 0x1001
+    assert lib.dll.b200q_i8_gemv(None, seg, 1) == EINVAL and "16-byte aligned" in lib.last_error()
+    assert lib.dll.b200q_i8_gemv(None, seg, 0) == EINVAL
+    assert lib.dll.b200q_xq(None, None, None, 0, 0, None, None, None, 1, 256) == EINVAL
+
+
+def test_no_cpu_fallback_without_device(pkg):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(RuntimeError):
+        pkg.make_cuda_backend(0)

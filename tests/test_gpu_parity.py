@@ -1,0 +1,237 @@
+"""GPU parity: every operator is called through the C ABI and compared with the oracle
+on the same seeded inputs.  Integer results are bit-exact; fp32 outputs are within 1e-5
+of the row's sum of |terms| (the tolerance the benchmark's north star states; the
+yardstick is the one the reference's own tests use for cancelling dot products,
+tests/backend/gpu/kernels/test_moe_grp_q6.cpp:184-206 of the reference)."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+TOL = 1e-5
+TYPES = (12, 13, 14, 8, 23)
+G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_vectors.npz"))
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def gpu_xq(be, x, up=None, TB=1):
+    from sycl_infer_b200.backend import alloc_act
+    x = np.ascontiguousarray(x, np.float32).reshape(TB, -1)
+    K = x.shape[1]
+    x8, xm, xs = alloc_act(TB, K)
+    dx = dev(x)
+    dup = None if up is None else dev(np.ascontiguousarray(up, np.float32).reshape(TB, -1))
+    be.xq(dx, dup, K, K, x8, xm, xs, None, TB, K)
+    be.synchronize()
+    return x8, xm, xs
+
+
+def gpu_gemm(be, t, w, K, N, act, TB, residual=None, alpha=1.0, out_stride=None, alias=False):
+    from sycl_infer_b200.backend import gemv_seg
+    out_stride = out_stride or N
+    out = torch.full((TB * out_stride,), 7.0, dtype=torch.float32, device="cuda")
+    res = None
+    if residual is not None:
+        if alias:
+            out.view(TB, out_stride)[:, :N] = dev(residual)
+            res = out
+        else:
+            r = np.zeros((TB, out_stride), np.float32)
+            r[:, :N] = residual
+            res = dev(r)
+    s = gemv_seg(w=dev(w), type=t, K=K, n_rows=N, out=out, out_stride=out_stride, residual=res, alpha=alpha,
+                 x8=dev(act.x8), xmeta=dev(act.xmeta), xsumq=dev(act.xsumq))
+    if TB == 1:
+        be.i8_gemv(s)
+    else:
+        be.i8_gemm(s, TB)
+    be.synchronize()
+    return out.cpu().numpy().reshape(TB, out_stride)
+
+
+def rel_err(got, ref, ab):
+    return float(np.max(np.abs(got.astype(np.float64) - ref) / np.maximum(ab, 1e-30)))
+
+
+@pytest.mark.parametrize("TB,K", [(1, 256), (1, 4096), (3, 5120), (16, 2048), (33, 512)])
+def test_xq_bit_exact(be, orc, pkg, TB, K):
+    x = pkg.synth.make_activation(TB, K, 300 + TB)
+    x[0, 32:64] = 0.0  # an all-zero group must encode as scale 0
+    a = orc.xq(x, None, TB)
+    x8, xm, xs = gpu_xq(be, x, None, TB)
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    assert np.array_equal(xm.cpu().numpy().view(np.uint32), a.xmeta.view(np.uint32))
+    assert np.array_equal(xs.cpu().numpy(), a.xsumq)
+
+
+def test_xq_golden_from_reference(be):
+    x8, xm, xs = gpu_xq(be, G["xq_x"], None, 3)
+    assert np.array_equal(x8.cpu().numpy(), G["xq_x8"])
+    assert np.array_equal(xm.cpu().numpy().view(np.uint32), G["xq_meta"].view(np.uint32))
+    assert np.array_equal(xs.cpu().numpy(), G["xq_sum"])
+
+
+@pytest.mark.parametrize("TB,K", [(1, 512), (4, 17408)])
+def test_xq_fused_silu(be, orc, pkg, TB, K):
+    """silu(x)*up goes through exp: the device evaluates it in double and rounds once.
+    Codes may differ from the host's expf only where a product lands on a rounding tie."""
+    x, up = pkg.synth.make_activation(TB, K, 310), pkg.synth.make_activation(TB, K, 311)
+    a = orc.xq(x, up, TB)
+    x8, xm, xs = gpu_xq(be, x, up, TB)
+    d = np.abs(x8.cpu().numpy().astype(np.int32) - a.x8.astype(np.int32))
+    assert d.max() <= 1 and np.count_nonzero(d) <= 1e-4 * d.size
+    sm = xm.cpu().numpy()
+    assert np.count_nonzero(sm.view(np.uint32) != a.xmeta.view(np.uint32)) <= 1e-3 * sm.size
+    assert np.max(np.abs(sm - a.xmeta)) <= 2.0 ** -10 * np.max(a.xmeta)
+
+
+def test_xq_fused_silu_golden(be):
+    x8, xm, _ = gpu_xq(be, G["xq_x"], G["xq_up"], 3)
+    d = np.abs(x8.cpu().numpy().astype(np.int32) - G["xq_x8_up"].astype(np.int32))
+    assert d.max() <= 1 and np.count_nonzero(d) <= 2
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("K,N,TB,tok", [(256, 3, 1, 0), (1024, 37, 1, 0), (4352, 9, 3, 2)])
+def test_block_dots_bit_exact(be, orc, po, pkg, t, K, N, TB, tok):
+    w = pkg.synth.make_weight(t, N, K, 400 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 401), None, TB)
+    want = orc.block_dots(t, w, K, N, a, tok)
+    wd = torch.empty(want.shape, dtype=torch.int32, device="cuda")
+    be.i8_block_dots(dev(w), t, K, N, dev(a.x8), TB, tok, wd)
+    be.synchronize()
+    assert np.array_equal(wd.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("K,N", [(256, 1), (512, 5), (1024, 37), (5120, 64), (17408, 11)])
+def test_gemv_parity(be, orc, pkg, t, K, N):
+    w = pkg.synth.make_weight(t, N, K, 500 + t)
+    a = orc.xq(pkg.synth.make_activation(1, K, 501))
+    ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
+    got = gpu_gemm(be, t, w, K, N, a, 1)
+    assert rel_err(got, ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("TB", [2, 3, 5, 8, 16, 33])
+def test_gemm_parity(be, orc, pkg, t, TB):
+    K, N = 1024, 45
+    w = pkg.synth.make_weight(t, N, K, 600 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 601), None, TB)
+    res = pkg.synth.make_activation(TB, N, 602)
+    ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=0.5)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=0.5) + np.abs(res)
+    got = gpu_gemm(be, t, w, K, N, a, TB, residual=res, alpha=0.5)
+    assert rel_err(got, ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("t", (12, 14))
+def test_residual_alias_and_wide_stride(be, orc, pkg, t):
+    """residual may alias out (in-place residual add, src/engine/graph.cpp:299,355 of the
+    reference) and out_stride may exceed n_rows (gate|up halves, graph.cpp:342-343);
+    columns beyond n_rows must stay untouched."""
+    K, N, TB, stride = 512, 19, 3, 50
+    w = pkg.synth.make_weight(t, N, K, 700 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 701), None, TB)
+    res = pkg.synth.make_activation(TB, N, 702)
+    ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=2.0)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=2.0) + np.abs(res)
+    got = gpu_gemm(be, t, w, K, N, a, TB, residual=res, alpha=2.0, out_stride=stride, alias=True)
+    assert rel_err(got[:, :N], ref, ab) <= TOL
+    assert np.all(got[:, N:] == 7.0)
+
+
+def test_multi_segment_call_mixed_types(be, orc, pkg):
+    """q|k|v of one call: three segments, two types, one shared activation, one launch."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    K, TB = 1024, 2
+    shapes = [(12, 96), (12, 24), (14, 24)]
+    x = pkg.synth.make_activation(TB, K, 801)
+    a = orc.xq(x, None, TB)
+    x8, xm, xs = alloc_act(TB, K)
+    dx = dev(x)
+    segs, outs, ws = [], [], []
+    for i, (t, n) in enumerate(shapes):
+        w = pkg.synth.make_weight(t, n, K, 810 + i)
+        ws.append(w)
+        o = torch.zeros(TB * n, dtype=torch.float32, device="cuda")
+        outs.append(o)
+        segs.append(gemv_seg(w=dev(w), type=t, K=K, n_rows=n, x=dx, x_stride=K, out=o, out_stride=n, x8=x8,
+                             xmeta=xm, xsumq=xs))
+    be.quant_gemv(segs, TB)
+    be.synchronize()
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    for (t, n), w, o in zip(shapes, ws, outs):
+        ref, ab = orc.gemm(t, w, K, n, a), orc.gemm_abs(t, w, K, n, a)
+        assert rel_err(o.cpu().numpy().reshape(TB, n), ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("t", (12, 13, 14))
+def test_golden_reference_outputs(be, orc, t):
+    """Outputs of the reference's own compiled CPU path (default build), from the fixture."""
+    K, N = 512, 5
+    a1 = orc.xq(G["xq_x"][0])
+    a3 = orc.xq(G["xq_x"], None, TB=3)
+    got1 = gpu_gemm(be, t, G[f"w_{t}"], K, N, a1, 1, residual=G["res"][:1], alpha=0.75)
+    got3 = gpu_gemm(be, t, G[f"w_{t}"], K, N, a3, 3, residual=G["res"], alpha=0.75)
+    ab1 = orc.gemm_abs(t, G[f"w_{t}"], K, N, a1, alpha=0.75) + np.abs(G["res"][:1])
+    ab3 = orc.gemm_abs(t, G[f"w_{t}"], K, N, a3, alpha=0.75) + np.abs(G["res"])
+    assert rel_err(got1, G[f"gemv_{t}"][None, :], ab1) <= TOL
+    assert rel_err(got3, G[f"gemm3_{t}"], ab3) <= TOL
+
+
+def test_reference_unit_test_case(be, orc):
+    a = orc.xq(G["ut_x"])
+    got = gpu_gemm(be, 12, G["ut_w"], 256, 3, a, 1)
+    ab = orc.gemm_abs(12, G["ut_w"], 256, 3, a)
+    assert rel_err(got, G["ut_gemv"][None, :], ab) <= TOL
+
+
+def test_config0_full_size(be, orc, pkg):
+    """Benchmark configuration 0 at full size: 4096x4096 Q4_K, batch 1."""
+    K = N = 4096
+    w = pkg.synth.make_weight(12, N, K, 0xB200)
+    x = pkg.synth.make_activation(1, K, 0xB201)
+    a = orc.xq(x)
+    x8, xm, xs = gpu_xq(be, x)
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    ref, ab = orc.gemm(12, w, K, N, a), orc.gemm_abs(12, w, K, N, a)
+    assert rel_err(gpu_gemm(be, 12, w, K, N, a, 1), ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("name", ["k", "v", "gate", "down"])
+def test_config1_layer_shapes_full_size(be, orc, pkg, name):
+    """Dense-layer projections of benchmark configuration 1 at full size (batch 1), plus
+    size-independent properties: alpha-linearity and row-slice consistency are exact."""
+    shape = {n: (t, r, k) for n, t, r, k in pkg.synth.dense_layer_shapes("Q4_K_M")}[name]
+    t, N, K = shape
+    w = pkg.synth.make_weight(t, N, K, 900)
+    a = orc.xq(pkg.synth.make_activation(1, K, 901))
+    ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
+    got = gpu_gemm(be, t, w, K, N, a, 1)
+    assert rel_err(got, ref, ab) <= TOL
+    got2 = gpu_gemm(be, t, w, K, N, a, 1, alpha=2.0)
+    assert np.array_equal(got2, 2.0 * got)  # scaling by a power of two is exact
+    rb = pkg.synth.row_bytes(t, K)
+    r0, r1 = N // 3, N // 3 + 100
+    part = gpu_gemm(be, t, w[r0 * rb:r1 * rb], K, r1 - r0, a, 1)
+    assert np.array_equal(part[0], got[0, r0:r1])
+
+
+def test_errors_are_reported_not_swallowed(be, pkg):
+    from sycl_infer_b200.backend import gemv_seg
+    from sycl_infer_b200.capi import B200QError
+    w = torch.zeros(144 * 4, dtype=torch.uint8, device="cuda")
+    o = torch.zeros(4, dtype=torch.float32, device="cuda")
+    with pytest.raises(B200QError) as e:
+        be.i8_gemv(gemv_seg(w=w, type=2, K=256, n_rows=4, out=o, x8=w, xmeta=o, xsumq=o))
+    assert e.value.code == 2
+    with pytest.raises(B200QError):
+        be.i8_gemv(gemv_seg(w=w, type=12, K=256, n_rows=4, out=o))  # no activation views
