@@ -96,6 +96,12 @@ int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs,
 int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int n_rows, const int8_t * x8, int TB,
                         int t, int32_t * wd);
 
+/* Device-side error word.  Kernels never spin without a limit: a wait that runs out stores
+ * B200Q_ETIMEOUT here and the kernel returns.  Synchronizes with the device (reads a device
+ * symbol); `clear` != 0 resets the word after reading.  No counterpart in the reference,
+ * whose kernels have no device-side waits. */
+int b200q_device_status(int * status /*host*/, int clear);
+
 /* compute_backend::synchronize (src/backend/backend.h:123): blocks until the stream drained. */
 int b200q_synchronize(void * stream);
 

@@ -127,6 +127,12 @@ class cuda_backend:
     def i8_block_dots(self, w, type, K, n_rows, x8, TB, t, wd):
         self.lib.check(self.lib.i8_block_dots(self._s(), _ptr(w), type, K, n_rows, _ptr(x8), TB, t, _ptr(wd)))
 
+    def device_status(self, clear=True):
+        """Error word set by a kernel whose bounded wait ran out (0 = none)."""
+        st = C.c_int(0)
+        self.lib.check(self.lib.device_status(C.byref(st), 1 if clear else 0))
+        return st.value
+
     # compute_backend::synchronize (backend.h:123): must truly block
     def synchronize(self):
         self.lib.check(self.lib.synchronize(self._s()))

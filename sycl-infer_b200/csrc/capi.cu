@@ -1,6 +1,7 @@
 // C ABI of the library: argument validation, error reporting, kernel dispatch.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "launch.h"
@@ -107,6 +108,19 @@ static int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t *
     return B200Q_OK;
 }
 
+// Kernel choice: 1..8 tokens stream the weights once through shared memory; larger
+// token counts take the general rows kernel.  B200Q_KERNEL=rows forces the latter (A/B).
+static cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
+    static const bool force_rows = [] {
+        const char * e = getenv("B200Q_KERNEL");
+        return e && strcmp(e, "rows") == 0;
+    }();
+    if (!force_rows && stream_supported(c)) {
+        return launch_gemv_stream(s, c, pdl_secondary);
+    }
+    return launch_gemv_rows(s, c, pdl_secondary);
+}
+
 } // namespace b200q
 
 using namespace b200q;
@@ -149,7 +163,7 @@ int b200q_i8_gemm(void * stream, const b200q_seg * segs, int n_segs, int TB) {
     if (rc != B200Q_OK) {
         return rc;
     }
-    B200Q_CUDA_OK(launch_gemv_rows((cudaStream_t)stream, c, false));
+    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, false));
     return B200Q_OK;
 }
 
@@ -181,7 +195,7 @@ int b200q_quant_gemv(void * stream, const b200q_seg * segs, int n_segs, int TB, 
     }
     B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
                             s0.K, true));
-    B200Q_CUDA_OK(launch_gemv_rows((cudaStream_t)stream, c, true));
+    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));
     return B200Q_OK;
 }
 
@@ -197,6 +211,18 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
     }
     B200Q_CUDA_OK(
         launch_block_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows, x8, TB, t, wd));
+    return B200Q_OK;
+}
+
+int b200q_device_status(int * status, int clear) {
+    if (!status) {
+        set_error("b200q_device_status: status must be non-null");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(read_device_status(status, clear != 0));
+    if (*status != 0) {
+        set_error("a bounded device-side wait ran out (status %d)", *status);
+    }
     return B200Q_OK;
 }
 

@@ -55,30 +55,62 @@ struct GmemW {
     }
 };
 
-// Shared memory (a staged tile).  The tile buffer carries slack after the last byte, so
-// the trailing word of a misaligned read may be fetched unconditionally.
+// Shared memory (a staged tile), explicit ld.shared.  The tile buffer carries slack after
+// the last byte, so the trailing word of a misaligned read may be fetched unconditionally.
+__device__ __forceinline__ uint32_t smem_u32(const void * p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
 struct SmemW {
-    static __device__ __forceinline__ uint4 ld128(const uint8_t * p) {
-        return *reinterpret_cast<const uint4 *>(p);
-    }
-    static __device__ __forceinline__ uint2 ld64(const uint8_t * p) {
-        return *reinterpret_cast<const uint2 *>(p);
-    }
-    static __device__ __forceinline__ uint32_t ld16(const uint8_t * p) {
-        return *reinterpret_cast<const uint16_t *>(p);
-    }
+    static __device__ __forceinline__ uint4 ld128(const uint8_t * p) { return lds128(smem_u32(p)); }
+    static __device__ __forceinline__ uint2 ld64(const uint8_t * p) { return lds64(smem_u32(p)); }
+    static __device__ __forceinline__ uint32_t ld16(const uint8_t * p) { return lds16(smem_u32(p)); }
     template <int N> static __device__ __forceinline__ void ld_a2(const uint8_t * p, uint32_t (&out)[N]) {
-        const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+        const uint32_t a = smem_u32(p);
         const uint32_t sh = (a & 2u) * 8;
-        const uint32_t * q = reinterpret_cast<const uint32_t *>(p - (a & 2u));
-        uint32_t prev = q[0];
+        const uint32_t q = a & ~3u;
+        uint32_t prev = lds32(q);
 #pragma unroll
         for (int k = 0; k < N; k++) {
-            const uint32_t next = q[k + 1];
+            const uint32_t next = lds32(q + 4 * (k + 1));
             out[k] = __funnelshift_r(prev, next, sh);
             prev = next;
         }
     }
+};
+
+// ---- activation memory policies (same group-major layout in either space) ---------
+struct GmemA {
+    static __device__ __forceinline__ uint4 ld128(const int8_t * p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+    static __device__ __forceinline__ uint2 ld64(const int8_t * p) { return __ldg(reinterpret_cast<const uint2 *>(p)); }
+    static __device__ __forceinline__ float ldf(const float * p) { return __ldg(p); }
+    static __device__ __forceinline__ int ldi(const int32_t * p) { return __ldg(p); }
+};
+struct SmemA {
+    static __device__ __forceinline__ uint4 ld128(const int8_t * p) { return lds128(smem_u32(p)); }
+    static __device__ __forceinline__ uint2 ld64(const int8_t * p) { return lds64(smem_u32(p)); }
+    static __device__ __forceinline__ float ldf(const float * p) { return __uint_as_float(lds32(smem_u32(p))); }
+    static __device__ __forceinline__ int ldi(const int32_t * p) { return (int)lds32(smem_u32(p)); }
 };
 
 __device__ __forceinline__ int dp4a_us(uint32_t w, uint32_t x, int acc) { // unsigned weights x signed codes
@@ -150,11 +182,12 @@ template <int TYPE, class WM> struct PartK45 {
         }
     }
     // exact int32 sums of this part against token t; idx[] = position in the row's dot array
+    template <class AM = GmemA>
     __device__ __forceinline__ void dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const size_t gi = (size_t)(G0 + g0 + i) * a.TB + t;
-            const uint4 x = __ldg(reinterpret_cast<const uint4 *>(a.x8 + gi * 32 + 16 * half));
+            const uint4 x = AM::ld128(a.x8 + gi * 32 + 16 * half);
             const uint32_t * w = i ? hi : lo;
             wd[i] = dp4a_us(w[0], x.x, dp4a_us(w[1], x.y, dp4a_us(w[2], x.z, dp4a_us(w[3], x.w, 0))));
             idx[i] = G0 + g0 + i;
@@ -163,15 +196,16 @@ template <int TYPE, class WM> struct PartK45 {
     __device__ __forceinline__ void raw_dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
         dots(a, G0, t, wd, idx);
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ float term(const ActView & a, int G0, int t) const {
         int wd[NP], idx[NP];
-        dots(a, G0, t, wd, idx);
+        dots<AM>(a, G0, t, wd, idx);
         float r = 0.f;
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const size_t gi = (size_t)idx[i] * a.TB + t;
-            const float sx = __ldg(a.xmeta + 2 * gi);
-            const int xs = __ldg(a.xsumq + 2 * gi + half);
+            const float sx = AM::ldf(a.xmeta + 2 * gi);
+            const int xs = AM::ldi(a.xsumq + 2 * gi + half);
             r += sx * (dsc[i] * (float)wd[i] - dmm[i] * (float)xs);
         }
         return r;
@@ -216,11 +250,12 @@ template <class WM> struct Part<kQ6_K, WM> {
     }
     // wd[] here are the dots of (q-32): what `term` needs.  raw_dots adds the 32*sum(x)
     // back so the parity instrument reports the reference's raw-code sums.
+    template <class AM = GmemA>
     __device__ __forceinline__ void dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
 #pragma unroll
         for (int p = 0; p < 4; p++) {
             const size_t gi = (size_t)(G0 + gb + p) * a.TB + t;
-            const uint2 x = __ldg(reinterpret_cast<const uint2 *>(a.x8 + gi * 32 + l0));
+            const uint2 x = AM::ld64(a.x8 + gi * 32 + l0);
             wd[p] = dp4a_ss(v[p][0], x.x, dp4a_ss(v[p][1], x.y, 0));
             idx[p] = G0 + gb + p;
         }
@@ -236,13 +271,14 @@ template <class WM> struct Part<kQ6_K, WM> {
             idx[p] = 2 * idx[p] + (l0 >> 4);
         }
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ float term(const ActView & a, int G0, int t) const {
         int wd[NP], idx[NP];
-        dots(a, G0, t, wd, idx);
+        dots<AM>(a, G0, t, wd, idx);
         float r = 0.f;
 #pragma unroll
         for (int p = 0; p < 4; p++) {
-            const float sx = __ldg(a.xmeta + 2 * ((size_t)idx[p] * a.TB + t));
+            const float sx = AM::ldf(a.xmeta + 2 * ((size_t)idx[p] * a.TB + t));
             r += (sx * ds[p]) * (float)wd[p];
         }
         return r;
@@ -285,10 +321,11 @@ template <class WM> struct Part<kIQ4_XS, WM> {
             v[4 + k] = iq4nl_lookup4((qw[k] >> 4) & 0x0F0F0F0Fu);
         }
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ void dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
         const size_t gi = (size_t)(G0 + g) * a.TB + t;
-        const uint4 x0 = __ldg(reinterpret_cast<const uint4 *>(a.x8 + gi * 32));
-        const uint4 x1 = __ldg(reinterpret_cast<const uint4 *>(a.x8 + gi * 32 + 16));
+        const uint4 x0 = AM::ld128(a.x8 + gi * 32);
+        const uint4 x1 = AM::ld128(a.x8 + gi * 32 + 16);
         int s = dp4a_ss(v[0], x0.x, dp4a_ss(v[1], x0.y, dp4a_ss(v[2], x0.z, dp4a_ss(v[3], x0.w, 0))));
         s = dp4a_ss(v[4], x1.x, dp4a_ss(v[5], x1.y, dp4a_ss(v[6], x1.z, dp4a_ss(v[7], x1.w, s))));
         wd[0] = s;
@@ -297,10 +334,11 @@ template <class WM> struct Part<kIQ4_XS, WM> {
     __device__ __forceinline__ void raw_dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
         dots(a, G0, t, wd, idx);
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ float term(const ActView & a, int G0, int t) const {
         int wd[NP], idx[NP];
-        dots(a, G0, t, wd, idx);
-        const float sx = __ldg(a.xmeta + 2 * ((size_t)idx[0] * a.TB + t));
+        dots<AM>(a, G0, t, wd, idx);
+        const float sx = AM::ldf(a.xmeta + 2 * ((size_t)idx[0] * a.TB + t));
         return (sx * dl) * (float)wd[0];
     }
 };
@@ -318,10 +356,11 @@ template <class WM> struct Part<kQ8_0, WM> {
         d = h2f((uint16_t)WM::ld16(blk));
         WM::template ld_a2<8>(blk + 2, v);
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ void dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
         const size_t gi = (size_t)(G0 + g) * a.TB + t;
-        const uint4 x0 = __ldg(reinterpret_cast<const uint4 *>(a.x8 + gi * 32));
-        const uint4 x1 = __ldg(reinterpret_cast<const uint4 *>(a.x8 + gi * 32 + 16));
+        const uint4 x0 = AM::ld128(a.x8 + gi * 32);
+        const uint4 x1 = AM::ld128(a.x8 + gi * 32 + 16);
         int s = dp4a_ss(v[0], x0.x, dp4a_ss(v[1], x0.y, dp4a_ss(v[2], x0.z, dp4a_ss(v[3], x0.w, 0))));
         s = dp4a_ss(v[4], x1.x, dp4a_ss(v[5], x1.y, dp4a_ss(v[6], x1.z, dp4a_ss(v[7], x1.w, s))));
         wd[0] = s;
@@ -330,10 +369,11 @@ template <class WM> struct Part<kQ8_0, WM> {
     __device__ __forceinline__ void raw_dots(const ActView & a, int G0, int t, int (&wd)[NP], int (&idx)[NP]) const {
         dots(a, G0, t, wd, idx);
     }
+    template <class AM = GmemA>
     __device__ __forceinline__ float term(const ActView & a, int G0, int t) const {
         int wd[NP], idx[NP];
-        dots(a, G0, t, wd, idx);
-        const float sx = __ldg(a.xmeta + 2 * ((size_t)idx[0] * a.TB + t));
+        dots<AM>(a, G0, t, wd, idx);
+        const float sx = AM::ldf(a.xmeta + 2 * ((size_t)idx[0] * a.TB + t));
         return (sx * d) * (float)wd[0];
     }
 };

@@ -235,3 +235,8 @@ def test_errors_are_reported_not_swallowed(be, pkg):
     assert e.value.code == 2
     with pytest.raises(B200QError):
         be.i8_gemv(gemv_seg(w=w, type=12, K=256, n_rows=4, out=o))  # no activation views
+
+
+def test_zy_no_device_side_wait_ran_out(be):
+    """Every mbarrier wait in the streaming kernel is bounded; none may have expired."""
+    assert be.device_status() == 0
