@@ -209,8 +209,15 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
         set_error("b200q_i8_block_dots: bad shape or alignment (K=%d n_rows=%d TB=%d t=%d)", K, n_rows, TB, t);
         return B200Q_EINVAL;
     }
-    B200Q_CUDA_OK(
-        launch_block_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows, x8, TB, t, wd));
+    // same rule as the GEMV dispatch: up to 8 tokens run the streaming kernel's decode path,
+    // more tokens the rows kernel's
+    if (TB <= 8) {
+        B200Q_CUDA_OK(launch_unit_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows, x8,
+                                       TB, t, wd));
+    } else {
+        B200Q_CUDA_OK(launch_block_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows,
+                                        x8, TB, t, wd));
+    }
     return B200Q_OK;
 }
 

@@ -1,40 +1,42 @@
 // Streaming decode GEMV for 1..8 tokens: the HBM-bound kernel of the library.
 //
-// Data movement.  The raw GGUF block stream of 8 consecutive weight rows x KB superblocks
-// is brought into shared memory by bulk asynchronous copies (cp.async.bulk, the 1-D TMA
-// path, no multicast) that complete on an mbarrier; a ring of STAGES such tiles keeps
-// ~100 KB per CTA in flight so the copy engine, not the warps, hides HBM latency.  A copy
-// must start on a 16-byte boundary and be a multiple of 16 bytes long: a row segment that
-// starts at address A is fetched from A & ~15 and decoded from offset A & 15 inside its
-// slot (Q6_K rows are only 2-byte aligned, IQ4_XS 8); the bytes read beyond either end lie
-// in the same 16-byte line as valid bytes, so they are always mapped.
+// Data movement.  A tile is the raw GGUF block stream of `rows_per_tile` consecutive weight
+// rows x kb superblocks.  It is brought into shared memory by bulk asynchronous copies
+// (cp.async.bulk, the 1-D TMA path, no multicast), one per row, that complete on an
+// mbarrier; a ring of tiles keeps ~75 KB per CTA in flight so the copy engine, not the
+// warps, hides HBM latency.  A copy must start on a 16-byte boundary and be a multiple of 16
+// bytes long: a row segment that starts at address A is fetched from A & ~15 and decoded
+// from offset A & 15 inside its slot (Q6_K rows are only 2-byte aligned, IQ4_XS 8); the
+// bytes read beyond either end lie in the same 16-byte line as valid bytes, so they are
+// always mapped.
 //
 // Roles.  Warp 8 is the producer: lane r issues the copy of row r of the tile.  Warps 0..7
-// are consumers: warp w owns row w of the tile for the whole K loop, so a row's partial
-// sums stay in registers and no cross-warp reduction exists.  Inside a tile lane l owns
-// part (l & 7) of superblocks (l >> 3), (l >> 3) + 4, ...  The quantized activation of a
-// single-token call is staged once per CTA in shared memory; for 2..8 tokens it is read
-// through L1.
+// are consumers: warp w owns rows RW*w .. RW*w+RW-1 of the tile for the whole K loop, so a
+// row's partial sums stay in registers and no cross-warp reduction exists.  Four lanes
+// cover a superblock (64 weights each, see units.cuh); the activation of a unit is loaded
+// once and used for all RW rows.  A single-token call stages its quantized activation once
+// per CTA in shared memory; for 2..8 tokens it is read through L1.
 //
-// Every wait on an mbarrier is bounded; a wait that runs out records an error status the
-// host can read (b200q_device_status) and the CTA leaves its loop.
+// Every wait on an mbarrier is bounded by a clock budget; a wait that runs out records an
+// error status the host can read (b200q_device_status) and the CTA leaves its loop.
+#include <cstdlib>
 #include <type_traits>
 
-#include "decode.cuh"
 #include "launch.h"
+#include "units.cuh"
 
 namespace b200q {
 
-constexpr int kRowsPerTile = 8;
 constexpr int kConsumerWarps = 8;
 constexpr int kStreamThreads = 32 * (kConsumerWarps + 1);
 constexpr long long kSpinCycles = 2000000000LL; // about one second of SM clocks
+constexpr int kSmemBudget = 110 * 1024;         // two CTAs per SM
 
 __device__ int g_device_status = 0;
 
 struct StreamArgs {
     CallDev c;
-    int32_t grp_end[B200Q_MAX_SEGS]; // exclusive prefix of 8-row groups per segment
+    int32_t grp_end[B200Q_MAX_SEGS]; // exclusive prefix of row groups (tiles along rows) per segment
     int32_t n_groups;
     int32_t kb_max;     // superblocks per tile along K
     int32_t slot_bytes; // shared bytes reserved per row of a tile
@@ -76,45 +78,64 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void * src, uint32_
                  : "memory");
 }
 
-// Shared-memory layout: barriers | ring of tiles | staged activation (single token only)
-struct Smem {
-    uint32_t full, empty, tiles, x8, xmeta, xsumq;
-};
-__device__ __forceinline__ Smem smem_layout(const StreamArgs & a, uint32_t base, bool stage_x) {
-    Smem m;
-    m.full = base;
-    m.empty = base + 64;
-    m.tiles = base + 128;
-    m.x8 = m.tiles + (uint32_t)(a.stages * kRowsPerTile * a.slot_bytes);
-    m.xmeta = m.x8 + (stage_x ? (uint32_t)a.c.K : 0u);
-    m.xsumq = m.xmeta + (stage_x ? (uint32_t)(a.c.K / 32 * 8) : 0u);
-    return m;
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
-// One warp, one row, one tile: every lane walks its parts and adds the fp32 terms.
-template <int TYPE, int TT, class AM>
-__device__ __forceinline__ void consume_tile(const uint8_t * seg, int kb, int sb0, const ActView & act,
-                                             float (&acc)[TT]) {
+// Build the activation pack of superblocks [sb0, sb0+n) of token 0 (see units.cuh).
+__device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int sb0, int n, int tid, int nthr) {
+    for (int i = tid; i < 8 * n; i += nthr) {
+        const int g = 8 * sb0 + i; // TB == 1: group index == array index
+        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + (size_t)g * 32);
+        const uint4 x0 = __ldg(gx), x1 = __ldg(gx + 1);
+        const float sx = __ldg(c.xmeta + 2 * (size_t)g);
+        const int2 xs = __ldg(reinterpret_cast<const int2 *>(c.xsumq) + g);
+        const uint32_t p = pack_addr(pack, i);
+        sts128(p, x0.x, x0.y, x0.z, x0.w);
+        sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
+        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint((float)(xs.x + xs.y)));
+    }
+}
+
+// One warp, RW rows, one tile.  Lane l owns unit (l & 3) of superblocks (l >> 2), +8, ...
+template <int TYPE, int RW, int TT, class AS>
+__device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
+                                             int sb0, const AS & as, float (&acc)[RW][TT]) {
     const int lane = threadIdx.x & 31;
-    const int j = lane & 7;
-    for (int b = lane >> 3; b < kb; b += 4) {
-        Part<TYPE, SmemW> p;
-        p.load(seg + b * Fmt<TYPE>::SB, j);
+    const int u = lane & 3;
+    for (int b = lane >> 2; b < kb; b += 8) {
+        if constexpr (TT == 1) {
+            typename WUnit<TYPE>::Act a;
+            load_act<TYPE>(as, sb0 + b, u, 0, a);
 #pragma unroll
-        for (int i = 0; i < TT; i++) {
-            const int t = TT == 1 ? 0 : min(i, act.TB - 1);
-            acc[i] += p.template term<AM>(act, 8 * (sb0 + b), t);
+            for (int r = 0; r < RW; r++) {
+                WUnit<TYPE> w;
+                w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
+                acc[r][0] += w.term(a);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+                WUnit<TYPE> w;
+                w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    typename WUnit<TYPE>::Act a;
+                    load_act<TYPE>(as, sb0 + b, u, min(t, as.TB - 1), a);
+                    acc[r][t] += w.term(a);
+                }
+            }
         }
     }
 }
 
-template <int TT>
+template <int TT, int RW>
 __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr bool kStageX = (TT == 1);
-    using AM = typename std::conditional<kStageX, SmemA, GmemA>::type;
+    constexpr int kRows = kConsumerWarps * RW; // rows per tile
     const uint32_t base = smem_u32(smem_raw);
-    const Smem sm = smem_layout(a, base, kStageX);
+    const uint32_t bar_full = base, bar_empty = base + 64, tiles = base + 128;
+    const uint32_t pack = tiles + (uint32_t)(a.stages * kRows * a.slot_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = a.c.K >> 8;
     const int n_chunks = (nb + a.kb_max - 1) / a.kb_max;
@@ -122,8 +143,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            mbar_init(sm.full + 8 * s, 1);
-            mbar_init(sm.empty + 8 * s, kConsumerWarps);
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, kConsumerWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -139,8 +160,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                 si++;
             }
             const SegDev & sg = a.c.seg[si];
-            const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRowsPerTile;
-            const int rows = min(kRowsPerTile, sg.n_rows - row0);
+            const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRows;
+            const int rows = min(kRows, sg.n_rows - row0);
             const int sbb = sb_bytes(sg.type);
             const size_t row_bytes = (size_t)nb * sbb;
             for (int ch = 0; ch < n_chunks && alive; ch++, it++) {
@@ -159,21 +180,21 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                 }
                 uint32_t total = len;
 #pragma unroll
-                for (int o = 4; o > 0; o >>= 1) {
+                for (int o = 16; o > 0; o >>= 1) {
                     total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
                 }
-                alive = mbar_wait(sm.empty + 8 * stage, par);
+                alive = mbar_wait(bar_empty + 8 * stage, par);
                 alive = __all_sync(0xFFFFFFFFu, alive);
                 if (!alive) {
                     break;
                 }
                 if (lane == 0) {
-                    mbar_expect_tx(sm.full + 8 * stage, total);
+                    mbar_expect_tx(bar_full + 8 * stage, total);
                 }
                 __syncwarp();
                 if (lane < rows) {
-                    bulk_g2s(sm.tiles + (uint32_t)((stage * kRowsPerTile + lane) * a.slot_bytes), src, len,
-                             sm.full + 8 * stage);
+                    bulk_g2s(tiles + (uint32_t)((stage * kRows + lane) * a.slot_bytes), src, len,
+                             bar_full + 8 * stage);
                 }
             }
         }
@@ -181,28 +202,21 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     }
 
     // ---------------------------------------------------------------------- consumers
-    // The weights above do not depend on the activation quantizer; everything below does.
+    // The weight copies above do not depend on the activation quantizer; all below does.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    ActView act{a.c.x8, a.c.xmeta, a.c.xsumq, a.c.TB};
-    if (kStageX) {
-        const int tid = threadIdx.x, nthr = 32 * kConsumerWarps;
-        const uint4 * gx = reinterpret_cast<const uint4 *>(a.c.x8);
-        for (int i = tid; i < a.c.K / 16; i += nthr) {
-            const uint4 v = __ldg(gx + i);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sm.x8 + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z),
-                         "r"(v.w));
-        }
-        const uint2 * gm = reinterpret_cast<const uint2 *>(a.c.xmeta);
-        const uint2 * gs = reinterpret_cast<const uint2 *>(a.c.xsumq);
-        for (int i = tid; i < a.c.K / 32; i += nthr) {
-            const uint2 m = __ldg(gm + i), s = __ldg(gs + i);
-            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sm.xmeta + 8 * i), "r"(m.x), "r"(m.y));
-            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sm.xsumq + 8 * i), "r"(s.x), "r"(s.y));
-        }
+    if constexpr (TT == 1) {
+        stage_pack(pack, a.c, 0, nb, threadIdx.x, 32 * kConsumerWarps);
         asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory");
-        act.x8 = reinterpret_cast<const int8_t *>(smem_raw + (sm.x8 - base));
-        act.xmeta = reinterpret_cast<const float *>(smem_raw + (sm.xmeta - base));
-        act.xsumq = reinterpret_cast<const int32_t *>(smem_raw + (sm.xsumq - base));
+    }
+    using AS = typename std::conditional<TT == 1, PackA, GlobA>::type;
+    AS as;
+    if constexpr (TT == 1) {
+        as.pack = pack;
+    } else {
+        as.x8 = a.c.x8;
+        as.xmeta = a.c.xmeta;
+        as.xsumq = a.c.xsumq;
+        as.TB = a.c.TB;
     }
 
     uint32_t it = 0;
@@ -212,51 +226,67 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
             si++;
         }
         const SegDev & sg = a.c.seg[si];
-        const int row = (g - (si ? a.grp_end[si - 1] : 0)) * kRowsPerTile + warp;
-        const bool valid = row < sg.n_rows;
+        const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRows + warp * RW;
         const int sbb = sb_bytes(sg.type);
-        const uint32_t mis =
-            (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)row * nb * sbb) & 15); // chunk sizes keep it
-        float acc[TT];
+        uint32_t mis0[RW];
 #pragma unroll
-        for (int i = 0; i < TT; i++) {
-            acc[i] = 0.f;
+        for (int r = 0; r < RW; r++) {
+            mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)(row0 + r) * nb * sbb) & 15);
+        }
+        float acc[RW][TT];
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                acc[r][t] = 0.f;
+            }
         }
         for (int ch = 0; ch < n_chunks; ch++, it++) {
             const int stage = it % S;
-            if (!mbar_wait(sm.full + 8 * stage, (it / S) & 1)) {
+            if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1)) {
                 return;
             }
             const int sb0 = ch * a.kb_max;
             const int kb = min(a.kb_max, nb - sb0);
-            if (valid) {
-                const uint32_t off = (uint32_t)((stage * kRowsPerTile + warp) * a.slot_bytes) +
-                                     ((mis + (uint32_t)sb0 * sbb) & 15);
-                const uint8_t * seg = smem_raw + (sm.tiles - base) + off;
+            if (row0 < sg.n_rows) { // rows past the end of the segment hold stale bytes: results are dropped
+                const uint32_t slot0 = tiles + (uint32_t)((stage * kRows + warp * RW) * a.slot_bytes);
+                uint32_t mis[RW];
+#pragma unroll
+                for (int r = 0; r < RW; r++) {
+                    mis[r] = (mis0[r] + (uint32_t)sb0 * sbb) & 15;
+                }
                 switch (sg.type) {
-                case kQ4_K: consume_tile<kQ4_K, TT, AM>(seg, kb, sb0, act, acc); break;
-                case kQ5_K: consume_tile<kQ5_K, TT, AM>(seg, kb, sb0, act, acc); break;
-                case kQ6_K: consume_tile<kQ6_K, TT, AM>(seg, kb, sb0, act, acc); break;
-                case kIQ4_XS: consume_tile<kIQ4_XS, TT, AM>(seg, kb, sb0, act, acc); break;
-                default: consume_tile<kQ8_0, TT, AM>(seg, kb, sb0, act, acc); break;
+                case kQ4_K: consume_tile<kQ4_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                case kQ5_K: consume_tile<kQ5_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                case kQ6_K: consume_tile<kQ6_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                case kIQ4_XS: consume_tile<kIQ4_XS, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                default: consume_tile<kQ8_0, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
                 }
             }
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(sm.empty + 8 * stage);
+                mbar_arrive(bar_empty + 8 * stage);
             }
         }
 #pragma unroll
-        for (int i = 0; i < TT; i++) {
-            acc[i] = warp_sum(acc[i]);
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                acc[r][t] = warp_sum(acc[r][t]);
+            }
         }
+        // lane (r*TT + t) stores row r, token t
         float mine = 0.f;
 #pragma unroll
-        for (int i = 0; i < TT; i++) {
-            mine = lane == i ? acc[i] : mine;
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                mine = lane == r * TT + t ? acc[r][t] : mine;
+            }
         }
-        if (valid && lane < TT && lane < a.c.TB) {
-            const size_t o = (size_t)lane * sg.out_stride + row;
+        const int r = lane / TT, t = lane % TT;
+        if (lane < RW * TT && row0 + r < sg.n_rows && t < a.c.TB) {
+            const size_t o = (size_t)t * sg.out_stride + row0 + r;
             float v = sg.alpha * mine;
             if (sg.residual) {
                 v += sg.residual[o];
@@ -267,27 +297,57 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
 }
 
 // ---- host side ----------------------------------------------------------------------------
-static int kb_cap(int type) { // superblocks per tile: 8 rows x kb x SB stays near 24-27 KB
-    switch (type) {
-    case kQ4_K: return 20;
-    case kQ5_K: return 16;
-    case kQ6_K: return 16;
-    case kIQ4_XS: return 24;
-    default: return 12;
-    }
+static int env_int(const char * name, int dflt) {
+    const char * e = getenv(name);
+    return e && *e ? atoi(e) : dflt;
 }
 
-template <int TT> static cudaError_t launch_stream_tt(cudaStream_t s, const StreamArgs & a, size_t smem, int grid,
-                                                      bool pdl_secondary) {
+template <int TT, int RW>
+static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_secondary) {
     static bool configured = false; // per instantiation; setting the attribute twice is harmless
     if (!configured) {
-        cudaError_t e =
-            cudaFuncSetAttribute(gemv_stream_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<TT, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBudget);
         if (e != cudaSuccess) {
             return e;
         }
         configured = true;
     }
+    static const int kb_env = env_int("B200Q_KB", 0), st_env = env_int("B200Q_STAGES", 0);
+    static const int grid_env = env_int("B200Q_GRID", 0);
+    const CallDev & c = a.c;
+    constexpr int kRows = kConsumerWarps * RW;
+    const int nb = c.K >> 8;
+    int groups = 0, max_sbb = 0;
+    for (int i = 0; i < c.n_segs; i++) {
+        groups += (c.seg[i].n_rows + kRows - 1) / kRows;
+        a.grp_end[i] = groups;
+        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+    }
+    a.n_groups = groups;
+    // superblocks per tile: a multiple of 8 (all 32 lanes busy) keeping a tile near 20-28 KB
+    int kb = kb_env > 0 ? kb_env : (28 * 1024 / (kRows * max_sbb)) / 8 * 8;
+    kb = kb < 8 ? 8 : kb;
+    if (kb < nb) { // equal chunks, rounded up to a multiple of 8
+        const int n_chunks = (nb + kb - 1) / kb;
+        kb = (((nb + n_chunks - 1) / n_chunks + 7) / 8) * 8;
+    }
+    a.kb_max = kb < nb ? kb : nb;
+    a.slot_bytes = ((a.kb_max * max_sbb + 32 + 15) / 16) * 16;
+    const size_t pack_bytes = TT == 1 ? (size_t)nb * kPackSB : 0;
+    const size_t fixed = 128 + pack_bytes;
+    if (fixed + 2 * (size_t)kRows * a.slot_bytes > (size_t)kSmemBudget) {
+        return cudaErrorInvalidConfiguration;
+    }
+    int stages = (int)((kSmemBudget - fixed) / ((size_t)kRows * a.slot_bytes));
+    stages = stages > 8 ? 8 : stages;
+    if (st_env > 0 && st_env < stages) {
+        stages = st_env;
+    }
+    a.stages = stages;
+    const size_t smem = 128 + (size_t)stages * kRows * a.slot_bytes + pack_bytes;
+    int grid = grid_env > 0 ? grid_env : 2 * kSMs;
+    grid = groups < grid ? groups : grid;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kStreamThreads);
@@ -298,52 +358,27 @@ template <int TT> static cudaError_t launch_stream_tt(cudaStream_t s, const Stre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_secondary ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<TT>, a);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<TT, RW>, a);
 }
 
 bool stream_supported(const CallDev & c) {
-    return c.TB >= 1 && c.TB <= 8 && c.K <= 32768;
+    // the single-token activation pack (400 B per superblock) must leave room for two tiles
+    return c.TB >= 1 && c.TB <= 8 && c.K <= 24576;
 }
 
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     StreamArgs a;
     a.c = c;
-    const int nb = c.K >> 8;
-    int groups = 0, kb = 1 << 30, max_sbb = 0;
-    for (int i = 0; i < c.n_segs; i++) {
-        groups += (c.seg[i].n_rows + kRowsPerTile - 1) / kRowsPerTile;
-        a.grp_end[i] = groups;
-        kb = kb < kb_cap(c.seg[i].type) ? kb : kb_cap(c.seg[i].type);
-        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
-    }
-    a.n_groups = groups;
-    if (kb < nb) { // split K into equal chunks of a multiple of 4 superblocks (all lanes busy)
-        const int n_chunks = (nb + kb - 1) / kb;
-        kb = (((nb + n_chunks - 1) / n_chunks + 3) / 4) * 4;
-    }
-    a.kb_max = kb < nb ? kb : nb;
-    a.slot_bytes = ((a.kb_max * max_sbb + 32 + 15) / 16) * 16;
-    const bool stage_x = c.TB == 1;
-    const size_t xbytes = stage_x ? (size_t)c.K + (size_t)c.K / 2 : 0;
-    const size_t budget = 110 * 1024 - 128 - xbytes;
-    int stages = (int)(budget / ((size_t)kRowsPerTile * a.slot_bytes));
-    stages = stages > 8 ? 8 : stages;
-    if (stages < 2) {
-        return cudaErrorInvalidConfiguration;
-    }
-    a.stages = stages;
-    const size_t smem = 128 + (size_t)stages * kRowsPerTile * a.slot_bytes + xbytes;
-    const int grid = groups < 2 * kSMs ? groups : 2 * kSMs;
     if (c.TB == 1) {
-        return launch_stream_tt<1>(s, a, smem, grid, pdl_secondary);
+        return launch_stream_tt<1, 2>(s, a, pdl_secondary);
     }
     if (c.TB == 2) {
-        return launch_stream_tt<2>(s, a, smem, grid, pdl_secondary);
+        return launch_stream_tt<2, 2>(s, a, pdl_secondary);
     }
     if (c.TB <= 4) {
-        return launch_stream_tt<4>(s, a, smem, grid, pdl_secondary);
+        return launch_stream_tt<4, 1>(s, a, pdl_secondary);
     }
-    return launch_stream_tt<8>(s, a, smem, grid, pdl_secondary);
+    return launch_stream_tt<8, 1>(s, a, pdl_secondary);
 }
 
 cudaError_t read_device_status(int * status, bool clear) {
@@ -353,6 +388,68 @@ cudaError_t read_device_status(int * status, bool clear) {
         e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     }
     return e;
+}
+
+// ---- parity instrument on the streaming kernel's decode path -------------------------------
+// One CTA per weight row.  The row is copied into shared memory with the same misalignment
+// it has in global memory, the activation pack of token t is built, and every (superblock,
+// unit) is decoded and dotted by exactly the WUnit code the streaming kernel runs.
+constexpr int kDotsChunk = 16; // superblocks staged at a time
+
+template <int TYPE>
+__device__ __forceinline__ void dots_chunk(uint32_t wbase, uint32_t pack, int sb0, int n, int32_t * wd) {
+    for (int i = threadIdx.x; i < 4 * n; i += blockDim.x) {
+        const int b = i >> 2, u = i & 3;
+        PackA as{pack};
+        typename WUnit<TYPE>::Act act;
+        load_act<TYPE>(as, b, u, 0, act);
+        WUnit<TYPE> w;
+        w.load(wbase + (uint32_t)(b * Fmt<TYPE>::SB), u);
+        unit_exact<TYPE>(w, act, sb0 + b, u, wd);
+    }
+}
+
+__global__ void __launch_bounds__(128) unit_dots_kernel(const uint8_t * w, int type, int K, const int8_t * x8, int TB,
+                                                        int t, int32_t * wd) {
+    __shared__ __align__(16) uint8_t wbuf[kDotsChunk * 272 + 32];
+    __shared__ __align__(16) uint8_t pbuf[kDotsChunk * kPackSB];
+    const int nb = K >> 8, sbb = sb_bytes(type);
+    const int D = type == kQ6_K ? K / 16 : K / 32;
+    const uint8_t * row = w + (size_t)blockIdx.x * nb * sbb;
+    int32_t * out = wd + (size_t)blockIdx.x * D;
+    const uint32_t wb = smem_u32(wbuf), pk = smem_u32(pbuf);
+    for (int sb0 = 0; sb0 < nb; sb0 += kDotsChunk) {
+        const int n = min(kDotsChunk, nb - sb0);
+        const uint8_t * src = row + (size_t)sb0 * sbb;
+        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * sbb / 2; i += blockDim.x) { // blocks are 2-byte aligned
+            reinterpret_cast<uint16_t *>(wbuf + mis)[i] = reinterpret_cast<const uint16_t *>(src)[i];
+        }
+        for (int i = threadIdx.x; i < 8 * n; i += blockDim.x) {
+            const size_t gi = (size_t)(8 * sb0 + i) * TB + t;
+            const uint4 * gx = reinterpret_cast<const uint4 *>(x8 + gi * 32);
+            const uint4 x0 = __ldg(gx), x1 = __ldg(gx + 1);
+            const uint32_t p = pack_addr(pk, i);
+            sts128(p, x0.x, x0.y, x0.z, x0.w);
+            sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
+            sts128(p + 32, 0, 0, 0, 0);
+        }
+        __syncthreads();
+        switch (type) {
+        case kQ4_K: dots_chunk<kQ4_K>(wb + mis, pk, sb0, n, out); break;
+        case kQ5_K: dots_chunk<kQ5_K>(wb + mis, pk, sb0, n, out); break;
+        case kQ6_K: dots_chunk<kQ6_K>(wb + mis, pk, sb0, n, out); break;
+        case kIQ4_XS: dots_chunk<kIQ4_XS>(wb + mis, pk, sb0, n, out); break;
+        default: dots_chunk<kQ8_0>(wb + mis, pk, sb0, n, out); break;
+        }
+    }
+}
+
+cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8, int TB,
+                             int t, int32_t * wd) {
+    unit_dots_kernel<<<(unsigned)n_rows, 128, 0, s>>>(w, type, K, x8, TB, t, wd);
+    return cudaGetLastError();
 }
 
 } // namespace b200q

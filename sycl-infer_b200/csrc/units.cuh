@@ -1,0 +1,396 @@
+// Lean per-type decode for the streaming kernel.
+//
+// Work unit: a quarter of a 256-value superblock (64 weights); four lanes cover a
+// superblock.  Which weights unit u holds:
+//   Q4_K / Q5_K     groups 2u (low nibbles of qs[32u..32u+31]) and 2u+1 (high nibbles)
+//   Q6_K            blk2 = u>>1, hs = u&1: elements 16hs..16hs+15 of the four groups
+//                   4*blk2 + plane (plane 0..3)
+//   Q8_0 / IQ4_XS   groups 2u and 2u+1
+// The activation a unit meets is loaded separately (ActG2 / ActG6) so that it is read
+// from shared memory once and reused by every weight row a warp owns.
+//
+// Integer sums are exact; two shortcuts keep them exact while saving instructions:
+//   * a high nibble is used in place ((q & 0xF0) = 16*hi), its scale carries the 1/16;
+//     Q5_K's high group uses 8*(hi + 16*bit) <= 248 with a 1/8 in the scale.  Scaling an
+//     fp32 by a power of two is exact, so the products are the reference's, bit for bit.
+//   * Q6_K keeps the raw 0..63 codes and subtracts 32*sum(x) as an integer, the form the
+//     reference uses (src/backend/cpu/kernels/i8.cpp:150-152 of the reference).
+// fp32 composition per group follows the reference's association
+// (src/backend/cpu/kernels/i8.cpp:59): sx * ((d*sc)*wd - (dmin*m)*xsum).
+#pragma once
+#include "decode.cuh"
+
+namespace b200q {
+
+// ---- activation pack in shared memory (single-token calls) ----------------------------
+// Per 32-value group 48 bytes: int8 codes [32] | sx (f32) | xs0 (i32) | xs1 (i32) | (float)(xs0+xs1);
+// eight groups (one superblock) are followed by 16 bytes of padding so that the eight
+// lanes of a quarter-warp hit distinct banks.
+constexpr int kPackGroup = 48;
+constexpr int kPackSB = 8 * kPackGroup + 16;
+
+__device__ __forceinline__ uint32_t pack_addr(uint32_t pack, int g) {
+    return pack + (uint32_t)((g >> 3) * kPackSB + (g & 7) * kPackGroup);
+}
+
+struct GroupMeta {
+    float sx;
+    int xs0, xs1;
+    float xsf;
+};
+
+// two consecutive groups, all 32 codes each
+struct ActG2 {
+    uint32_t xa[8], xb[8];
+    GroupMeta ma, mb;
+};
+
+// four groups, 16 codes each (one half), for a Q6_K unit
+struct ActG6 {
+    uint32_t x[4][4];
+    float sx[4];
+    int xs[4];
+};
+
+__device__ __forceinline__ void meta_from(const uint4 & v, GroupMeta & m) {
+    m.sx = __uint_as_float(v.x);
+    m.xs0 = (int)v.y;
+    m.xs1 = (int)v.z;
+    m.xsf = __uint_as_float(v.w);
+}
+
+struct PackA { // staged pack, token 0
+    uint32_t pack;
+    __device__ __forceinline__ void g2(int g, int, ActG2 & a) const {
+        const uint32_t p = pack_addr(pack, g); // g even: both groups in the same superblock
+        const uint4 a0 = lds128(p), a1 = lds128(p + 16), am = lds128(p + 32);
+        const uint4 b0 = lds128(p + 48), b1 = lds128(p + 64), bm = lds128(p + 80);
+        a.xa[0] = a0.x, a.xa[1] = a0.y, a.xa[2] = a0.z, a.xa[3] = a0.w;
+        a.xa[4] = a1.x, a.xa[5] = a1.y, a.xa[6] = a1.z, a.xa[7] = a1.w;
+        a.xb[0] = b0.x, a.xb[1] = b0.y, a.xb[2] = b0.z, a.xb[3] = b0.w;
+        a.xb[4] = b1.x, a.xb[5] = b1.y, a.xb[6] = b1.z, a.xb[7] = b1.w;
+        meta_from(am, a.ma);
+        meta_from(bm, a.mb);
+    }
+    __device__ __forceinline__ void g6(int g, int hs, int, ActG6 & a) const {
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const uint32_t q = pack_addr(pack, g + p);
+            const uint4 x = lds128(q + 16 * hs), m = lds128(q + 32);
+            a.x[p][0] = x.x, a.x[p][1] = x.y, a.x[p][2] = x.z, a.x[p][3] = x.w;
+            a.sx[p] = __uint_as_float(m.x);
+            a.xs[p] = hs ? (int)m.z : (int)m.y;
+        }
+    }
+};
+
+struct GlobA { // the caller's group-major arrays, any token count, read through L1
+    const int8_t * x8;
+    const float * xmeta;
+    const int32_t * xsumq;
+    int TB;
+    __device__ __forceinline__ void meta(size_t gi, GroupMeta & m) const {
+        const float2 s = __ldg(reinterpret_cast<const float2 *>(xmeta) + gi);
+        const int2 q = __ldg(reinterpret_cast<const int2 *>(xsumq) + gi);
+        m.sx = s.x;
+        m.xs0 = q.x;
+        m.xs1 = q.y;
+        m.xsf = (float)(q.x + q.y);
+    }
+    __device__ __forceinline__ void g2(int g, int t, ActG2 & a) const {
+        const size_t ga = (size_t)g * TB + t, gb = ga + TB;
+        const uint4 * pa = reinterpret_cast<const uint4 *>(x8 + ga * 32);
+        const uint4 * pb = reinterpret_cast<const uint4 *>(x8 + gb * 32);
+        const uint4 a0 = __ldg(pa), a1 = __ldg(pa + 1), b0 = __ldg(pb), b1 = __ldg(pb + 1);
+        a.xa[0] = a0.x, a.xa[1] = a0.y, a.xa[2] = a0.z, a.xa[3] = a0.w;
+        a.xa[4] = a1.x, a.xa[5] = a1.y, a.xa[6] = a1.z, a.xa[7] = a1.w;
+        a.xb[0] = b0.x, a.xb[1] = b0.y, a.xb[2] = b0.z, a.xb[3] = b0.w;
+        a.xb[4] = b1.x, a.xb[5] = b1.y, a.xb[6] = b1.z, a.xb[7] = b1.w;
+        meta(ga, a.ma);
+        meta(gb, a.mb);
+    }
+    __device__ __forceinline__ void g6(int g, int hs, int t, ActG6 & a) const {
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const size_t gi = (size_t)(g + p) * TB + t;
+            const uint4 x = __ldg(reinterpret_cast<const uint4 *>(x8 + gi * 32 + 16 * hs));
+            a.x[p][0] = x.x, a.x[p][1] = x.y, a.x[p][2] = x.z, a.x[p][3] = x.w;
+            a.sx[p] = __ldg(xmeta + 2 * gi);
+            a.xs[p] = __ldg(xsumq + 2 * gi + hs);
+        }
+    }
+};
+
+// 16 bytes from a 2-byte-aligned shared address: five aligned words, funnel-shifted
+__device__ __forceinline__ void lds128_a2(uint32_t a, uint32_t (&o)[4]) {
+    const uint32_t sh = (a & 2u) * 8, q = a & ~3u;
+    uint32_t w0 = lds32(q), w1 = lds32(q + 4), w2 = lds32(q + 8), w3 = lds32(q + 12), w4 = lds32(q + 16);
+    o[0] = __funnelshift_r(w0, w1, sh);
+    o[1] = __funnelshift_r(w1, w2, sh);
+    o[2] = __funnelshift_r(w2, w3, sh);
+    o[3] = __funnelshift_r(w3, w4, sh);
+}
+
+template <int TYPE> struct WUnit;
+
+// ------------------------------------------------------------------------ Q4_K / Q5_K
+template <int TYPE> struct WUnitK45 {
+    using Act = ActG2;
+    static constexpr int kHiShift = TYPE == kQ4_K ? 4 : 3; // high group is scaled by 16 (Q4_K) or 8 (Q5_K)
+    uint32_t lo[8], hi[8];
+    float dscA, dscB, dmmA, dmmB;
+
+    __device__ __forceinline__ void load(uint32_t sb, int u) {
+        const uint4 hdr = lds128(sb);
+        const uint32_t qoff = TYPE == kQ4_K ? 16u : 48u;
+        const uint4 q0 = lds128(sb + qoff + 32 * u), q1 = lds128(sb + qoff + 32 * u + 16);
+        const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        if (TYPE == kQ4_K) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                lo[k] = q[k] & 0x0F0F0F0Fu;
+                hi[k] = q[k] & 0xF0F0F0F0u;
+            }
+        } else { // bit 2u / 2u+1 of qh[i] is the fifth bit of element i of the low / high group
+            const uint4 h0 = lds128(sb + 16), h1 = lds128(sb + 32);
+            const uint32_t h[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const uint32_t t = h[k] >> (2 * u);
+                lo[k] = (q[k] & 0x0F0F0F0Fu) | ((t & 0x01010101u) << 4);
+                hi[k] = ((q[k] >> 1) & 0x78787878u) | ((t & 0x02020202u) << 6);
+            }
+        }
+        // 6-bit (scale, min) of groups 2u, 2u+1 (get_scale_min_k4, src/common/quant.h:136-144
+        // of the reference), two at a time in 16-bit lanes
+        const uint32_t sh = 16 * (u & 1);
+        const uint32_t y = (hdr.y >> sh) & 0xFFFF, z = (hdr.z >> sh) & 0xFFFF, w = (hdr.w >> sh) & 0xFFFF;
+        uint32_t sc, mn;
+        if (u < 2) {
+            sc = y & 0x3F3F;
+            mn = z & 0x3F3F;
+        } else {
+            const uint32_t y0 = hdr.y >> sh, z0 = hdr.z >> sh; // groups 4..7 borrow the top bits of 0..3
+            sc = (w & 0x0F0F) | ((y0 & 0xC0C0) >> 2);
+            mn = ((w >> 4) & 0x0F0F) | ((z0 & 0xC0C0) >> 2);
+        }
+        const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
+        dscA = d * (float)(sc & 0xFF);
+        dscB = (d * (TYPE == kQ4_K ? 0.0625f : 0.125f)) * (float)(sc >> 8);
+        dmmA = dmin * (float)(mn & 0xFF);
+        dmmB = dmin * (float)(mn >> 8);
+    }
+    // exact int32 sums of the two groups (the high group's sum is returned unscaled)
+    __device__ __forceinline__ void dots(const ActG2 & a, int & wa, int & wb) const {
+        int sa = 0, sb = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            sa = dp4a_us(lo[k], a.xa[k], sa);
+            sb = dp4a_us(hi[k], a.xb[k], sb);
+        }
+        wa = sa;
+        wb = sb;
+    }
+    __device__ __forceinline__ float term(const ActG2 & a) const {
+        int wa, wb;
+        dots(a, wa, wb);
+        const float ta = dscA * (float)wa - dmmA * a.ma.xsf;
+        const float tb = dscB * (float)wb - dmmB * a.mb.xsf;
+        return a.ma.sx * ta + a.mb.sx * tb;
+    }
+    __device__ __forceinline__ void exact(const ActG2 & a, int G, int32_t * wd) const {
+        int wa, wb;
+        dots(a, wa, wb);
+        wd[G] = wa;
+        wd[G + 1] = wb >> kHiShift;
+    }
+};
+template <> struct WUnit<kQ4_K> : WUnitK45<kQ4_K> {};
+template <> struct WUnit<kQ5_K> : WUnitK45<kQ5_K> {};
+
+// ------------------------------------------------------------------------------- Q6_K
+template <> struct WUnit<kQ6_K> {
+    using Act = ActG6;
+    uint32_t v[4][4]; // raw codes 0..63, plane p, 16 elements
+    float ds[4];
+
+    __device__ __forceinline__ void load(uint32_t sb, int u) {
+        const int blk2 = u >> 1, hs = u & 1;
+        uint32_t qa[4], qb[4], qh[4];
+        lds128_a2(sb + 64 * blk2 + 16 * hs, qa);
+        lds128_a2(sb + 64 * blk2 + 32 + 16 * hs, qb);
+        lds128_a2(sb + 128 + 32 * blk2 + 16 * hs, qh);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t a = qa[k], b = qb[k], h = qh[k];
+            v[0][k] = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+            v[1][k] = (b & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+            v[2][k] = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+            v[3][k] = ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+        }
+        const float d = h2f((uint16_t)lds16(sb + 208));
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            int s8;
+            asm volatile("ld.shared.s8 %0, [%1];" : "=r"(s8) : "r"(sb + 192 + 8 * blk2 + 2 * p + hs));
+            ds[p] = d * (float)s8;
+        }
+    }
+    __device__ __forceinline__ void dots(const ActG6 & a, int (&w)[4]) const {
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            int s = 0;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                s = dp4a_us(v[p][k], a.x[p][k], s);
+            }
+            w[p] = s;
+        }
+    }
+    // raw-code sums per 16-value scale group: index 2*group + half
+    __device__ __forceinline__ void exact(const ActG6 & a, int G, int hs, int32_t * wd) const {
+        int w[4];
+        dots(a, w);
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            wd[2 * (G + p) + hs] = w[p];
+        }
+    }
+    __device__ __forceinline__ float term(const ActG6 & a) const {
+        int w[4];
+        dots(a, w);
+        float r = 0.f;
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            r += (a.sx[p] * ds[p]) * (float)(w[p] - 32 * a.xs[p]);
+        }
+        return r;
+    }
+};
+
+// ----------------------------------------------------------------------------- IQ4_XS
+// Codebook kvalues_iq4nl (src/common/quant.h:417 of the reference) as four little-endian words.
+// A 32-bit word of eight 4-bit indices n0..n7 is looked up with byte permutes whose
+// selectors are the indices themselves: result word 0 holds kv[n0],kv[n1],kv[n2],kv[n3].
+// Since n0,n2 are low nibbles (elements i, i+1) and n1,n3 high nibbles (elements 16+i, 17+i),
+// the activation bytes are interleaved the same way before the dp4a.
+__device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t & r0, uint32_t & r1) {
+    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;
+    const uint32_t s = q & 0x77777777u;
+    const uint32_t l0 = __byte_perm(T0, T1, s), l1 = __byte_perm(T0, T1, s >> 16);
+    const uint32_t h0 = __byte_perm(T2, T3, s), h1 = __byte_perm(T2, T3, s >> 16);
+    // byte masks from bit 3 of every nibble: sign-replicating permutes of q (odd nibbles)
+    // and q << 4 (even nibbles), interleaved in nibble order
+    const uint32_t e = q << 4;
+    const uint32_t m0 = __byte_perm(e, q, 0xD9C8), m1 = __byte_perm(e, q, 0xFBEA);
+    r0 = (l0 & ~m0) | (h0 & m0);
+    r1 = (l1 & ~m1) | (h1 & m1);
+}
+
+template <> struct WUnit<kIQ4_XS> {
+    using Act = ActG2;
+    uint32_t v[16]; // codebook values; word pairs in interleaved element order
+    float dlA, dlB;
+
+    __device__ __forceinline__ void load(uint32_t sb, int u) {
+        const uint2 hdr = lds64(sb); // d | scales_h << 16, scales_l[4]
+        const uint32_t sl = (hdr.y >> (8 * u)) & 0xFF, shh = (hdr.x >> (16 + 4 * u)) & 0xF;
+        const int lsA = (int)((sl & 0xF) | ((shh & 3) << 4)), lsB = (int)((sl >> 4) | ((shh >> 2) << 4));
+        const float d = h2f((uint16_t)(hdr.x & 0xFFFF));
+        dlA = d * (float)(lsA - 32);
+        dlB = d * (float)(lsB - 32);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint2 q = lds64(sb + 8 + 32 * u + 8 * k);
+            iq4_lookup8(q.x, v[4 * k], v[4 * k + 1]);
+            iq4_lookup8(q.y, v[4 * k + 2], v[4 * k + 3]);
+        }
+    }
+    // group g of the unit occupies v[8g..8g+7]; word pair (2j, 2j+1) covers index word j:
+    // elements 4j..4j+3 (low nibbles) and 16+4j..19+4j (high nibbles), interleaved
+    static __device__ __forceinline__ int group_dot(const uint32_t * vv, const uint32_t * x) {
+        int s = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t xl = x[j], xh = x[4 + j];
+            s = dp4a_ss(vv[2 * j], __byte_perm(xl, xh, 0x5140), s);
+            s = dp4a_ss(vv[2 * j + 1], __byte_perm(xl, xh, 0x7362), s);
+        }
+        return s;
+    }
+    __device__ __forceinline__ void dots(const ActG2 & a, int & wa, int & wb) const {
+        wa = group_dot(v, a.xa);
+        wb = group_dot(v + 8, a.xb);
+    }
+    __device__ __forceinline__ float term(const ActG2 & a) const {
+        int wa, wb;
+        dots(a, wa, wb);
+        return (a.ma.sx * dlA) * (float)wa + (a.mb.sx * dlB) * (float)wb;
+    }
+    __device__ __forceinline__ void exact(const ActG2 & a, int G, int32_t * wd) const {
+        dots(a, wd[G], wd[G + 1]);
+    }
+};
+
+// ------------------------------------------------------------------------------- Q8_0
+template <> struct WUnit<kQ8_0> {
+    using Act = ActG2;
+    uint32_t va[8], vb[8];
+    float dA, dB;
+
+    __device__ __forceinline__ void load(uint32_t sb, int u) {
+        const uint32_t ba = sb + 68 * u, bb = ba + 34;
+        dA = h2f((uint16_t)lds16(ba));
+        dB = h2f((uint16_t)lds16(bb));
+        uint32_t t[4];
+        lds128_a2(ba + 2, t);
+        va[0] = t[0], va[1] = t[1], va[2] = t[2], va[3] = t[3];
+        lds128_a2(ba + 18, t);
+        va[4] = t[0], va[5] = t[1], va[6] = t[2], va[7] = t[3];
+        lds128_a2(bb + 2, t);
+        vb[0] = t[0], vb[1] = t[1], vb[2] = t[2], vb[3] = t[3];
+        lds128_a2(bb + 18, t);
+        vb[4] = t[0], vb[5] = t[1], vb[6] = t[2], vb[7] = t[3];
+    }
+    __device__ __forceinline__ void dots(const ActG2 & a, int & wa, int & wb) const {
+        int sa = 0, sb = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            sa = dp4a_ss(va[k], a.xa[k], sa);
+            sb = dp4a_ss(vb[k], a.xb[k], sb);
+        }
+        wa = sa;
+        wb = sb;
+    }
+    __device__ __forceinline__ float term(const ActG2 & a) const {
+        int wa, wb;
+        dots(a, wa, wb);
+        return (a.ma.sx * dA) * (float)wa + (a.mb.sx * dB) * (float)wb;
+    }
+    __device__ __forceinline__ void exact(const ActG2 & a, int G, int32_t * wd) const {
+        dots(a, wd[G], wd[G + 1]);
+    }
+};
+
+// load the activation of unit u of superblock `sbi` (token t) for any weight type
+template <int TYPE, class AS>
+__device__ __forceinline__ void load_act(const AS & as, int sbi, int u, int t, typename WUnit<TYPE>::Act & a) {
+    if constexpr (TYPE == kQ6_K) {
+        as.g6(8 * sbi + 4 * (u >> 1), u & 1, t, a);
+    } else {
+        as.g2(8 * sbi + 2 * u, t, a);
+    }
+}
+
+// exact int32 sums of unit u of superblock sbi into the row's dot array
+template <int TYPE>
+__device__ __forceinline__ void unit_exact(const WUnit<TYPE> & w, const typename WUnit<TYPE>::Act & a, int sbi, int u,
+                                           int32_t * wd) {
+    if constexpr (TYPE == kQ6_K) {
+        w.exact(a, 8 * sbi + 4 * (u >> 1), u & 1, wd);
+    } else {
+        w.exact(a, 8 * sbi + 2 * u, wd);
+    }
+}
+
+} // namespace b200q
