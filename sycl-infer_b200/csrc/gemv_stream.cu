@@ -41,6 +41,9 @@ struct StreamArgs {
     int32_t kb_max;     // superblocks per tile along K
     int32_t slot_bytes; // shared bytes reserved per row of a tile
     int32_t stages;
+    int32_t contig;     // tiles hold whole rows: one bulk copy per tile, rows packed back to back
+    int32_t tile_bytes; // shared bytes reserved per tile
+    int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
 
 // ---- mbarrier / bulk-copy primitives (PTX) --------------------------------------------
@@ -54,8 +57,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    const long long t0 = clock64();
-    for (;;) {
+    long long t0 = 0;
+    for (uint32_t n = 0;; n++) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                      "selp.u32 %0, 1, 0, p;\n\t}"
@@ -65,7 +68,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (ok) {
             return true;
         }
-        if (clock64() - t0 > kSpinCycles) {
+        if (n == 64) {
+            t0 = clock64();
+        } else if (n > 64 && clock64() - t0 > kSpinCycles) {
             break;
         }
     }
@@ -135,12 +140,16 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     constexpr int kRows = kConsumerWarps * RW; // rows per tile
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t bar_full = base, bar_empty = base + 64, tiles = base + 128;
-    const uint32_t pack = tiles + (uint32_t)(a.stages * kRows * a.slot_bytes);
+    const uint32_t pack = tiles + (uint32_t)(a.stages * a.tile_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = a.c.K >> 8;
     const int n_chunks = (nb + a.kb_max - 1) / a.kb_max;
     const int S = a.stages;
 
+    // Let the next kernel in the stream be scheduled as soon as this grid is resident: its
+    // CTAs start on SMs this grid's tail frees, and prefetch weights while it still waits
+    // (griddepcontrol.wait) for this grid to complete.
+    asm volatile("griddepcontrol.launch_dependents;");
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(bar_full + 8 * s, 1);
@@ -171,7 +180,14 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                 const int kb = min(a.kb_max, nb - sb0);
                 uint32_t len = 0;
                 const uint8_t * src = nullptr;
-                if (lane < rows) {
+                if (a.contig) {
+                    if (lane == 0) { // the tile's rows are one contiguous byte range
+                        const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
+                        const uintptr_t A0 = A & ~uintptr_t(15);
+                        len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
+                        src = reinterpret_cast<const uint8_t *>(A0);
+                    }
+                } else if (lane < rows) {
                     const uint8_t * p = sg.w + (size_t)(row0 + lane) * row_bytes + (size_t)sb0 * sbb;
                     const uintptr_t A = reinterpret_cast<uintptr_t>(p);
                     const uintptr_t A0 = A & ~uintptr_t(15);
@@ -192,8 +208,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                     mbar_expect_tx(bar_full + 8 * stage, total);
                 }
                 __syncwarp();
-                if (lane < rows) {
-                    bulk_g2s(tiles + (uint32_t)((stage * kRows + lane) * a.slot_bytes), src, len,
+                if (len) {
+                    bulk_g2s(tiles + (uint32_t)(stage * a.tile_bytes + (a.contig ? 0 : lane * a.slot_bytes)), src, len,
                              bar_full + 8 * stage);
                 }
             }
@@ -228,10 +244,14 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
         const SegDev & sg = a.c.seg[si];
         const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRows + warp * RW;
         const int sbb = sb_bytes(sg.type);
+        // where a row's bytes start inside its slot: its own misalignment, or in contiguous
+        // mode the misalignment of the tile's first row
+        const int tile_row0 = row0 - warp * RW;
         uint32_t mis0[RW];
 #pragma unroll
         for (int r = 0; r < RW; r++) {
-            mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)(row0 + r) * nb * sbb) & 15);
+            const int rr = a.contig ? tile_row0 : row0 + r;
+            mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)rr * nb * sbb) & 15);
         }
         float acc[RW][TT];
 #pragma unroll
@@ -248,8 +268,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
             }
             const int sb0 = ch * a.kb_max;
             const int kb = min(a.kb_max, nb - sb0);
-            if (row0 < sg.n_rows) { // rows past the end of the segment hold stale bytes: results are dropped
-                const uint32_t slot0 = tiles + (uint32_t)((stage * kRows + warp * RW) * a.slot_bytes);
+            if (row0 < sg.n_rows && !a.dry) { // rows past the end of the segment hold stale bytes: results are dropped
+                const uint32_t slot0 = tiles + (uint32_t)(stage * a.tile_bytes + warp * RW * a.slot_bytes);
                 uint32_t mis[RW];
 #pragma unroll
                 for (int r = 0; r < RW; r++) {
@@ -325,27 +345,51 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
         max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
     }
     a.n_groups = groups;
-    // superblocks per tile: a multiple of 8 (all 32 lanes busy) keeping a tile near 20-28 KB
-    int kb = kb_env > 0 ? kb_env : (28 * 1024 / (kRows * max_sbb)) / 8 * 8;
-    kb = kb < 8 ? 8 : kb;
-    if (kb < nb) { // equal chunks, rounded up to a multiple of 8
-        const int n_chunks = (nb + kb - 1) / kb;
+    // Superblocks per tile along K.  Copies are efficient when large (the copy engine spends
+    // about as long on a copy's fixed cost as on 750 bytes), so take whole rows when two
+    // tiles of whole rows fit, else the largest multiple of 8 superblocks (all 32 lanes
+    // busy) that leaves room for two tiles.
+    const size_t pack_probe = TT == 1 ? (size_t)nb * kPackSB : 0;
+    const size_t room = (kSmemBudget - 128 - pack_probe) / 2; // bytes per tile with two stages
+    int kb;
+    if (kb_env > 0) {
+        kb = kb_env;
+    } else if ((size_t)kRows * nb * max_sbb + 48 <= room) {
+        kb = nb;
+    } else {
+        kb = (int)((room / kRows - 48) / max_sbb) / 8 * 8;
+        kb = kb < 8 ? 8 : kb;
+        const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of 8
         kb = (((nb + n_chunks - 1) / n_chunks + 7) / 8) * 8;
     }
     a.kb_max = kb < nb ? kb : nb;
-    a.slot_bytes = ((a.kb_max * max_sbb + 32 + 15) / 16) * 16;
+    static const int contig_env = env_int("B200Q_CONTIG", 1);
+    bool same_type = true;
+    for (int i = 1; i < c.n_segs; i++) {
+        same_type = same_type && c.seg[i].type == c.seg[0].type;
+    }
+    a.contig = (contig_env && a.kb_max == nb && same_type) ? 1 : 0;
+    if (a.contig) {
+        a.slot_bytes = nb * max_sbb;
+        a.tile_bytes = ((kRows * a.slot_bytes + 32 + 15) / 16) * 16;
+    } else {
+        a.slot_bytes = ((a.kb_max * max_sbb + 32 + 15) / 16) * 16;
+        a.tile_bytes = kRows * a.slot_bytes;
+    }
     const size_t pack_bytes = TT == 1 ? (size_t)nb * kPackSB : 0;
     const size_t fixed = 128 + pack_bytes;
-    if (fixed + 2 * (size_t)kRows * a.slot_bytes > (size_t)kSmemBudget) {
+    if (fixed + 2 * (size_t)a.tile_bytes > (size_t)kSmemBudget) {
         return cudaErrorInvalidConfiguration;
     }
-    int stages = (int)((kSmemBudget - fixed) / ((size_t)kRows * a.slot_bytes));
+    int stages = (int)((kSmemBudget - fixed) / (size_t)a.tile_bytes);
     stages = stages > 8 ? 8 : stages;
     if (st_env > 0 && st_env < stages) {
         stages = st_env;
     }
     a.stages = stages;
-    const size_t smem = 128 + (size_t)stages * kRows * a.slot_bytes + pack_bytes;
+    static const int dry_env = env_int("B200Q_DRY", 0);
+    a.dry = dry_env;
+    const size_t smem = 128 + (size_t)stages * a.tile_bytes + pack_bytes;
     int grid = grid_env > 0 ? grid_env : 2 * kSMs;
     grid = groups < grid ? groups : grid;
     cudaLaunchConfig_t cfg = {};
@@ -357,7 +401,8 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_secondary ? 1 : 0;
+    static const int pdl_env = env_int("B200Q_PDL", 1);
+    cfg.numAttrs = (pdl_secondary || pdl_env) && pdl_env >= 0 ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<TT, RW>, a);
 }
 
@@ -369,8 +414,9 @@ bool stream_supported(const CallDev & c) {
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     StreamArgs a;
     a.c = c;
+    static const int rw_env = env_int("B200Q_RW", 2);
     if (c.TB == 1) {
-        return launch_stream_tt<1, 2>(s, a, pdl_secondary);
+        return rw_env == 1 ? launch_stream_tt<1, 1>(s, a, pdl_secondary) : launch_stream_tt<1, 2>(s, a, pdl_secondary);
     }
     if (c.TB == 2) {
         return launch_stream_tt<2, 2>(s, a, pdl_secondary);

@@ -274,15 +274,23 @@ template <> struct WUnit<kQ6_K> {
 // selectors are the indices themselves: result word 0 holds kv[n0],kv[n1],kv[n2],kv[n3].
 // Since n0,n2 are low nibbles (elements i, i+1) and n1,n3 high nibbles (elements 16+i, 17+i),
 // the activation bytes are interleaved the same way before the dp4a.
+// prmt.b32 in its default mode: a selector nibble with bit 3 set replicates the sign bit of
+// the selected byte (the __byte_perm intrinsic only defines the low three bits)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
 __device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t & r0, uint32_t & r1) {
     constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;
     const uint32_t s = q & 0x77777777u;
-    const uint32_t l0 = __byte_perm(T0, T1, s), l1 = __byte_perm(T0, T1, s >> 16);
-    const uint32_t h0 = __byte_perm(T2, T3, s), h1 = __byte_perm(T2, T3, s >> 16);
+    const uint32_t l0 = prmt(T0, T1, s), l1 = prmt(T0, T1, s >> 16);
+    const uint32_t h0 = prmt(T2, T3, s), h1 = prmt(T2, T3, s >> 16);
     // byte masks from bit 3 of every nibble: sign-replicating permutes of q (odd nibbles)
     // and q << 4 (even nibbles), interleaved in nibble order
     const uint32_t e = q << 4;
-    const uint32_t m0 = __byte_perm(e, q, 0xD9C8), m1 = __byte_perm(e, q, 0xFBEA);
+    const uint32_t m0 = prmt(e, q, 0xD9C8), m1 = prmt(e, q, 0xFBEA);
     r0 = (l0 & ~m0) | (h0 & m0);
     r1 = (l1 & ~m1) | (h1 & m1);
 }

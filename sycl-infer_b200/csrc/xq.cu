@@ -9,6 +9,8 @@
 // (no contraction, no approximate division).  With `up` the value is silu(x)*up with
 // silu(x) = x / (1 + exp(-x)); exp is evaluated in double and rounded once, which equals
 // a correctly rounded expf.
+#include <cstdlib>
+
 #include "launch.h"
 
 namespace b200q {
@@ -26,6 +28,8 @@ __global__ void __launch_bounds__(256) xq_kernel(const float * __restrict__ x, c
     // Let a dependent GEMV launch start its prologue; it still waits for this grid to
     // finish (griddepcontrol.wait) before it reads what is written here.
     asm volatile("griddepcontrol.launch_dependents;");
+    // ... and wait for the producer of x when this launch was itself chained programmatically
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (w >= (long long)TB * G) {
@@ -57,9 +61,20 @@ cudaError_t launch_xq(cudaStream_t s, const float * x, const float * up, int x_s
     (void)pdl_primary;
     const int G = K / 32;
     const long long warps = (long long)TB * G;
-    const unsigned blocks = (unsigned)((warps + 7) / 8);
-    xq_kernel<<<blocks, 256, 0, s>>>(x, up, x_stride, up_stride, x8, xmeta, xsumq, TB, G);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((warps + 7) / 8));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool pdl = [] {
+        const char * e = getenv("B200Q_PDL");
+        return !(e && atoi(e) < 0);
+    }();
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, xq_kernel, x, up, x_stride, up_stride, x8, xmeta, xsumq, TB, G);
 }
 
 } // namespace b200q
