@@ -36,8 +36,6 @@ __device__ int g_device_status = 0;
 
 struct StreamArgs {
     CallDev c;
-    int32_t grp_end[B200Q_MAX_SEGS]; // exclusive prefix of row groups (tiles along rows) per segment
-    int32_t n_groups;
     int32_t kb_max;     // superblocks per tile along K
     int32_t slot_bytes; // shared bytes reserved per row of a tile
     int32_t stages;
@@ -98,40 +96,113 @@ __device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int
         const uint32_t p = pack_addr(pack, i);
         sts128(p, x0.x, x0.y, x0.z, x0.w);
         sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
-        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint((float)(xs.x + xs.y)));
+        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
     }
 }
 
-// One warp, RW rows, one tile.  Lane l owns unit (l & 3) of superblocks (l >> 2), +8, ...
-template <int TYPE, int RW, int TT, class AS>
+// One warp, RW rows, one tile, one token.  A superblock is H units (Unit1<TYPE>::H); lane l
+// owns unit l % H of superblocks l / H, + 32/H, ...  The superblocks left over after the
+// full passes are handled with the lanes split between the rows when that fills more lanes.
+template <int TYPE, int RW>
+__device__ __forceinline__ void consume_tile1(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
+                                              int sb0, const PackA & as, float (&acc)[RW][1]) {
+    using U = Unit1<TYPE>;
+    constexpr int H = U::H, SPI = 32 / H, SB = Fmt<TYPE>::SB;
+    const int lane = threadIdx.x & 31;
+    const int bl = lane / H, u = lane % H;
+    const int full = kb / SPI, rem = kb - full * SPI;
+    for (int it = 0; it < full; it++) {
+        const int b = it * SPI + bl;
+        typename U::Act a;
+        U::load_act(as, sb0 + b, u, a);
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+            acc[r][0] += U::term(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * SB), u, a);
+        }
+    }
+    if (rem == 0) {
+        return;
+    }
+    const int m = rem * H; // units per row in the tail, < 32
+    if (RW > 1 && 2 * m <= 32) {
+        const int rpp = min(RW, 32 / m); // rows per pass
+        for (int r0 = 0; r0 < RW; r0 += rpp) {
+            const int rr = lane / m, item = lane - rr * m, row = r0 + rr;
+            const bool valid = rr < rpp && row < RW;
+            float t = 0.f;
+            if (valid) {
+                const int b = full * SPI + item / H, uu = item % H;
+                uint32_t mr = mis[0];
+#pragma unroll
+                for (int r = 1; r < RW; r++) {
+                    mr = row == r ? mis[r] : mr;
+                }
+                typename U::Act a;
+                U::load_act(as, sb0 + b, uu, a);
+                t = U::term(slot0 + row * slot_stride + mr + (uint32_t)(b * SB), uu, a);
+            }
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+                acc[r][0] += row == r ? t : 0.f;
+            }
+        }
+    } else if (bl < rem) {
+        const int b = full * SPI + bl;
+        typename U::Act a;
+        U::load_act(as, sb0 + b, u, a);
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+            acc[r][0] += U::term(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * SB), u, a);
+        }
+    }
+}
+
+// 2..8 tokens: quarter-superblock units whose unpacked weights stay in registers for all tokens
+template <int TYPE, int RW, int TT>
 __device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                             int sb0, const AS & as, float (&acc)[RW][TT]) {
+                                             int sb0, const GlobA & as, float (&acc)[RW][TT]) {
     const int lane = threadIdx.x & 31;
     const int u = lane & 3;
     for (int b = lane >> 2; b < kb; b += 8) {
-        if constexpr (TT == 1) {
-            typename WUnit<TYPE>::Act a;
-            load_act<TYPE>(as, sb0 + b, u, 0, a);
 #pragma unroll
-            for (int r = 0; r < RW; r++) {
-                WUnit<TYPE> w;
-                w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
-                acc[r][0] += w.term(a);
-            }
-        } else {
+        for (int r = 0; r < RW; r++) {
+            WUnit<TYPE> w;
+            w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
 #pragma unroll
-            for (int r = 0; r < RW; r++) {
-                WUnit<TYPE> w;
-                w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
-#pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    typename WUnit<TYPE>::Act a;
-                    load_act<TYPE>(as, sb0 + b, u, min(t, as.TB - 1), a);
-                    acc[r][t] += w.term(a);
-                }
+            for (int t = 0; t < TT; t++) {
+                typename WUnit<TYPE>::Act a;
+                load_act<TYPE>(as, sb0 + b, u, min(t, as.TB - 1), a);
+                acc[r][t] += w.term(a);
             }
         }
     }
+}
+template <int TYPE, int RW, int TT>
+__device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
+                                             int sb0, const PackA & as, float (&acc)[RW][TT]) {
+    static_assert(TT == 1, "the activation pack holds one token");
+    consume_tile1<TYPE, RW>(slot0, slot_stride, mis, kb, sb0, as, acc);
+}
+
+// The rows of a call are split among the CTAs in proportion to their bytes: CTA c owns the
+// flattened cost range [total*c/G, total*(c+1)/G), cost = rows x bytes per superblock.
+struct RowRange {
+    int lo, hi;
+};
+__device__ __forceinline__ RowRange cta_rows(const CallDev & c, int si, unsigned long long lo, unsigned long long hi) {
+    unsigned long long c0 = 0;
+    for (int i = 0; i < si; i++) {
+        c0 += (unsigned long long)c.seg[i].n_rows * sb_bytes(c.seg[i].type);
+    }
+    const unsigned long long w = sb_bytes(c.seg[si].type);
+    const unsigned long long c1 = c0 + (unsigned long long)c.seg[si].n_rows * w;
+    const unsigned long long a = lo > c0 ? lo : c0, b = hi < c1 ? hi : c1;
+    RowRange r{0, 0};
+    if (a < b) {
+        r.lo = (int)((a - c0 + w - 1) / w);
+        r.hi = (int)((b - c0 + w - 1) / w);
+    }
+    return r;
 }
 
 template <int TT, int RW>
@@ -145,6 +216,12 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     const int nb = a.c.K >> 8;
     const int n_chunks = (nb + a.kb_max - 1) / a.kb_max;
     const int S = a.stages;
+    unsigned long long cost_total = 0;
+    for (int i = 0; i < a.c.n_segs; i++) {
+        cost_total += (unsigned long long)a.c.seg[i].n_rows * sb_bytes(a.c.seg[i].type);
+    }
+    const unsigned long long cost_lo = cost_total * blockIdx.x / gridDim.x;
+    const unsigned long long cost_hi = cost_total * (blockIdx.x + 1) / gridDim.x;
 
     // Let the next kernel in the stream be scheduled as soon as this grid is resident: its
     // CTAs start on SMs this grid's tail frees, and prefetch weights while it still waits
@@ -163,54 +240,52 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
         // ------------------------------------------------------------------ producer
         uint32_t it = 0;
         bool alive = true;
-        for (int g = blockIdx.x; g < a.n_groups && alive; g += gridDim.x) {
-            int si = 0;
-            while (si + 1 < a.c.n_segs && g >= a.grp_end[si]) {
-                si++;
-            }
+        for (int si = 0; si < a.c.n_segs && alive; si++) {
             const SegDev & sg = a.c.seg[si];
-            const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRows;
-            const int rows = min(kRows, sg.n_rows - row0);
+            const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
             const int sbb = sb_bytes(sg.type);
             const size_t row_bytes = (size_t)nb * sbb;
-            for (int ch = 0; ch < n_chunks && alive; ch++, it++) {
-                const int stage = it % S;
-                const uint32_t par = ((it / S) & 1) ^ 1;
-                const int sb0 = ch * a.kb_max;
-                const int kb = min(a.kb_max, nb - sb0);
-                uint32_t len = 0;
-                const uint8_t * src = nullptr;
-                if (a.contig) {
-                    if (lane == 0) { // the tile's rows are one contiguous byte range
-                        const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
+            for (int row0 = rr.lo; row0 < rr.hi && alive; row0 += kRows) {
+                const int rows = min(kRows, rr.hi - row0);
+                for (int ch = 0; ch < n_chunks && alive; ch++, it++) {
+                    const int stage = it % S;
+                    const uint32_t par = ((it / S) & 1) ^ 1;
+                    const int sb0 = ch * a.kb_max;
+                    const int kb = min(a.kb_max, nb - sb0);
+                    uint32_t len = 0;
+                    const uint8_t * src = nullptr;
+                    if (a.contig) {
+                        if (lane == 0) { // the tile's rows are one contiguous byte range
+                            const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
+                            const uintptr_t A0 = A & ~uintptr_t(15);
+                            len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
+                            src = reinterpret_cast<const uint8_t *>(A0);
+                        }
+                    } else if (lane < rows) {
+                        const uint8_t * p = sg.w + (size_t)(row0 + lane) * row_bytes + (size_t)sb0 * sbb;
+                        const uintptr_t A = reinterpret_cast<uintptr_t>(p);
                         const uintptr_t A0 = A & ~uintptr_t(15);
-                        len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
+                        len = (uint32_t)(((A + (size_t)kb * sbb + 15) & ~uintptr_t(15)) - A0);
                         src = reinterpret_cast<const uint8_t *>(A0);
                     }
-                } else if (lane < rows) {
-                    const uint8_t * p = sg.w + (size_t)(row0 + lane) * row_bytes + (size_t)sb0 * sbb;
-                    const uintptr_t A = reinterpret_cast<uintptr_t>(p);
-                    const uintptr_t A0 = A & ~uintptr_t(15);
-                    len = (uint32_t)(((A + (size_t)kb * sbb + 15) & ~uintptr_t(15)) - A0);
-                    src = reinterpret_cast<const uint8_t *>(A0);
-                }
-                uint32_t total = len;
+                    uint32_t total = len;
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
-                }
-                alive = mbar_wait(bar_empty + 8 * stage, par);
-                alive = __all_sync(0xFFFFFFFFu, alive);
-                if (!alive) {
-                    break;
-                }
-                if (lane == 0) {
-                    mbar_expect_tx(bar_full + 8 * stage, total);
-                }
-                __syncwarp();
-                if (len) {
-                    bulk_g2s(tiles + (uint32_t)(stage * a.tile_bytes + (a.contig ? 0 : lane * a.slot_bytes)), src, len,
-                             bar_full + 8 * stage);
+                    for (int o = 16; o > 0; o >>= 1) {
+                        total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
+                    }
+                    alive = mbar_wait(bar_empty + 8 * stage, par);
+                    alive = __all_sync(0xFFFFFFFFu, alive);
+                    if (!alive) {
+                        break;
+                    }
+                    if (lane == 0) {
+                        mbar_expect_tx(bar_full + 8 * stage, total);
+                    }
+                    __syncwarp();
+                    if (len) {
+                        bulk_g2s(tiles + (uint32_t)(stage * a.tile_bytes + (a.contig ? 0 : lane * a.slot_bytes)), src,
+                                 len, bar_full + 8 * stage);
+                    }
                 }
             }
         }
@@ -236,82 +311,80 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     }
 
     uint32_t it = 0;
-    for (int g = blockIdx.x; g < a.n_groups; g += gridDim.x) {
-        int si = 0;
-        while (si + 1 < a.c.n_segs && g >= a.grp_end[si]) {
-            si++;
-        }
+    for (int si = 0; si < a.c.n_segs; si++) {
         const SegDev & sg = a.c.seg[si];
-        const int row0 = (g - (si ? a.grp_end[si - 1] : 0)) * kRows + warp * RW;
+        const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
         const int sbb = sb_bytes(sg.type);
-        // where a row's bytes start inside its slot: its own misalignment, or in contiguous
-        // mode the misalignment of the tile's first row
-        const int tile_row0 = row0 - warp * RW;
-        uint32_t mis0[RW];
+        for (int tile_row0 = rr.lo; tile_row0 < rr.hi; tile_row0 += kRows) {
+            const int row0 = tile_row0 + warp * RW;
+            // where a row's bytes start inside its slot: its own misalignment, or in contiguous
+            // mode the misalignment of the tile's first row
+            uint32_t mis0[RW];
 #pragma unroll
-        for (int r = 0; r < RW; r++) {
-            const int rr = a.contig ? tile_row0 : row0 + r;
-            mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)rr * nb * sbb) & 15);
-        }
-        float acc[RW][TT];
-#pragma unroll
-        for (int r = 0; r < RW; r++) {
-#pragma unroll
-            for (int t = 0; t < TT; t++) {
-                acc[r][t] = 0.f;
+            for (int r = 0; r < RW; r++) {
+                const int rx = a.contig ? tile_row0 : row0 + r;
+                mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)rx * nb * sbb) & 15);
             }
-        }
-        for (int ch = 0; ch < n_chunks; ch++, it++) {
-            const int stage = it % S;
-            if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1)) {
-                return;
-            }
-            const int sb0 = ch * a.kb_max;
-            const int kb = min(a.kb_max, nb - sb0);
-            if (row0 < sg.n_rows && !a.dry) { // rows past the end of the segment hold stale bytes: results are dropped
-                const uint32_t slot0 = tiles + (uint32_t)(stage * a.tile_bytes + warp * RW * a.slot_bytes);
-                uint32_t mis[RW];
+            float acc[RW][TT];
 #pragma unroll
-                for (int r = 0; r < RW; r++) {
-                    mis[r] = (mis0[r] + (uint32_t)sb0 * sbb) & 15;
-                }
-                switch (sg.type) {
-                case kQ4_K: consume_tile<kQ4_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                case kQ5_K: consume_tile<kQ5_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                case kQ6_K: consume_tile<kQ6_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                case kIQ4_XS: consume_tile<kIQ4_XS, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                default: consume_tile<kQ8_0, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+            for (int r = 0; r < RW; r++) {
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    acc[r][t] = 0.f;
                 }
             }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_empty + 8 * stage);
-            }
-        }
+            for (int ch = 0; ch < n_chunks; ch++, it++) {
+                const int stage = it % S;
+                if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1)) {
+                    return;
+                }
+                const int sb0 = ch * a.kb_max;
+                const int kb = min(a.kb_max, nb - sb0);
+                if (row0 < rr.hi && !a.dry) { // rows past the range hold stale bytes: their results are dropped
+                    const uint32_t slot0 = tiles + (uint32_t)(stage * a.tile_bytes + warp * RW * a.slot_bytes);
+                    uint32_t mis[RW];
 #pragma unroll
-        for (int r = 0; r < RW; r++) {
-#pragma unroll
-            for (int t = 0; t < TT; t++) {
-                acc[r][t] = warp_sum(acc[r][t]);
+                    for (int r = 0; r < RW; r++) {
+                        mis[r] = (mis0[r] + (uint32_t)sb0 * sbb) & 15;
+                    }
+                    switch (sg.type) {
+                    case kQ4_K: consume_tile<kQ4_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                    case kQ5_K: consume_tile<kQ5_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                    case kQ6_K: consume_tile<kQ6_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                    case kIQ4_XS: consume_tile<kIQ4_XS, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                    default: consume_tile<kQ8_0, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_empty + 8 * stage);
+                }
             }
-        }
-        // lane (r*TT + t) stores row r, token t
-        float mine = 0.f;
 #pragma unroll
-        for (int r = 0; r < RW; r++) {
+            for (int r = 0; r < RW; r++) {
 #pragma unroll
-            for (int t = 0; t < TT; t++) {
-                mine = lane == r * TT + t ? acc[r][t] : mine;
+                for (int t = 0; t < TT; t++) {
+                    acc[r][t] = warp_sum(acc[r][t]);
+                }
             }
-        }
-        const int r = lane / TT, t = lane % TT;
-        if (lane < RW * TT && row0 + r < sg.n_rows && t < a.c.TB) {
-            const size_t o = (size_t)t * sg.out_stride + row0 + r;
-            float v = sg.alpha * mine;
-            if (sg.residual) {
-                v += sg.residual[o];
+            // lane (r*TT + t) stores row r, token t
+            float mine = 0.f;
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    mine = lane == r * TT + t ? acc[r][t] : mine;
+                }
             }
-            sg.out[o] = v;
+            const int r = lane / TT, t = lane % TT;
+            if (lane < RW * TT && row0 + r < rr.hi && t < a.c.TB) {
+                const size_t o = (size_t)t * sg.out_stride + row0 + r;
+                float v = sg.alpha * mine;
+                if (sg.residual) {
+                    v += sg.residual[o];
+                }
+                sg.out[o] = v;
+            }
         }
     }
 }
@@ -341,10 +414,8 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     int groups = 0, max_sbb = 0;
     for (int i = 0; i < c.n_segs; i++) {
         groups += (c.seg[i].n_rows + kRows - 1) / kRows;
-        a.grp_end[i] = groups;
         max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
     }
-    a.n_groups = groups;
     // Superblocks per tile along K.  Copies are efficient when large (the copy engine spends
     // about as long on a copy's fixed cost as on 750 bytes), so take whole rows when two
     // tiles of whole rows fit, else the largest multiple of 8 superblocks (all 32 lanes
@@ -414,9 +485,12 @@ bool stream_supported(const CallDev & c) {
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     StreamArgs a;
     a.c = c;
-    static const int rw_env = env_int("B200Q_RW", 2);
+    static const int rw_env = env_int("B200Q_RW", 0);
     if (c.TB == 1) {
-        return rw_env == 1 ? launch_stream_tt<1, 1>(s, a, pdl_secondary) : launch_stream_tt<1, 2>(s, a, pdl_secondary);
+        // two rows per warp share every activation load; one row per warp gives twice the
+        // tiles, which matters when a call is too small to give every CTA a 16-row tile
+        const bool rw2 = rw_env ? rw_env == 2 : c.total_rows >= 16 * 2 * kSMs;
+        return rw2 ? launch_stream_tt<1, 2>(s, a, pdl_secondary) : launch_stream_tt<1, 1>(s, a, pdl_secondary);
     }
     if (c.TB == 2) {
         return launch_stream_tt<2, 2>(s, a, pdl_secondary);
@@ -441,17 +515,31 @@ cudaError_t read_device_status(int * status, bool clear) {
 // it has in global memory, the activation pack of token t is built, and every (superblock,
 // unit) is decoded and dotted by exactly the WUnit code the streaming kernel runs.
 constexpr int kDotsChunk = 16; // superblocks staged at a time
+template <int TYPE> __device__ constexpr int dots_per_sb() {
+    return TYPE == kQ6_K ? 16 : 8;
+}
 
 template <int TYPE>
-__device__ __forceinline__ void dots_chunk(uint32_t wbase, uint32_t pack, int sb0, int n, int32_t * wd) {
-    for (int i = threadIdx.x; i < 4 * n; i += blockDim.x) {
-        const int b = i >> 2, u = i & 3;
-        PackA as{pack};
-        typename WUnit<TYPE>::Act act;
-        load_act<TYPE>(as, b, u, 0, act);
-        WUnit<TYPE> w;
-        w.load(wbase + (uint32_t)(b * Fmt<TYPE>::SB), u);
-        unit_exact<TYPE>(w, act, sb0 + b, u, wd);
+__device__ __forceinline__ void dots_chunk(uint32_t wbase, uint32_t pack, int sb0, int n, bool single, int32_t * wd) {
+    PackA as{pack};
+    if (single) { // the units a single-token call runs
+        using U = Unit1<TYPE>;
+        for (int i = threadIdx.x; i < U::H * n; i += blockDim.x) {
+            const int b = i / U::H, u = i % U::H;
+            typename U::Act act;
+            U::load_act(as, b, u, act);
+            // the unit writes at superblock index sb0 + b of the row's array
+            U::exact(wbase + (uint32_t)(b * Fmt<TYPE>::SB), b, u, act, wd + dots_per_sb<TYPE>() * sb0);
+        }
+    } else { // the quarter units a 2..8 token call runs
+        for (int i = threadIdx.x; i < 4 * n; i += blockDim.x) {
+            const int b = i >> 2, u = i & 3;
+            typename WUnit<TYPE>::Act act;
+            load_act<TYPE>(as, b, u, 0, act);
+            WUnit<TYPE> w;
+            w.load(wbase + (uint32_t)(b * Fmt<TYPE>::SB), u);
+            unit_exact<TYPE>(w, act, b, u, wd + dots_per_sb<TYPE>() * sb0);
+        }
     }
 }
 
@@ -483,11 +571,11 @@ __global__ void __launch_bounds__(128) unit_dots_kernel(const uint8_t * w, int t
         }
         __syncthreads();
         switch (type) {
-        case kQ4_K: dots_chunk<kQ4_K>(wb + mis, pk, sb0, n, out); break;
-        case kQ5_K: dots_chunk<kQ5_K>(wb + mis, pk, sb0, n, out); break;
-        case kQ6_K: dots_chunk<kQ6_K>(wb + mis, pk, sb0, n, out); break;
-        case kIQ4_XS: dots_chunk<kIQ4_XS>(wb + mis, pk, sb0, n, out); break;
-        default: dots_chunk<kQ8_0>(wb + mis, pk, sb0, n, out); break;
+        case kQ4_K: dots_chunk<kQ4_K>(wb + mis, pk, sb0, n, TB == 1, out); break;
+        case kQ5_K: dots_chunk<kQ5_K>(wb + mis, pk, sb0, n, TB == 1, out); break;
+        case kQ6_K: dots_chunk<kQ6_K>(wb + mis, pk, sb0, n, TB == 1, out); break;
+        case kIQ4_XS: dots_chunk<kIQ4_XS>(wb + mis, pk, sb0, n, TB == 1, out); break;
+        default: dots_chunk<kQ8_0>(wb + mis, pk, sb0, n, TB == 1, out); break;
         }
     }
 }

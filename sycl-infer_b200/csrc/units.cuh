@@ -23,7 +23,7 @@
 namespace b200q {
 
 // ---- activation pack in shared memory (single-token calls) ----------------------------
-// Per 32-value group 48 bytes: int8 codes [32] | sx (f32) | xs0 (i32) | xs1 (i32) | (float)(xs0+xs1);
+// Per 32-value group 48 bytes: int8 codes [32] | sx (f32) | xs0 (i32) | xs1 (i32) | sx*(float)(xs0+xs1);
 // eight groups (one superblock) are followed by 16 bytes of padding so that the eight
 // lanes of a quarter-warp hit distinct banks.
 constexpr int kPackGroup = 48;
@@ -36,7 +36,14 @@ __device__ __forceinline__ uint32_t pack_addr(uint32_t pack, int g) {
 struct GroupMeta {
     float sx;
     int xs0, xs1;
-    float xsf;
+    float xsf; // (float)(xs0 + xs1)
+};
+
+// four consecutive groups (half a superblock), all 32 codes each, for a Q4_K/Q5_K half unit;
+// c = sx * (float)(xs0 + xs1) is the activation side of the min term
+struct ActG4 {
+    uint32_t x[4][8];
+    float sx[4], c[4];
 };
 
 // two consecutive groups, all 32 codes each
@@ -56,7 +63,7 @@ __device__ __forceinline__ void meta_from(const uint4 & v, GroupMeta & m) {
     m.sx = __uint_as_float(v.x);
     m.xs0 = (int)v.y;
     m.xs1 = (int)v.z;
-    m.xsf = __uint_as_float(v.w);
+    m.xsf = (float)(m.xs0 + m.xs1);
 }
 
 struct PackA { // staged pack, token 0
@@ -71,6 +78,18 @@ struct PackA { // staged pack, token 0
         a.xb[4] = b1.x, a.xb[5] = b1.y, a.xb[6] = b1.z, a.xb[7] = b1.w;
         meta_from(am, a.ma);
         meta_from(bm, a.mb);
+    }
+    __device__ __forceinline__ void g4(int g, ActG4 & a) const { // g a multiple of 4
+        const uint32_t p0 = pack_addr(pack, g);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t p = p0 + i * kPackGroup;
+            const uint4 x0 = lds128(p), x1 = lds128(p + 16), m = lds128(p + 32);
+            a.x[i][0] = x0.x, a.x[i][1] = x0.y, a.x[i][2] = x0.z, a.x[i][3] = x0.w;
+            a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
+            a.sx[i] = __uint_as_float(m.x);
+            a.c[i] = __uint_as_float(m.w);
+        }
     }
     __device__ __forceinline__ void g6(int g, int hs, int, ActG6 & a) const {
 #pragma unroll
@@ -207,6 +226,86 @@ template <int TYPE> struct WUnitK45 {
 };
 template <> struct WUnit<kQ4_K> : WUnitK45<kQ4_K> {};
 template <> struct WUnit<kQ5_K> : WUnitK45<kQ5_K> {};
+
+// Half a Q4_K/Q5_K superblock (groups 4h..4h+3, 128 weights) for single-token calls: the
+// four 6-bit (scale, min) pairs of a half unpack with a handful of 32-bit operations
+// (bytes 0-3 / 4-7 hold groups 0-3 directly; groups 4-7 take four bits from bytes 8-11 and
+// two from the top of bytes 0-7), and the fp32 work is factored as
+//   d * sum_g sc_g * (sx_g * wd_g)  -  dmin * sum_g m_g * (sx_g * xsum_g)
+// so only two multiplies per superblock half touch d and dmin.
+template <int TYPE> struct HalfK45 {
+    static constexpr int kHiShift = TYPE == kQ4_K ? 4 : 3;
+    static constexpr float kHiScale = TYPE == kQ4_K ? 0.0625f : 0.125f;
+
+    // exact sums of the four groups; odd groups come scaled by 1 << kHiShift
+    static __device__ __forceinline__ void dots(uint32_t sb, int h, const ActG4 & a, int (&w)[4]) {
+        const uint32_t qs = sb + (TYPE == kQ4_K ? 16u : 48u) + 64u * h;
+        uint32_t hq[8];
+        if (TYPE == kQ5_K) {
+            const uint4 h0 = lds128(sb + 16), h1 = lds128(sb + 32);
+            hq[0] = h0.x, hq[1] = h0.y, hq[2] = h0.z, hq[3] = h0.w;
+            hq[4] = h1.x, hq[5] = h1.y, hq[6] = h1.z, hq[7] = h1.w;
+        }
+#pragma unroll
+        for (int pr = 0; pr < 2; pr++) { // pair pr: groups 4h+2pr (low nibbles), 4h+2pr+1 (high)
+            const uint4 q0 = lds128(qs + 32 * pr), q1 = lds128(qs + 32 * pr + 16);
+            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            int sa0 = 0, sa1 = 0, sb0 = 0, sb1 = 0;
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                uint32_t lo0, hi0, lo1, hi1;
+                if (TYPE == kQ4_K) {
+                    lo0 = q[k] & 0x0F0F0F0Fu, hi0 = q[k] & 0xF0F0F0F0u;
+                    lo1 = q[k + 1] & 0x0F0F0F0Fu, hi1 = q[k + 1] & 0xF0F0F0F0u;
+                } else { // bit g of qh[i] is the fifth bit of element i of group g
+                    const uint32_t t0 = hq[k] >> (4 * h + 2 * pr), t1 = hq[k + 1] >> (4 * h + 2 * pr);
+                    lo0 = (q[k] & 0x0F0F0F0Fu) | ((t0 & 0x01010101u) << 4);
+                    hi0 = ((q[k] >> 1) & 0x78787878u) | ((t0 & 0x02020202u) << 6);
+                    lo1 = (q[k + 1] & 0x0F0F0F0Fu) | ((t1 & 0x01010101u) << 4);
+                    hi1 = ((q[k + 1] >> 1) & 0x78787878u) | ((t1 & 0x02020202u) << 6);
+                }
+                sa0 = dp4a_us(lo0, a.x[2 * pr][k], sa0);
+                sb0 = dp4a_us(hi0, a.x[2 * pr + 1][k], sb0);
+                sa1 = dp4a_us(lo1, a.x[2 * pr][k + 1], sa1);
+                sb1 = dp4a_us(hi1, a.x[2 * pr + 1][k + 1], sb1);
+            }
+            w[2 * pr] = sa0 + sa1;
+            w[2 * pr + 1] = sb0 + sb1;
+        }
+    }
+    static __device__ __forceinline__ float term(uint32_t sb, int h, const ActG4 & a) {
+        const uint4 hdr = lds128(sb);
+        int w[4];
+        dots(sb, h, a, w);
+        // (scale, min) of groups 4h..4h+3 (get_scale_min_k4, src/common/quant.h:136-144 of the reference)
+        const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, mn_lo = hdr.z & 0x3F3F3F3Fu;
+        const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y & 0xC0C0C0C0u) >> 2);
+        const uint32_t mn_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z & 0xC0C0C0C0u) >> 2);
+        const uint32_t sc = h ? sc_hi : sc_lo, mn = h ? mn_hi : mn_lo;
+        float ve = 0.f, vo = 0.f, ms = 0.f;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const float scf = (float)((sc >> (8 * g)) & 0xFF), mnf = (float)((mn >> (8 * g)) & 0xFF);
+            const float u = a.sx[g] * (float)w[g];
+            if (g & 1) {
+                vo = fmaf(scf, u, vo);
+            } else {
+                ve = fmaf(scf, u, ve);
+            }
+            ms = fmaf(mnf, a.c[g], ms);
+        }
+        const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
+        return d * fmaf(vo, kHiScale, ve) - dmin * ms;
+    }
+    static __device__ __forceinline__ void exact(uint32_t sb, int h, const ActG4 & a, int G, int32_t * wd) {
+        int w[4];
+        dots(sb, h, a, w);
+        wd[G] = w[0];
+        wd[G + 1] = w[1] >> kHiShift;
+        wd[G + 2] = w[2];
+        wd[G + 3] = w[3] >> kHiShift;
+    }
+};
 
 // ------------------------------------------------------------------------------- Q6_K
 template <> struct WUnit<kQ6_K> {
@@ -400,5 +499,41 @@ __device__ __forceinline__ void unit_exact(const WUnit<TYPE> & w, const typename
         w.exact(a, 8 * sbi + 2 * u, wd);
     }
 }
+
+// ---- the unit a single-token call works in -----------------------------------------------
+// H units per superblock; the activation of a unit is loaded once (from the pack) and met
+// by every row the warp owns.
+template <int TYPE> struct Unit1 {
+    static constexpr int H = 4;
+    using Act = typename WUnit<TYPE>::Act;
+    static __device__ __forceinline__ void load_act(const PackA & as, int sbi, int u, Act & a) {
+        b200q::load_act<TYPE>(as, sbi, u, 0, a);
+    }
+    static __device__ __forceinline__ float term(uint32_t sb, int u, const Act & a) {
+        WUnit<TYPE> w;
+        w.load(sb, u);
+        return w.term(a);
+    }
+    static __device__ __forceinline__ void exact(uint32_t sb, int sbi, int u, const Act & a, int32_t * wd) {
+        WUnit<TYPE> w;
+        w.load(sb, u);
+        unit_exact<TYPE>(w, a, sbi, u, wd);
+    }
+};
+template <int TYPE> struct Unit1K45 {
+    static constexpr int H = 2;
+    using Act = ActG4;
+    static __device__ __forceinline__ void load_act(const PackA & as, int sbi, int u, Act & a) {
+        as.g4(8 * sbi + 4 * u, a);
+    }
+    static __device__ __forceinline__ float term(uint32_t sb, int u, const Act & a) {
+        return HalfK45<TYPE>::term(sb, u, a);
+    }
+    static __device__ __forceinline__ void exact(uint32_t sb, int sbi, int u, const Act & a, int32_t * wd) {
+        HalfK45<TYPE>::exact(sb, u, a, 8 * sbi + 4 * u, wd);
+    }
+};
+template <> struct Unit1<kQ4_K> : Unit1K45<kQ4_K> {};
+template <> struct Unit1<kQ5_K> : Unit1K45<kQ5_K> {};
 
 } // namespace b200q

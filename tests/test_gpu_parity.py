@@ -98,7 +98,7 @@ def test_xq_fused_silu_golden(be):
 
 
 @pytest.mark.parametrize("t", TYPES)
-@pytest.mark.parametrize("K,N,TB,tok", [(256, 3, 1, 0), (1024, 37, 1, 0), (4352, 9, 3, 2)])
+@pytest.mark.parametrize("K,N,TB,tok", [(256, 3, 1, 0), (1024, 37, 1, 0), (5120, 7, 1, 0), (4352, 9, 3, 2), (512, 5, 9, 4)])
 def test_block_dots_bit_exact(be, orc, po, pkg, t, K, N, TB, tok):
     w = pkg.synth.make_weight(t, N, K, 400 + t)
     a = orc.xq(pkg.synth.make_activation(TB, K, 401), None, TB)
@@ -209,7 +209,9 @@ def test_config0_full_size(be, orc, pkg):
 @pytest.mark.parametrize("name", ["k", "v", "gate", "down"])
 def test_config1_layer_shapes_full_size(be, orc, pkg, name):
     """Dense-layer projections of benchmark configuration 1 at full size (batch 1), plus
-    size-independent properties: alpha-linearity and row-slice consistency are exact."""
+    size-independent properties: alpha-linearity is exact, and a row slice computed as its own
+    call agrees with the same rows of the full call (the two may tile differently, so the
+    fp32 summation order may differ)."""
     shape = {n: (t, r, k) for n, t, r, k in pkg.synth.dense_layer_shapes("Q4_K_M")}[name]
     t, N, K = shape
     w = pkg.synth.make_weight(t, N, K, 900)
@@ -222,7 +224,7 @@ def test_config1_layer_shapes_full_size(be, orc, pkg, name):
     rb = pkg.synth.row_bytes(t, K)
     r0, r1 = N // 3, N // 3 + 100
     part = gpu_gemm(be, t, w[r0 * rb:r1 * rb], K, r1 - r0, a, 1)
-    assert np.array_equal(part[0], got[0, r0:r1])
+    assert rel_err(part, got[:, r0:r1].astype(np.float64), ab[:, r0:r1]) <= 1e-6
 
 
 def test_errors_are_reported_not_swallowed(be, pkg):
