@@ -489,7 +489,17 @@ cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secon
     if (c.TB == 1) {
         // two rows per warp share every activation load; one row per warp gives twice the
         // tiles, which matters when a call is too small to give every CTA a 16-row tile
-        const bool rw2 = rw_env ? rw_env == 2 : c.total_rows >= 16 * 2 * kSMs;
+        // ... and when rows are too long for two 16-row tiles of at least 3 KB per row copy
+        // (small bulk copies waste the copy engine), 8-row tiles with longer segments win
+        int max_sbb = 0;
+        for (int i = 0; i < c.n_segs; i++) {
+            max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+        }
+        const int nb = c.K >> 8;
+        const size_t room = (kSmemBudget - 128 - (size_t)nb * kPackSB) / 2;
+        const bool whole_rows = (size_t)16 * nb * max_sbb + 48 <= room;
+        const bool long_copies = room / 16 >= 3072 + 48;
+        const bool rw2 = rw_env ? rw_env == 2 : (c.total_rows >= 16 * 2 * kSMs && (whole_rows || long_copies));
         return rw2 ? launch_stream_tt<1, 2>(s, a, pdl_secondary) : launch_stream_tt<1, 1>(s, a, pdl_secondary);
     }
     if (c.TB == 2) {
