@@ -89,6 +89,24 @@ int b200q_i8_gemm(void * stream, const b200q_seg * segs /*host*/, int n_segs, in
 int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
                      int32_t * xsumq);
 
+/* b200q_quant_gemv for callers that cannot allocate device memory.
+ * No counterpart in the reference.  Some hosts of this library have no allocator to give
+ * it: an engine that committed all device memory to its weight blob and arena up front, a
+ * plugin that must not call cudaMalloc in its host process, a call site where allocation is
+ * illegal.  They cannot provide the int8 activation scratch b200q_quant_gemv asks for, so
+ * this entry point uses a scratch array built into the library image (56 KB on every GPU
+ * that loads the library, for the life of the process).  It allocates nothing and calls no
+ * allocating routine.  Limits and rules:
+ *  - one token per call (TB = 1) and K <= B200Q_STATIC_MAX_K; larger K is refused with
+ *    B200Q_EUNSUPPORTED and a message naming b200q_quant_gemv as the alternative;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress)
+ *    with that device current; make that first call before starting any stream capture;
+ *  - every call on a device shares the one array.  Calls that may overlap on the GPU
+ *    (different streams, or graphs replayed concurrently) race on it: serialize them.  The
+ *    array keeps the previous call's contents; each call overwrites all it reads. */
+#define B200Q_STATIC_MAX_K 32768
+int b200q_quant_gemv_static(void * stream, const b200q_seg * segs /*host*/, int n_segs);
+
 /* Parity instrument: the exact int32 per-group dot products the reference forms inside
  * q4k/q5k/q6k_i8_block (src/backend/cpu/kernels/i8.cpp:57,117,149) for token t.
  * wd[row*D + j], D = K/32 (K/16 for Q6_K: raw codes 0..63, 16-value scale groups).

@@ -123,6 +123,12 @@ class cuda_backend:
         s0 = segs[0] if not isinstance(segs, gemv_seg) else segs
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
+    def quant_gemv_static(self, segs):
+        """One-token quant_gemv on the library's built-in scratch: for hosts that cannot
+        allocate the activation scratch themselves (K <= 32768; calls must not overlap)."""
+        arr, n = _pack(segs)
+        self.lib.check(self.lib.quant_gemv_static(self._s(), arr, n))
+
     # parity instrument (no reference operator: the reference never exposes these sums)
     def i8_block_dots(self, w, type, K, n_rows, x8, TB, t, wd):
         self.lib.check(self.lib.i8_block_dots(self._s(), _ptr(w), type, K, n_rows, _ptr(x8), TB, t, _ptr(wd)))

@@ -32,7 +32,7 @@ static inline bool aligned(const void * p, size_t a) {
 
 // Validate the segments of one call and flatten them for the kernels.  A call shares
 // one quantized activation, so every segment must have the same K.
-static int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
+int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
                       const int32_t * xsumq, CallDev & c) {
     if (!segs || n_segs < 1 || n_segs > B200Q_MAX_SEGS) {
         set_error("n_segs must be 1..%d (got %d)", B200Q_MAX_SEGS, n_segs);
@@ -110,7 +110,7 @@ static int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t *
 
 // Kernel choice: 1..8 tokens stream the weights once through shared memory; larger
 // token counts take the general rows kernel.  B200Q_KERNEL=rows forces the latter (A/B).
-static cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
+cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     static const bool force_rows = [] {
         const char * e = getenv("B200Q_KERNEL");
         return e && strcmp(e, "rows") == 0;

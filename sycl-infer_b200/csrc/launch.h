@@ -15,4 +15,9 @@ cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K,
 cudaError_t launch_block_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8,
                               int TB, int t, int32_t * wd);
 
+// shared by the C-ABI translation units: validate + flatten a call, pick the GEMV kernel
+int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
+               const int32_t * xsumq, CallDev & c);
+cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary);
+
 } // namespace b200q
