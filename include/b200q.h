@@ -89,6 +89,41 @@ int b200q_i8_gemm(void * stream, const b200q_seg * segs /*host*/, int n_segs, in
 int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
                      int32_t * xsumq);
 
+/* ---- routed mixture-of-experts (free launchers in the reference, src/backend/gpu/kernels/kernels.h:595-792,
+ * host twins src/backend/cpu/cpu_types.h:195-211).  Expert e's weights are the plane
+ * bank + e*plane_bytes of raw GGUF blocks; a pair p = t*top_k + j is token t's j-th expert. ---- */
+
+/* moe_router_launch (kernels.h:600-601) = cpu_moe_route (src/backend/cpu/kernels/moe.cpp:72-137).
+ * gate_inp: F32 router [n_expert][n_embd], or NULL when `logits` already holds the logits.
+ * On return logits holds the softmax probabilities, ids/wts [n_tok][top_k] the selection. */
+int b200q_moe_route(void * stream, const float * gate_inp, const float * x, int x_stride, int n_tok, int n_embd,
+                    int n_expert, int top_k, float * logits, int32_t * ids, float * wts);
+
+/* moe_csr_clear/count/prefix/scatter_launch (kernels.h:604-609) in one launch: off[n_expert+1],
+ * pair[n_pairs] (pairs of an expert in increasing pair order), active[n_expert], n_active[1]. */
+int b200q_moe_csr(void * stream, const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,
+                  int32_t * active, int32_t * n_active);
+
+/* moe_grp_gate_up_launch (kernels.h:638-642): h[p*h_stride + i] = silu(gate_e[i].x_t) * (up_e[i].x_t) for
+ * every pair, on the tokens' quantized activation (x8/xmeta/xsumq with TB = n_tok, from b200q_xq).
+ * n_act_max bounds the number of active experts (grid size; n_expert is always safe). */
+int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
+                      size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                      const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                      const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                      int n_ff_exp, int top_k);
+
+/* moe_grp_down_launch (kernels.h:718-721): acc[p*acc_stride + r] = down_e[r] . h_p on the pairs'
+ * re-quantized intermediate (h8/hmeta/hsumq with TB = n_pairs, from b200q_xq on h). */
+int b200q_moe_down(void * stream, const void * dbank, uint32_t dtype, size_t slot_db, const int32_t * off,
+                   const int32_t * pair, const int32_t * active, const int32_t * n_active, int n_act_max,
+                   const int8_t * h8, const float * hmeta, const int32_t * hsumq, int n_pairs, float * acc,
+                   int acc_stride, int n_embd, int n_ff_exp);
+
+/* moe_reduce_launch (kernels.h:753-754) = cpu_moe_reduce (moe.cpp:562-574): out[t] += sum_j wts[t,j]*acc[t*top_k+j] */
+int b200q_moe_reduce(void * stream, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
+                     int acc_stride, float * out, int out_stride);
+
 /* b200q_quant_gemv for callers that cannot allocate device memory.
  * No counterpart in the reference.  Some hosts of this library have no allocator to give
  * it: an engine that committed all device memory to its weight blob and arena up front, a

@@ -35,6 +35,13 @@ _SIGS = {
     "b200q_i8_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_gemm": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int]),
     "b200q_quant_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_moe_route": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_moe_csr": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
+    "b200q_moe_gate_up": (C.c_int, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp,
+                                    C.c_int, _vp, _vp, _vp, C.c_int, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "b200q_moe_down": (C.c_int, [_vp, _vp, C.c_uint32, C.c_size_t, _vp, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp,
+                                 C.c_int, _vp, C.c_int, C.c_int, C.c_int]),
+    "b200q_moe_reduce": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int]),
     "b200q_quant_gemv_static": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_block_dots": (C.c_int, [_vp, _vp, C.c_uint32, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]),
     "b200q_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),

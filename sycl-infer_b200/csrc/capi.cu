@@ -221,6 +221,102 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
     return B200Q_OK;
 }
 
+int b200q_moe_route(void * stream, const float * gate_inp, const float * x, int x_stride, int n_tok, int n_embd,
+                    int n_expert, int top_k, float * logits, int32_t * ids, float * wts) {
+    if (!logits || !ids || !wts || (gate_inp && !x)) {
+        set_error("b200q_moe_route: logits, ids, wts (and x with gate_inp) must be non-null");
+        return B200Q_EINVAL;
+    }
+    if (n_tok < 1 || n_expert < 1 || n_expert > 4096 || top_k < 1 || top_k > n_expert || (gate_inp && n_embd < 1)) {
+        set_error("b200q_moe_route: bad shape (n_tok=%d n_expert=%d top_k=%d n_embd=%d)", n_tok, n_expert, top_k,
+                  n_embd);
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_route((cudaStream_t)stream, gate_inp, x, x_stride, n_tok, n_embd, n_expert, top_k, logits,
+                                   ids, wts));
+    return B200Q_OK;
+}
+
+int b200q_moe_csr(void * stream, const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,
+                  int32_t * active, int32_t * n_active) {
+    if (!ids || !off || !pair || !active || !n_active || n_pairs < 1 || n_expert < 1) {
+        set_error("b200q_moe_csr: null pointer or empty shape");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_csr((cudaStream_t)stream, ids, n_pairs, n_expert, off, pair, active, n_active));
+    return B200Q_OK;
+}
+
+static int moe_check(const char * who, const void * bank, uint32_t type, int K, int n_rows, const void * a,
+                     const void * b, const void * c, const void * d) {
+    if (!bank || !a || !b || !c || !d) {
+        set_error("%s: null pointer", who);
+        return B200Q_EINVAL;
+    }
+    if (!type_ok(type)) {
+        set_error("%s: unsupported ggml type %u", who, type);
+        return B200Q_EUNSUPPORTED;
+    }
+    if (K < 256 || (K & 255) || n_rows < 1 || !aligned(bank, 16)) {
+        set_error("%s: K must be a multiple of 256, rows >= 1, banks 16-byte aligned (K=%d rows=%d)", who, K, n_rows);
+        return B200Q_EINVAL;
+    }
+    return B200Q_OK;
+}
+
+int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
+                      size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                      const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                      const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                      int n_ff_exp, int top_k) {
+    int rc = moe_check("b200q_moe_gate_up", gbank, gtype, n_embd, n_ff_exp, off, pair, active, n_active);
+    if (rc == B200Q_OK) {
+        rc = moe_check("b200q_moe_gate_up", ubank, utype, n_embd, n_ff_exp, x8, xmeta, xsumq, h);
+    }
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    if (n_act_max < 1 || n_tok < 1 || top_k < 1 || h_stride < n_ff_exp || (slot_gb & 15) || (slot_ub & 15)) {
+        set_error("b200q_moe_gate_up: bad n_act_max/n_tok/top_k/h_stride or plane bytes not a multiple of 16");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_rows((cudaStream_t)stream, gbank, ubank, (int)gtype, (int)utype, slot_gb, slot_ub, off,
+                                  pair, active, n_active, n_act_max, x8, xmeta, xsumq, n_tok, top_k, n_embd, n_ff_exp,
+                                  h, h_stride, 1));
+    return B200Q_OK;
+}
+
+int b200q_moe_down(void * stream, const void * dbank, uint32_t dtype, size_t slot_db, const int32_t * off,
+                   const int32_t * pair, const int32_t * active, const int32_t * n_active, int n_act_max,
+                   const int8_t * h8, const float * hmeta, const int32_t * hsumq, int n_pairs, float * acc,
+                   int acc_stride, int n_embd, int n_ff_exp) {
+    int rc = moe_check("b200q_moe_down", dbank, dtype, n_ff_exp, n_embd, off, pair, active, n_active);
+    if (rc == B200Q_OK) {
+        rc = moe_check("b200q_moe_down", dbank, dtype, n_ff_exp, n_embd, h8, hmeta, hsumq, acc);
+    }
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    if (n_act_max < 1 || n_pairs < 1 || acc_stride < n_embd || (slot_db & 15)) {
+        set_error("b200q_moe_down: bad n_act_max/n_pairs/acc_stride or plane bytes not a multiple of 16");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_rows((cudaStream_t)stream, dbank, nullptr, (int)dtype, (int)dtype, slot_db, 0, off, pair,
+                                  active, n_active, n_act_max, h8, hmeta, hsumq, n_pairs, 0, n_ff_exp, n_embd, acc,
+                                  acc_stride, 0));
+    return B200Q_OK;
+}
+
+int b200q_moe_reduce(void * stream, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
+                     int acc_stride, float * out, int out_stride) {
+    if (!acc || !wts || !out || top_k < 1 || n_tok < 1 || n_embd < 1 || acc_stride < n_embd || out_stride < n_embd) {
+        set_error("b200q_moe_reduce: null pointer or bad shape");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_reduce((cudaStream_t)stream, acc, wts, top_k, n_tok, n_embd, acc_stride, out, out_stride));
+    return B200Q_OK;
+}
+
 int b200q_device_status(int * status, int clear) {
     if (!status) {
         set_error("b200q_device_status: status must be non-null");

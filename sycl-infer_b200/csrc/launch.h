@@ -15,6 +15,18 @@ cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K,
 cudaError_t launch_block_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8,
                               int TB, int t, int32_t * wd);
 
+cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
+                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts);
+cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
+                           int32_t * pair, int32_t * active, int32_t * n_active);
+cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
+                            size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
+                            const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                            const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
+                            float * out, int out_stride, int fuse_silu);
+cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
+                              int acc_stride, float * out, int out_stride);
+
 // shared by the C-ABI translation units: validate + flatten a call, pick the GEMV kernel
 int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
                const int32_t * xsumq, CallDev & c);

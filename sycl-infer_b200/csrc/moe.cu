@@ -1,0 +1,309 @@
+// Routed mixture-of-experts on raw GGUF expert planes: router, token->expert CSR, grouped
+// gate|up (silu(gate)*up fused), grouped down, weighted reduction.
+//
+// Arithmetic follows the reference's host twins (src/backend/cpu/kernels/moe.cpp of the
+// reference): router = softmax over all experts with a sequential fp32 sum, top-k by rank
+// counting with ties to the lower index, weights divided by max(sum, 6.103515625e-5)
+// (:72-137); experts = int8 gate/up rows on the token's quantized activation, h = silu(g)*u,
+// h re-quantized per 32 values, down rows on that (:476-559); reduce = out[t] += sum_j w*acc
+// with a double accumulator (:562-574).  Expert e's plane starts at bank + e*plane_bytes.
+#include "decode.cuh"
+#include "launch.h"
+
+namespace b200q {
+
+// ---- router --------------------------------------------------------------------------------
+// One CTA per token.  logits are given or computed as gate_inp . x with double accumulation.
+__global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
+                                                        int x_stride, int n_embd, int n_expert, int top_k,
+                                                        float * __restrict__ logits, int32_t * __restrict__ ids,
+                                                        float * __restrict__ wts) {
+    extern __shared__ float p[]; // n_expert probabilities, then n_expert selection flags
+    int * sel = reinterpret_cast<int *>(p + n_expert);
+    __shared__ float s_max, s_inv, s_den;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    float * lg = logits + (size_t)t * n_expert;
+    if (gate_inp) {
+        const float * xr = x + (size_t)t * x_stride;
+        for (int e = warp; e < n_expert; e += nw) {
+            const float * w = gate_inp + (size_t)e * n_embd;
+            double a = 0.0;
+            for (int k = lane; k < n_embd; k += 32) {
+                a += (double)w[k] * (double)xr[k];
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+            }
+            if (lane == 0) {
+                p[e] = (float)a;
+            }
+        }
+    } else {
+        for (int e = tid; e < n_expert; e += blockDim.x) {
+            p[e] = lg[e];
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float mx = -3.402823466e38f;
+        for (int e = 0; e < n_expert; e++) {
+            mx = fmaxf(mx, p[e]);
+        }
+        s_max = mx;
+    }
+    __syncthreads();
+    for (int e = tid; e < n_expert; e += blockDim.x) {
+        p[e] = (float)exp((double)__fsub_rn(p[e], s_max)); // one rounding: a correctly rounded expf
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        for (int e = 0; e < n_expert; e++) {
+            sum = __fadd_rn(sum, p[e]);
+        }
+        s_inv = __fdiv_rn(1.f, sum);
+    }
+    __syncthreads();
+    for (int e = tid; e < n_expert; e += blockDim.x) {
+        p[e] = __fmul_rn(p[e], s_inv);
+        lg[e] = p[e]; // the reference leaves the probabilities in its logits scratch
+    }
+    __syncthreads();
+    for (int e = tid; e < n_expert; e += blockDim.x) {
+        const float pe = p[e];
+        int rank = 0;
+        for (int f = 0; f < n_expert; f++) {
+            const float pf = p[f];
+            rank += (pf > pe) || (pf == pe && f < e);
+        }
+        sel[e] = rank < top_k ? rank : -1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float wsum = 0.f;
+        for (int e = 0; e < n_expert; e++) { // expert order, like the reference's accumulation
+            if (sel[e] >= 0) {
+                wsum = __fadd_rn(wsum, p[e]);
+            }
+        }
+        s_den = fmaxf(wsum, 6.103515625e-5f);
+    }
+    __syncthreads();
+    for (int e = tid; e < n_expert; e += blockDim.x) {
+        if (sel[e] >= 0) {
+            ids[(size_t)t * top_k + sel[e]] = e;
+            wts[(size_t)t * top_k + sel[e]] = __fdiv_rn(p[e], s_den);
+        }
+    }
+}
+
+// ---- token -> expert CSR (one CTA) -----------------------------------------------------------
+// off[e]..off[e+1] index `pair`, which lists the (token, slot) pair ids routed to expert e in
+// increasing pair order; active[0..n_active) lists the experts with at least one pair.
+__global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict__ ids, int n_pairs, int n_expert,
+                                                      int32_t * off, int32_t * pair, int32_t * active,
+                                                      int32_t * n_active) {
+    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
+        off[e] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < n_expert) {
+            atomicAdd(&off[e + 1], 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int na = 0;
+        for (int e = 0; e < n_expert; e++) {
+            if (off[e + 1] > 0) {
+                active[na++] = e;
+            }
+            off[e + 1] += off[e];
+        }
+        *n_active = na;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) { // deterministic fill in pair order
+        int o = off[e];
+        const int end = off[e + 1];
+        for (int i = 0; i < n_pairs && o < end; i++) {
+            if (ids[i] == e) {
+                pair[o++] = i;
+            }
+        }
+    }
+}
+
+// ---- grouped expert rows ---------------------------------------------------------------------
+constexpr int kMoeTT = 4; // pairs of one expert handled per pass over a weight row
+
+template <int TYPE, int TT>
+__device__ __forceinline__ void expert_row(const uint8_t * wrow, int nb, const ActView & a, const int (&tok)[TT],
+                                           float (&acc)[TT]) {
+    const int lane = threadIdx.x & 31, j = lane & 7;
+    for (int b = lane >> 3; b < nb; b += 4) {
+        Part<TYPE, GmemW> p;
+        p.load(wrow + (size_t)b * Fmt<TYPE>::SB, j);
+#pragma unroll
+        for (int i = 0; i < TT; i++) {
+            acc[i] += p.term(a, 8 * b, tok[i]);
+        }
+    }
+}
+
+template <int TT>
+__device__ __forceinline__ void expert_row_any(int type, const uint8_t * wrow, int nb, const ActView & a,
+                                               const int (&tok)[TT], float (&acc)[TT]) {
+    switch (type) {
+    case kQ4_K: expert_row<kQ4_K, TT>(wrow, nb, a, tok, acc); break;
+    case kQ5_K: expert_row<kQ5_K, TT>(wrow, nb, a, tok, acc); break;
+    case kQ6_K: expert_row<kQ6_K, TT>(wrow, nb, a, tok, acc); break;
+    case kIQ4_XS: expert_row<kIQ4_XS, TT>(wrow, nb, a, tok, acc); break;
+    default: expert_row<kQ8_0, TT>(wrow, nb, a, tok, acc); break;
+    }
+}
+
+struct MoeArgs {
+    const uint8_t *bank_a, *bank_b; // gate and up planes (gate|up), or down plane in bank_a
+    size_t plane_a, plane_b;
+    int type_a, type_b;
+    const int32_t *off, *pair, *active, *n_active;
+    const int8_t * x8;
+    const float * xmeta;
+    const int32_t * xsumq;
+    int TB;         // tokens (gate|up) or pairs (down) in the activation views
+    int top_k;      // gate|up: token of pair p is p / top_k; down: 0 (activation row = pair)
+    int K, n_rows;  // input length, rows per expert plane
+    float * out;    // h[pair*out_stride + row] or acc[pair*out_stride + row]
+    int out_stride;
+    int fuse_silu;  // 1: out = silu(a) * b, 0: out = a
+};
+
+__device__ __forceinline__ float silu_host_like(float g) { // x / (1 + expf(-x)), expf rounded once
+    const float e = (float)exp((double)(-g));
+    return __fdiv_rn(g, __fadd_rn(1.0f, e));
+}
+
+// grid.x = row blocks (8 rows each), grid.y = expert slots; one warp per row of the expert
+__global__ void __launch_bounds__(256) moe_rows_kernel(const __grid_constant__ MoeArgs m) {
+    const int slot = blockIdx.y;
+    if (slot >= *m.n_active) {
+        return;
+    }
+    const int e = m.active[slot];
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= m.n_rows) {
+        return;
+    }
+    const int nb = m.K >> 8;
+    const int p0 = m.off[e], p1 = m.off[e + 1];
+    const ActView a{m.x8, m.xmeta, m.xsumq, m.TB};
+    const uint8_t * wa = m.bank_a + (size_t)e * m.plane_a + (size_t)row * nb * sb_bytes(m.type_a);
+    const uint8_t * wb = m.fuse_silu ? m.bank_b + (size_t)e * m.plane_b + (size_t)row * nb * sb_bytes(m.type_b) : nullptr;
+    for (int q = p0; q < p1; q += kMoeTT) {
+        int pr[kMoeTT], tok[kMoeTT];
+#pragma unroll
+        for (int i = 0; i < kMoeTT; i++) {
+            pr[i] = m.pair[min(q + i, p1 - 1)];
+            tok[i] = m.top_k > 0 ? pr[i] / m.top_k : pr[i];
+        }
+        float ga[kMoeTT] = {0.f, 0.f, 0.f, 0.f}, ua[kMoeTT] = {0.f, 0.f, 0.f, 0.f};
+        expert_row_any<kMoeTT>(m.type_a, wa, nb, a, tok, ga);
+        if (m.fuse_silu) {
+            expert_row_any<kMoeTT>(m.type_b, wb, nb, a, tok, ua);
+        }
+#pragma unroll
+        for (int i = 0; i < kMoeTT; i++) {
+            ga[i] = warp_sum(ga[i]);
+            ua[i] = warp_sum(ua[i]);
+        }
+        if (lane < kMoeTT && q + lane < p1) {
+            float g = 0.f, u = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMoeTT; i++) {
+                g = lane == i ? ga[i] : g;
+                u = lane == i ? ua[i] : u;
+            }
+            int pi = pr[0];
+#pragma unroll
+            for (int i = 1; i < kMoeTT; i++) {
+                pi = lane == i ? pr[i] : pi;
+            }
+            m.out[(size_t)pi * m.out_stride + row] = m.fuse_silu ? __fmul_rn(silu_host_like(g), u) : g;
+        }
+    }
+}
+
+// out[t*out_stride + c] += (float) sum_j (double)w[t,j] * acc[(t*top_k + j)*acc_stride + c]
+__global__ void __launch_bounds__(256) moe_reduce_kernel(const float * __restrict__ acc, const float * __restrict__ wts,
+                                                         int top_k, int n_tok, int n_embd, int acc_stride, float * out,
+                                                         int out_stride) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tok * n_embd) {
+        return;
+    }
+    const int t = (int)(i / n_embd), c = (int)(i - (long long)t * n_embd);
+    double a = 0.0;
+    for (int j = 0; j < top_k; j++) {
+        const size_t pr = (size_t)t * top_k + j;
+        a += (double)wts[pr] * (double)acc[pr * (size_t)acc_stride + c];
+    }
+    out[(size_t)t * out_stride + c] += (float)a;
+}
+
+// ---- launchers -----------------------------------------------------------------------------------
+cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
+                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts) {
+    moe_route_kernel<<<n_tok, 256, (size_t)n_expert * 8, s>>>(gate_inp, x, x_stride, n_embd, n_expert, top_k, logits,
+                                                              ids, wts);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
+                           int32_t * pair, int32_t * active, int32_t * n_active) {
+    moe_csr_kernel<<<1, 256, 0, s>>>(ids, n_pairs, n_expert, off, pair, active, n_active);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
+                            size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
+                            const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                            const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
+                            float * out, int out_stride, int fuse_silu) {
+    MoeArgs m;
+    m.bank_a = static_cast<const uint8_t *>(bank_a);
+    m.bank_b = static_cast<const uint8_t *>(bank_b);
+    m.plane_a = plane_a;
+    m.plane_b = plane_b;
+    m.type_a = type_a;
+    m.type_b = type_b;
+    m.off = off;
+    m.pair = pair;
+    m.active = active;
+    m.n_active = n_active;
+    m.x8 = x8;
+    m.xmeta = xmeta;
+    m.xsumq = xsumq;
+    m.TB = TB;
+    m.top_k = top_k;
+    m.K = K;
+    m.n_rows = n_rows;
+    m.out = out;
+    m.out_stride = out_stride;
+    m.fuse_silu = fuse_silu;
+    const dim3 grid((unsigned)((n_rows + 7) / 8), (unsigned)n_act_max);
+    moe_rows_kernel<<<grid, 256, 0, s>>>(m);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
+                              int acc_stride, float * out, int out_stride) {
+    const long long n = (long long)n_tok * n_embd;
+    moe_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(acc, wts, top_k, n_tok, n_embd, acc_stride, out,
+                                                                 out_stride);
+    return cudaGetLastError();
+}
+
+} // namespace b200q

@@ -1,0 +1,115 @@
+"""Routed-MoE parity through the C ABI (benchmark configuration 3 and small cases).
+
+Stage by stage against the oracle, because each stage re-quantizes the previous one's output:
+router ids exact and weights within 1e-6 (tests/backend/cpu/kernels/test_cpu_moe_qsa_units.cpp:59-105
+of the reference); gate|up within 1e-5 of the sum of |terms|; down and reduce are checked on the
+intermediate the GPU itself produced (the oracle is run on those bytes), so a one-ulp difference
+in h cannot masquerade as a down-projection error.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+TOL = 1e-5
+G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_vectors.npz"))
+
+
+def test_router_golden_from_reference(be):
+    from sycl_infer_b200.moe import moe_router_launch
+    x, gate = torch.from_numpy(G["moe_x"]).cuda(), torch.from_numpy(G["moe_gate_inp"]).cuda()
+    n_tok, n_embd = x.shape
+    E, top_k = gate.shape[0], 2
+    logits = torch.zeros(n_tok, E, device="cuda")
+    ids = torch.zeros(n_tok, top_k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n_tok, top_k, device="cuda")
+    moe_router_launch(be, gate, 0, x, n_embd, n_tok, n_embd, E, top_k, logits, ids, wts)
+    be.synchronize()
+    assert np.array_equal(ids.cpu().numpy(), G["moe_ids"])
+    assert np.max(np.abs(wts.cpu().numpy() - G["moe_wts"])) <= 1e-6
+    assert np.max(np.abs(logits.cpu().numpy() - G["moe_logits"])) <= 1e-6
+
+
+@pytest.mark.parametrize("n_tok,E,top_k", [(1, 8, 2), (16, 256, 8), (5, 64, 6)])
+def test_router_from_logits(be, orc, pkg, n_tok, E, top_k):
+    from sycl_infer_b200.moe import moe_router_launch
+    lg = pkg.synth.make_router_logits(n_tok, E, 77 + E)
+    lg[0, :4] = lg[0, 0]  # ties go to the lower index
+    p, ids_o, wts_o = orc.moe_route_logits(lg, top_k)
+    logits = torch.from_numpy(lg.copy()).cuda()
+    ids = torch.zeros(n_tok, top_k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n_tok, top_k, device="cuda")
+    moe_router_launch(be, None, 0, None, 0, n_tok, 0, E, top_k, logits, ids, wts)
+    be.synchronize()
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    assert np.max(np.abs(wts.cpu().numpy() - wts_o)) <= 1e-6
+    assert np.max(np.abs(logits.cpu().numpy() - p)) <= 1e-7
+
+
+def _run_moe(be, orc, pkg, E, top_k, n_embd, n_ff, n_tok, types, seed):
+    from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_call
+    host, dev = make_synthetic_moe(E, top_k, n_embd, n_ff, types, seed)
+    x = pkg.synth.make_activation(n_tok, n_embd, seed + 50)
+    lg = pkg.synth.make_router_logits(n_tok, E, seed + 51)
+    base = pkg.synth.make_activation(n_tok, n_embd, seed + 52)
+    S = MoeScratch(dev, n_tok)
+    S.logits.copy_(torch.from_numpy(lg))
+    out = torch.from_numpy(base.copy()).cuda()
+    moe_call(be, dev, S, torch.from_numpy(x).cuda(), n_tok, out, logits_given=True)
+    be.synchronize()
+    assert be.device_status() == 0
+    # router
+    _, ids_o, wts_o = orc.moe_route_logits(lg, top_k)
+    ids = S.ids.cpu().numpy()
+    assert np.array_equal(ids, ids_o)
+    # CSR: every pair listed once under its expert, in increasing pair order
+    off, pair = S.off.cpu().numpy(), S.pair.cpu().numpy()
+    flat = ids.reshape(-1)
+    assert off[0] == 0 and off[-1] == n_tok * top_k
+    for e in range(E):
+        assert list(pair[off[e]:off[e + 1]]) == list(np.nonzero(flat == e)[0])
+    assert int(S.n_active.cpu()[0]) == len(np.unique(flat))
+    # gate|up: h vs the oracle's h (same activation codes on both sides)
+    a = orc.xq(x, None, n_tok)
+    assert np.array_equal(S.xq[0].cpu().numpy(), a.x8)
+    gw, uw, dw = host.gate_exps.numpy(), host.up_exps.numpy(), host.down_exps.numpy()
+    h_o, acc_o = orc.moe_experts(gw, uw, dw, types, n_embd, n_ff, x, ids_o)
+    h = S.h.cpu().numpy()
+    scale = np.max(np.abs(h_o)) + 1e-30
+    assert np.max(np.abs(h - h_o)) <= 2e-5 * scale  # product of two dots of ~1e-7 relative error each
+    # down on the GPU's own h: oracle quantizes those bytes and runs the down rows
+    rb = pkg.synth.row_bytes(types[2], n_ff) * n_embd
+    acc = S.acc.cpu().numpy()
+    hq = orc.xq(h, None, n_tok * top_k)
+    assert np.array_equal(S.hq[0].cpu().numpy(), hq.x8)
+    for p in range(0, n_tok * top_k, max(1, n_tok * top_k // 12)):  # a dozen pairs, full rows
+        e = flat[p]
+        one = orc.xq(h[p])
+        ref = orc.gemm(types[2], dw[e * rb:(e + 1) * rb], n_ff, n_embd, one)[0]
+        ab = orc.gemm_abs(types[2], dw[e * rb:(e + 1) * rb], n_ff, n_embd, one)[0]
+        assert np.max(np.abs(acc[p] - ref) / np.maximum(ab, 1e-30)) <= TOL
+    # reduce on the GPU's acc
+    ref_out = orc.moe_reduce(acc, S.wts.cpu().numpy(), base)
+    got = out.cpu().numpy()
+    assert np.max(np.abs(got - ref_out)) <= 1e-6 * max(1.0, np.max(np.abs(ref_out)))
+    # end to end against the all-oracle pipeline (loose: h is re-quantized on both sides)
+    full = orc.moe_reduce(acc_o, wts_o, base)
+    assert np.max(np.abs(got - full)) <= 2e-2 * np.max(np.abs(full))
+    return len(np.unique(flat))
+
+
+@pytest.mark.parametrize("types", [(12, 12, 12), (12, 12, 8), (13, 13, 14), (23, 23, 23)])
+def test_moe_small(be, orc, pkg, types):
+    _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=5, types=types, seed=3)
+
+
+def test_moe_single_token(be, orc, pkg):
+    _run_moe(be, orc, pkg, E=16, top_k=4, n_embd=256, n_ff=256, n_tok=1, types=(12, 12, 12), seed=5)
+
+
+def test_moe_config3_full_size(be, orc, pkg):
+    """256 experts, top-8, hidden 2048, expert FFN 512, Q4_K, 16 tokens."""
+    n = _run_moe(be, orc, pkg, E=256, top_k=8, n_embd=2048, n_ff=512, n_tok=16, types=(12, 12, 12), seed=0xB3)
+    assert 60 <= n <= 128
