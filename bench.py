@@ -140,7 +140,6 @@ def gpu_arm(args):
     for ly in layers:
         ly.attn.copy_(attn)
     out = torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
-    step_bytes = layers[0].algorithmic_bytes() if world == 1 else None
     full_bytes = pkg.synth.layer_weight_bytes("Q4_K_M") + 4 * (
         2 * hidden + layers[0].q_dim + 2 * layers[0].n_ff + (layers[0].q_dim + 2 * layers[0].kv_dim)
         + 2 * hidden + 2 * layers[0].n_ff)
@@ -172,8 +171,10 @@ def gpu_arm(args):
             if graphs:
                 graphs[(first + i) % L].replay()
             else:
-                layers[(first + i) % L].forward(xs[(first + i) % L], out)
+                j = (first + i) % L
+                layers[j].forward(xs[j], out, cached[j])
 
+    cached = [ly.calls(xs[i], out) for i, ly in enumerate(layers)]
     run_steps(max(args.warmup, 3))
     barrier()
     sampler = ClockSampler(local)

@@ -1,0 +1,55 @@
+"""Row-sharded layer on 2 GPUs (NCCL all-gather) against the same layer on one GPU.
+Skipped on a single-GPU box; the host logic is covered on CPU by test_sharding_cpu.py."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _worker(rank, world, port, TB, ret):
+    import sys
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    from sycl_infer_b200.layer import DenseLayer
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        be = pkg.make_cuda_backend(rank)
+        kw = dict(hidden=1024, n_head=8, n_kv=2, head_dim=128, n_ff=2048)
+        x = torch.from_numpy(pkg.synth.make_activation(TB, 1024, 5)).cuda()
+        attn = torch.from_numpy(pkg.synth.make_activation(TB, 1024, 6)).cuda()
+        outs = []
+        for r, w in ((rank, world), (0, 1)):
+            ly = DenseLayer(be, "Q4_K_M", seed=9, TB=TB, rank=r, world=w, **kw)
+            ly.attn.copy_(attn)
+            out = torch.zeros(TB, 1024, device="cuda")
+            ly.forward(x, out)
+            torch.cuda.synchronize()
+            outs.append((out.cpu().numpy(), ly.qkv.cpu().numpy(), ly.gu.cpu().numpy()))
+        ret[rank] = outs
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("TB", [1, 3])
+def test_row_sharded_layer_matches_single_gpu(TB):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, TB, ret), nprocs=2, join=True)
+    for rank in (0, 1):
+        (o2, qkv2, gu2), (o1, qkv1, gu1) = ret[rank]
+        for a, b in ((qkv2, qkv1), (gu2, gu1), (o2, o1)):
+            assert np.max(np.abs(a - b)) <= 1e-5 * max(1.0, np.max(np.abs(b)))
