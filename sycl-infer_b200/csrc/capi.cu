@@ -118,6 +118,10 @@ cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     if (!force_rows && stream_supported(c)) {
         return launch_gemv_stream(s, c, pdl_secondary);
     }
+    // more than 8 tokens: one tcgen05 int8 MMA per 32-value group (B200Q_KERNEL=rows: dp4a)
+    if (!force_rows && c.TB > 8) {
+        return launch_gemm_mma(s, c, pdl_secondary);
+    }
     return launch_gemv_rows(s, c, pdl_secondary);
 }
 
@@ -323,6 +327,9 @@ int b200q_device_status(int * status, int clear) {
         return B200Q_EINVAL;
     }
     B200Q_CUDA_OK(read_device_status(status, clear != 0));
+    int mma = 0;
+    B200Q_CUDA_OK(read_mma_status(&mma, clear != 0));
+    *status = *status ? *status : mma;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

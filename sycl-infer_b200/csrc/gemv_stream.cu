@@ -22,6 +22,7 @@
 #include <cstdlib>
 #include <type_traits>
 
+#include "async.cuh"
 #include "launch.h"
 #include "units.cuh"
 
@@ -29,7 +30,6 @@ namespace b200q {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kStreamThreads = 32 * (kConsumerWarps + 1);
-constexpr long long kSpinCycles = 2000000000LL; // about one second of SM clocks
 constexpr int kSmemBudget = 110 * 1024;         // two CTAs per SM
 
 __device__ int g_device_status = 0;
@@ -43,47 +43,6 @@ struct StreamArgs {
     int32_t tile_bytes; // shared bytes reserved per tile
     int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
-
-// ---- mbarrier / bulk-copy primitives (PTX) --------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    long long t0 = 0;
-    for (uint32_t n = 0;; n++) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok)
-                     : "r"(bar), "r"(parity)
-                     : "memory");
-        if (ok) {
-            return true;
-        }
-        if (n == 64) {
-            t0 = clock64();
-        } else if (n > 64 && clock64() - t0 > kSpinCycles) {
-            break;
-        }
-    }
-    atomicExch(&g_device_status, B200Q_ETIMEOUT);
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
 
 // Build the activation pack of superblocks [sb0, sb0+n) of token 0 (see units.cuh).
 __device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int sb0, int n, int tid, int nthr) {
@@ -273,7 +232,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                     for (int o = 16; o > 0; o >>= 1) {
                         total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
                     }
-                    alive = mbar_wait(bar_empty + 8 * stage, par);
+                    alive = mbar_wait(bar_empty + 8 * stage, par, &g_device_status);
                     alive = __all_sync(0xFFFFFFFFu, alive);
                     if (!alive) {
                         break;
@@ -335,7 +294,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
             }
             for (int ch = 0; ch < n_chunks; ch++, it++) {
                 const int stage = it % S;
-                if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1)) {
+                if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1, &g_device_status)) {
                     return;
                 }
                 const int sb0 = ch * a.kb_max;

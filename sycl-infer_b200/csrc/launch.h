@@ -10,6 +10,8 @@ cudaError_t launch_gemv_rows(cudaStream_t s, const CallDev & call, bool pdl_seco
 bool stream_supported(const CallDev & call);
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 cudaError_t read_device_status(int * status, bool clear);
+cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & call, bool pdl_secondary);
+cudaError_t read_mma_status(int * status, bool clear);
 cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8, int TB,
                              int t, int32_t * wd);
 cudaError_t launch_block_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8,
