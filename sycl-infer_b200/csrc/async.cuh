@@ -50,6 +50,16 @@ __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint3
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t x) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(x) : "memory");
 }
+// 16-byte asynchronous copy global -> shared (no register staging), tracked in commit groups
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 // make generic-proxy shared-memory writes visible to the async proxy (tensor core, TMA)
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

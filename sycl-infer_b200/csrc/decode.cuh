@@ -41,6 +41,9 @@ struct GmemW {
     static __device__ __forceinline__ uint32_t ld16(const uint8_t * p) {
         return __ldg(reinterpret_cast<const uint16_t *>(p));
     }
+    static __device__ __forceinline__ int ld8s(const uint8_t * p) {
+        return (int)__ldg(reinterpret_cast<const int8_t *>(p));
+    }
     template <int N> static __device__ __forceinline__ void ld_a2(const uint8_t * p, uint32_t (&out)[N]) {
         const uintptr_t a = reinterpret_cast<uintptr_t>(p);
         const uint32_t * q = reinterpret_cast<const uint32_t *>(a & ~uintptr_t(3));
@@ -85,6 +88,11 @@ struct SmemW {
     static __device__ __forceinline__ uint4 ld128(const uint8_t * p) { return lds128(smem_u32(p)); }
     static __device__ __forceinline__ uint2 ld64(const uint8_t * p) { return lds64(smem_u32(p)); }
     static __device__ __forceinline__ uint32_t ld16(const uint8_t * p) { return lds16(smem_u32(p)); }
+    static __device__ __forceinline__ int ld8s(const uint8_t * p) {
+        int v;
+        asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)));
+        return v;
+    }
     template <int N> static __device__ __forceinline__ void ld_a2(const uint8_t * p, uint32_t (&out)[N]) {
         const uint32_t a = smem_u32(p);
         const uint32_t sh = (a & 2u) * 8;
