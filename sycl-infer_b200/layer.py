@@ -49,7 +49,10 @@ class DenseLayer:
         t, n, K = self.shapes[name]
         r0, r1 = self.rows[name]
         stride = out.shape[1]
+        # synthetic blocks have weights of magnitude ~3; alpha keeps every call's output O(1) so the
+        # chain stays inside the f16 range of the activation scales (a real model's weights do)
         seg = gemv_seg(w=self.w[name], type=t, K=K, n_rows=r1 - r0, x=x, x_stride=x.shape[1], act_up=act_up,
+                       alpha=1.0 / (3.0 * K ** 0.5),
                        out=out.view(-1)[col0 + r0:], out_stride=stride,
                        residual=None if residual is None else residual.view(-1)[col0 + r0:], x8=act[0],
                        xmeta=act[1], xsumq=act[2])

