@@ -133,13 +133,17 @@ def gpu_arm(args):
     from sycl_infer_b200.layer import DenseLayer
     be = pkg.make_cuda_backend(local)
     L = args.layers
-    layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1, rank=rank, world=world) for i in range(L)]
+    arena = None
+    if world > 1 and args.gather == "peer":
+        from sycl_infer_b200.sharding import PeerArena
+        arena = PeerArena(L * 65536 + 8192, rank, world)
+    layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1, rank=rank, world=world, arena=arena) for i in range(L)]
     hidden = layers[0].hidden
     xs = [torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)).cuda() for i in range(L)]
     attn = torch.from_numpy(pkg.synth.make_activation(1, layers[0].q_dim, 3)).cuda()
     for ly in layers:
         ly.attn.copy_(attn)
-    out = torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
+    out = arena.alloc(1, hidden) if arena is not None else torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
     full_bytes = pkg.synth.layer_weight_bytes("Q4_K_M") + 4 * (
         2 * hidden + layers[0].q_dim + 2 * layers[0].n_ff + (layers[0].q_dim + 2 * layers[0].kv_dim)
         + 2 * hidden + 2 * layers[0].n_ff)
@@ -153,7 +157,7 @@ def gpu_arm(args):
     # One CUDA graph per weight set: the engine this path plugs into replays a recorded graph
     # per decode step too, so a step is one graph launch (8 kernels), not 8 host launches.
     graphs = []
-    if world == 1 and not args.no_graph:
+    if (world == 1 or arena is not None) and not args.no_graph:
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
             for i in range(L):
@@ -265,7 +269,8 @@ def gpu_arm(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xu4/u6->int32, fp32 scales",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "launch": "cuda graph per step" if graphs else "host launches", "l2": f"inputs larger than L2: {L} rotating weight sets of 210 MB",
-                       "bytes_per_step": step_bytes, "parallelism": f"row-sharded x{world}" if world > 1 else "1 GPU",
+                       "bytes_per_step": step_bytes, "parallelism": (f"row-sharded x{world}, " + ("peer-store epilogue + flag barrier" if arena is not None
+                                                                 else "NCCL all-gather")) if world > 1 else "1 GPU",
                        "decode_tok_s_64_layers": 1e3 / (per_step * LAYERS_PER_TOKEN),
                        "pct_of_measured_hbm": 100.0 * gbs / peaks["hbm_gbs"], "pct_of_8TBs": 100.0 * gbs / 8000.0},
             "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
@@ -294,6 +299,8 @@ def main():
     ap.add_argument("--layers", type=int, default=8, help="distinct weight sets rotated through (L2 defeat)")
     ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: GEMV epilogue stores rows on every GPU + flag barrier (peer), or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels from the host instead of CUDA graphs")
     args = ap.parse_args()
     if args.impl == "reference":

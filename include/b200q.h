@@ -42,6 +42,7 @@ enum {
 };
 
 #define B200Q_MAX_SEGS 8
+#define B200Q_MAX_PEERS 7
 
 /* One GEMV output segment: field for field the reference's cpu_gemv_seg
  * (src/backend/cpu/cpu_types.h:68-86) / gemv_seg (src/backend/gpu/kernels/kernels.h:44-81)
@@ -88,6 +89,31 @@ int b200q_i8_gemm(void * stream, const b200q_seg * segs /*host*/, int n_segs, in
  * The segments' x8/xmeta/xsumq fields are ignored; the scratch arguments are used. */
 int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
                      int32_t * xsumq);
+
+/* ---- row-sharded calls across the GPUs of one box (new relative to the reference, which has no
+ * tensor parallelism: its only multi-device mode is the layer split, src/engine/engine.cpp:3505-3570).
+ * Every rank owns a contiguous slice of each weight's rows and all ranks need the whole output.
+ * Instead of a collective after the GEMV, the GEMV's epilogue stores each value into every rank's
+ * copy of the output buffer: plain peer stores over NVLink.  The output buffers must lie in one
+ * arena that every rank maps at the same layout (CUDA IPC / symmetric memory);
+ * out_delta[i] is the byte distance from this rank's mapping to peer i's. ---- */
+typedef struct b200q_peers {
+    int32_t n_peers; /* other ranks, 0..B200Q_MAX_PEERS */
+    int64_t out_delta[B200Q_MAX_PEERS];
+} b200q_peers;
+
+/* b200q_quant_gemv whose outputs also land on the peers. */
+int b200q_quant_gemv_scatter(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8,
+                             float * xmeta, int32_t * xsumq, const b200q_peers * peers /*host*/);
+
+/* Cross-GPU barrier that closes a scattered call: tells every peer "my stores of step `seq` are
+ * done" (flag word `rank` of the peer's flag array) and waits until every peer has said the same
+ * here.  flags[p] (host array of `world` device pointers) is rank p's flag array of `world` words
+ * (plus a private counter at word 32) as mapped on this GPU.  seq must increase by one per barrier;
+ * seq = 0 lets the kernel number the barriers itself from that counter, which is what a recorded
+ * launch sequence (CUDA graph) needs since its arguments are frozen.  The wait is bounded (about a
+ * second); a peer that never arrives sets the device status word instead of hanging the GPU. */
+int b200q_peer_barrier(void * stream, uint32_t * const * flags /*host*/, int world, int rank, uint32_t seq);
 
 /* ---- routed mixture-of-experts (free launchers in the reference, src/backend/gpu/kernels/kernels.h:595-792,
  * host twins src/backend/cpu/cpu_types.h:195-211).  Expert e's weights are the plane

@@ -123,6 +123,17 @@ class cuda_backend:
         s0 = segs[0] if not isinstance(segs, gemv_seg) else segs
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
+    def quant_gemv_scatter(self, segs, TB, peers):
+        """quant_gemv whose outputs are also stored into the peers' copies of the output arena."""
+        arr, n = _pack(segs)
+        s0 = segs[0]
+        self.lib.check(self.lib.quant_gemv_scatter(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq),
+                                                   C.byref(peers)))
+
+    def peer_barrier(self, flag_ptrs, world, rank, seq):
+        """Signal every peer that this rank's stores are done and wait for theirs (bounded)."""
+        self.lib.check(self.lib.peer_barrier(self._s(), flag_ptrs, world, rank, seq))
+
     def quant_gemv_static(self, segs):
         """One-token quant_gemv on the library's built-in scratch: for hosts that cannot
         allocate the activation scratch themselves (K <= 32768; calls must not overlap)."""

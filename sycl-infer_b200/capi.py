@@ -20,6 +20,11 @@ class B200QError(RuntimeError):
         self.code = code
 
 
+class Peers(C.Structure):
+    """struct b200q_peers."""
+    _fields_ = [("n_peers", C.c_int32), ("out_delta", C.c_int64 * 7)]
+
+
 class Seg(C.Structure):
     """struct b200q_seg, field for field."""
     _fields_ = [("w", _vp), ("type", C.c_uint32), ("K", C.c_int32), ("n_rows", C.c_int32), ("x", _vp),
@@ -35,6 +40,8 @@ _SIGS = {
     "b200q_i8_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_gemm": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int]),
     "b200q_quant_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_quant_gemv_scatter": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(Peers)]),
+    "b200q_peer_barrier": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, C.c_uint32]),
     "b200q_moe_route": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
     "b200q_moe_csr": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "b200q_moe_gate_up": (C.c_int, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp,

@@ -203,6 +203,61 @@ int b200q_quant_gemv(void * stream, const b200q_seg * segs, int n_segs, int TB, 
     return B200Q_OK;
 }
 
+int b200q_quant_gemv_scatter(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
+                             int32_t * xsumq, const b200q_peers * peers) {
+    if (!x8 || !xmeta || !xsumq || !peers) {
+        set_error("b200q_quant_gemv_scatter: scratch and peers must be non-null");
+        return B200Q_EINVAL;
+    }
+    if (peers->n_peers < 0 || peers->n_peers > B200Q_MAX_PEERS) {
+        set_error("b200q_quant_gemv_scatter: n_peers must be 0..%d (got %d)", B200Q_MAX_PEERS, peers->n_peers);
+        return B200Q_EINVAL;
+    }
+    CallDev c;
+    const int rc = build_call(segs, n_segs, TB, x8, xmeta, xsumq, c);
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    const b200q_seg & s0 = segs[0];
+    if (!s0.x || s0.x_stride < s0.K) {
+        set_error("b200q_quant_gemv_scatter: segs[0].x must be non-null with x_stride >= K");
+        return B200Q_EINVAL;
+    }
+    for (int i = 1; i < n_segs; i++) {
+        if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
+            set_error("b200q_quant_gemv_scatter: segment %d does not share the call's activation", i);
+            return B200Q_EINVAL;
+        }
+    }
+    c.n_peers = peers->n_peers;
+    for (int i = 0; i < peers->n_peers; i++) {
+        if (peers->out_delta[i] & 3) {
+            set_error("b200q_quant_gemv_scatter: out_delta[%d] is not a multiple of 4 bytes", i);
+            return B200Q_EINVAL;
+        }
+        c.peer_delta[i] = peers->out_delta[i];
+    }
+    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
+                            s0.K, true));
+    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));
+    return B200Q_OK;
+}
+
+int b200q_peer_barrier(void * stream, uint32_t * const * flags, int world, int rank, uint32_t seq) {
+    if (!flags || world < 1 || world > B200Q_MAX_PEERS + 1 || rank < 0 || rank >= world) {
+        set_error("b200q_peer_barrier: bad world/rank (%d/%d) or null flags", rank, world);
+        return B200Q_EINVAL;
+    }
+    for (int i = 0; i < world; i++) {
+        if (!flags[i]) {
+            set_error("b200q_peer_barrier: flags[%d] is null", i);
+            return B200Q_EINVAL;
+        }
+    }
+    B200Q_CUDA_OK(launch_peer_barrier((cudaStream_t)stream, flags, world, rank, seq));
+    return B200Q_OK;
+}
+
 int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int n_rows, const int8_t * x8, int TB,
                         int t, int32_t * wd) {
     if (!w || !x8 || !wd || !type_ok(type)) {
@@ -330,6 +385,9 @@ int b200q_device_status(int * status, int clear) {
     int mma = 0;
     B200Q_CUDA_OK(read_mma_status(&mma, clear != 0));
     *status = *status ? *status : mma;
+    int peer = 0;
+    B200Q_CUDA_OK(read_peer_status(&peer, clear != 0));
+    *status = *status ? *status : peer;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

@@ -120,6 +120,19 @@ struct CallDev {
     int32_t K;
     int32_t TB;
     int32_t total_rows;
+    // row-sharded calls: every output value is also stored into the same place of n_peers other
+    // GPUs' mappings of the shared output arena (plain stores over NVLink, no multicast)
+    int32_t n_peers;
+    int64_t peer_delta[B200Q_MAX_PEERS];
 };
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void store_out(const CallDev & c, float * p, float v) {
+    *p = v;
+    for (int i = 0; i < c.n_peers; i++) {
+        *reinterpret_cast<float *>(reinterpret_cast<char *>(p) + c.peer_delta[i]) = v;
+    }
+}
+#endif
 
 } // namespace b200q

@@ -389,7 +389,7 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
                     if (sg.residual) {
                         v += sg.residual[o];
                     }
-                    sg.out[o] = v;
+                    store_out(a.c, &sg.out[o], v);
                 }
             }
         }

@@ -71,7 +71,7 @@ template <int TT> __global__ void __launch_bounds__(256) gemv_rows_kernel(const 
             if (sg.residual) {
                 v += sg.residual[o];
             }
-            sg.out[o] = v;
+            store_out(c, &sg.out[o], v);
         }
     }
 }

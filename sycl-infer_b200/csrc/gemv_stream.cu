@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                 if (sg.residual) {
                     v += sg.residual[o];
                 }
-                sg.out[o] = v;
+                store_out(a.c, &sg.out[o], v);
             }
         }
     }

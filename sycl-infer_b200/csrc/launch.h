@@ -29,6 +29,9 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
 cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
                               int acc_stride, float * out, int out_stride);
 
+cudaError_t launch_peer_barrier(cudaStream_t s, uint32_t * const * flags, int world, int rank, uint32_t seq);
+cudaError_t read_peer_status(int * status, bool clear);
+
 // shared by the C-ABI translation units: validate + flatten a call, pick the GEMV kernel
 int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
                const int32_t * xsumq, CallDev & c);

@@ -18,8 +18,11 @@ from .sharding import gather_rows, shard_rows
 
 class DenseLayer:
     def __init__(self, be, mix="Q4_K_M", seed=0, TB=1, rank=0, world=1, hidden=5120, n_head=40, n_kv=8,
-                 head_dim=128, n_ff=17408, group=None):
+                 head_dim=128, n_ff=17408, group=None, arena=None):
+        """`arena` (sharding.PeerArena): outputs live in memory every rank maps, each call's GEMV
+        stores its rows on all ranks and a flag barrier replaces the all-gather."""
         self.be, self.TB, self.rank, self.world, self.group = be, TB, rank, world, group
+        self.arena = arena if world > 1 else None
         self.hidden, self.n_ff, self.q_dim, self.kv_dim = hidden, n_ff, n_head * head_dim, n_kv * head_dim
         dev = be.device
         self.shapes = {n: (t, r, k) for n, t, r, k in
@@ -33,10 +36,14 @@ class DenseLayer:
             self.w[name] = torch.from_numpy(full[r0 * rb:r1 * rb].copy()).to(dev)
             self.rows[name] = (r0, r1)
         f32 = dict(dtype=torch.float32, device=dev)
-        self.qkv = torch.zeros(TB, self.q_dim + 2 * self.kv_dim, **f32)
+        new = (lambda *sh: self.arena.alloc(*sh)) if self.arena else (lambda *sh: torch.zeros(*sh, **f32))
+        self.qkv = new(TB, self.q_dim + 2 * self.kv_dim)
         self.attn = torch.zeros(TB, self.q_dim, **f32)
-        self.o_out = torch.zeros(TB, hidden, **f32)
-        self.gu = torch.zeros(TB, 2 * n_ff, **f32)
+        self.o_out = new(TB, hidden)
+        self.gu = new(TB, 2 * n_ff)
+        self.out = new(TB, hidden)  # the layer's output when the caller passes none
+        if self.arena:
+            self._peers, self._flags = self.arena.peers(), self.arena.flag_ptrs()
         self.act_h = alloc_act(TB, hidden, dev)
         self.act_q = alloc_act(TB, self.q_dim, dev)
         self.act_f = alloc_act(TB, n_ff, dev)
@@ -73,6 +80,10 @@ class DenseLayer:
 
     def forward(self, x, out, calls=None):
         for segs, gathers in (calls or self.calls(x, out)):
+            if self.arena:
+                self.be.quant_gemv_scatter(segs, self.TB, self._peers)
+                self.be.peer_barrier(self._flags, self.world, self.rank, 0)  # device-numbered: graph-safe
+                continue
             self.be.quant_gemv(segs, self.TB)
             if self.world > 1:
                 for buf, n, col0 in gathers:

@@ -134,3 +134,47 @@ def run_layer_split(ranges: List[LayerRange], rank: int, x: torch.Tensor, run_la
         if i + 1 < len(ranges):
             handoff_x(x, i, i + 1, rank, group)
     return x
+
+
+class PeerArena:
+    """One fp32 output arena that every rank of the group maps at the same layout (torch
+    symmetric memory: CUDA IPC / fabric handles underneath), plus the flag words of the
+    cross-GPU barrier.  Buffers carved from it can be the `out` of a scattered call: the GEMV
+    epilogue stores each value into every rank's copy, so no collective follows the GEMV."""
+
+    def __init__(self, n_floats: int, rank: int, world: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.rank, self.world = rank, world
+        self.buf = symm_mem.empty(n_floats + 64, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.used = 64  # the first 64 words are the barrier flags (one word per source rank)
+        self.seq = 0
+        dist.barrier(group)
+
+    def alloc(self, *shape):
+        n = 1
+        for d in shape:
+            n *= d
+        n_al = -(-n // 64) * 64
+        t = self.buf[self.used:self.used + n].view(*shape)
+        self.used += n_al
+        if self.used > self.buf.numel():
+            raise MemoryError("PeerArena exhausted")
+        return t
+
+    def peers(self):
+        """b200q_peers for this rank: byte distances to the other ranks' mappings."""
+        from .capi import Peers
+        p = Peers()
+        others = [r for r in range(self.world) if r != self.rank]
+        p.n_peers = len(others)
+        for i, r in enumerate(others):
+            p.out_delta[i] = self.ptrs[r] - self.ptrs[self.rank]
+        return p
+
+    def flag_ptrs(self):
+        import ctypes as C
+        return (C.c_void_p * self.world)(*self.ptrs)  # flags live at the start of every mapping

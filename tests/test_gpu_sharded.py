@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-def _worker(rank, world, port, TB, ret):
+def _worker(rank, world, port, TB, ret, fused=False):
     import sys
     import torch.distributed as dist
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -27,20 +27,27 @@ def _worker(rank, world, port, TB, ret):
         x = torch.from_numpy(pkg.synth.make_activation(TB, 1024, 5)).cuda()
         attn = torch.from_numpy(pkg.synth.make_activation(TB, 1024, 6)).cuda()
         outs = []
+        arena = None
+        if fused:
+            from sycl_infer_b200.sharding import PeerArena
+            arena = PeerArena(TB * 16384, rank, world)
         for r, w in ((rank, world), (0, 1)):
-            ly = DenseLayer(be, "Q4_K_M", seed=9, TB=TB, rank=r, world=w, **kw)
+            ly = DenseLayer(be, "Q4_K_M", seed=9, TB=TB, rank=r, world=w, arena=arena if w > 1 else None, **kw)
             ly.attn.copy_(attn)
-            out = torch.zeros(TB, 1024, device="cuda")
-            ly.forward(x, out)
+            out = ly.out if (fused and w > 1) else torch.zeros(TB, 1024, device="cuda")
+            for _ in range(3):  # several steps: the flag sequence and buffer reuse across steps
+                ly.forward(x, out)
             torch.cuda.synchronize()
             outs.append((out.cpu().numpy(), ly.qkv.cpu().numpy(), ly.gu.cpu().numpy()))
+        assert be.device_status() == 0
         ret[rank] = outs
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("TB", [1, 3])
-def test_row_sharded_layer_matches_single_gpu(TB):
+def test_row_sharded_layer_matches_single_gpu(TB, fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -48,7 +55,7 @@ def test_row_sharded_layer_matches_single_gpu(TB):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, port, TB, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, TB, ret, fused), nprocs=2, join=True)
     for rank in (0, 1):
         (o2, qkv2, gu2), (o1, qkv1, gu1) = ret[rank]
         # q|k|v come straight from the same quantized input: only the fp32 summation order differs
@@ -57,3 +64,25 @@ def test_row_sharded_layer_matches_single_gpu(TB):
         # an int8 code, so these agree to quantization accuracy, not to fp32 rounding
         for a, b in ((gu2, gu1), (o2, o1)):
             assert np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b))
+
+
+def test_peer_barrier_times_out_instead_of_hanging(be):
+    """A peer that never signals: the bounded wait gives up after about a second and reports
+    through the device status word; the context stays usable.  The 'peer' is a second flag
+    array on this same GPU that nothing ever writes to this rank's slot of."""
+    import ctypes as C
+    import time
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")
+    other = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags = (C.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    t0 = time.time()
+    be.peer_barrier(flags, 2, 0, 1)
+    be.synchronize()
+    assert time.time() - t0 < 10
+    assert int(other[0]) == 1          # this rank's signal landed at the peer
+    assert be.device_status() == 4     # B200Q_ETIMEOUT, and the word is cleared by the read
+    assert be.device_status() == 0
+    mine[1] = 1                        # the peer "arrives": the same barrier now passes
+    be.peer_barrier(flags, 2, 0, 1)
+    be.synchronize()
+    assert be.device_status() == 0
