@@ -15,9 +15,10 @@
 //               block into the K-major core-matrix layout the MMA reads, copy the tokens'
 //               int8 group the same way, publish the per-row / per-token fp32 factors
 //   warp 12     one thread issues the MMAs and commits them to mbarriers; it owns TMEM
-// A four-deep ring (shared tiles + factor arrays + TMEM accumulator) links the roles with
-// three mbarrier arrays: full (producers -> MMA), acc_full (MMA -> epilogue), acc_empty
-// (epilogue -> producers).  All waits are bounded; TMEM is always released before exit.
+// Operands travel in slots of eight steps (one superblock): one producer/consumer handshake per
+// slot.  mbarrier arrays: full (producers -> MMA) and done (epilogue -> producers) per slot,
+// acc_full (MMA -> epilogue) and acc_empty (epilogue -> MMA) per tensor-memory accumulator, of
+// which all 512 columns are used as a ring.  All waits are bounded; TMEM is always released.
 #include <cstdlib>
 
 #include "async.cuh"
@@ -29,15 +30,17 @@ namespace b200q {
 __device__ int g_mma_status = 0;
 
 constexpr int kTileM = 128;
-constexpr int kRing = 4;   // tensor-memory accumulators in flight
+// tensor-memory accumulators in flight: all 512 columns, at most 16 (the MMA -> epilogue -> MMA
+// round trip is latency-bound, so the deeper the ring the more steps overlap)
+__host__ __device__ constexpr int acc_ring(int NT) {
+    return 512 / NT < 16 ? 512 / NT : 16;
+}
 constexpr int kHdr = 512;  // bytes of mbarriers + the TMEM address at the start of shared memory
 // Role mix per instantiation <NT, EW, PG>: EW epilogue warpgroups (each covers all 128 TMEM
 // lanes and NT/EW token columns), PG producer groups of 128 threads that take the steps in
 // turn (step i belongs to group i % PG) so their global/shared round trips overlap.
+constexpr int kMaxDepth = 4; // operand slots of eight steps each; as many as shared memory holds
 template <int NT, int EW, int PG> struct Roles {
-    // operand/factor slots in shared memory: deeper than the accumulator ring so producers run
-    // many steps ahead of the epilogue and a step never waits on a global-memory round trip
-    static constexpr int kDepth = 8;
     static constexpr int kEpiWarps = 4 * EW, kProdWarps = 4 * PG;
     static constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 1);
 };
@@ -47,6 +50,7 @@ struct MmaArgs {
     int32_t tiles_m[B200Q_MAX_SEGS]; // exclusive prefix of 128-row tiles per segment
     int32_t n_tiles_m, n_tiles_t;
     int32_t raw_bytes; // per-thread staging bytes for one raw superblock (16-byte units)
+    int32_t depth;     // operand slots in the shared-memory ring
     int32_t lbo, sbo; // operand descriptor strides (bytes): K-adjacent core matrices, 8-row groups
 };
 
@@ -114,145 +118,209 @@ __device__ __forceinline__ void unpack_step(const uint8_t * sb, int s, uint32_t 
     }
 }
 
-// Shared-memory ring slot: A [128 rows][32 B] and B [NT tokens][32 B] as core matrices
-// (8 rows x 16 B = 128 B contiguous; the two K halves 128 B apart, 8-row groups 256 B apart),
-// then rowA[128], rowB[128], tokA[NT], tokB[NT], tokC[NT] as fp32.
+// Shared-memory ring slot = kSlotSteps consecutive MMA steps (one superblock; half a Q6_K
+// superblock).  Per step s: A[s] = [128 rows][32 B]; per activation group a B buffer = [NT
+// tokens][32 B]; both as core matrices (8 rows x 16 B = 128 B contiguous; the two K halves 128 B
+// apart, 8-row groups 256 B apart).  Then per step the fp32 factors rowA[128], rowB[128],
+// tokA[NT], tokB[NT], tokC[NT].
+constexpr int kSlotSteps = 8;
 template <int NT> struct Slot {
-    static constexpr int A = 0, B = kTileM * 32, ROWA = B + NT * 32, ROWB = ROWA + kTileM * 4,
-                         TOKA = ROWB + kTileM * 4, TOKB = TOKA + NT * 4, TOKC = TOKB + NT * 4,
-                         BYTES = TOKC + NT * 4;
+    static constexpr int A = 0, B = kSlotSteps * kTileM * 32, ROWA = B + kSlotSteps * NT * 32,
+                         ROWB = ROWA + kSlotSteps * kTileM * 4, TOKA = ROWB + kSlotSteps * kTileM * 4,
+                         TOKB = TOKA + kSlotSteps * NT * 4, TOKC = TOKB + kSlotSteps * NT * 4,
+                         BYTES = TOKC + kSlotSteps * NT * 4;
 };
 __device__ __forceinline__ uint32_t core_off(int row, int khalf) {
     return (uint32_t)((row >> 3) * 256 + khalf * 128 + (row & 7) * 16);
 }
 
 struct Bars {
-    uint32_t full, done, acc_full, acc_empty; // [depth] producers->MMA, [depth] epilogue->producers, [4], [4]
+    uint32_t full, done, acc_full, acc_empty; // [slots] producers->MMA, [slots] epilogue->producers, [acc], [acc]
     int depth;
 };
 
-// ---- one tile, one role each ---------------------------------------------------------------
-// Producer: software-pipelined so that no step waits on a global-memory round trip.
-//   * the thread's own weight row is staged superblock by superblock into a private region of
-//     shared memory with 16-byte cp.async copies (double buffered: superblock b+1 is in flight
-//     while the steps of b are unpacked from shared memory);
-//   * the tokens' int8 chunks of step s+1 are cp.async'ed straight into the operand slot of
-//     step s+1 while step s is unpacked; the per-token factors of step s+1 sit in registers.
-
-struct TokPrefetch {
-    float sx;
-    int2 xs;
-};
-
-template <int TYPE, int NT>
-__device__ __forceinline__ void issue_tokens(const MmaArgs & a, int b, int s, int t0, int r, uint32_t base,
-                                             TokPrefetch & tp) {
-    using F = StepFmt<TYPE>;
-    const int TB = a.c.TB, G = 8 * b + (F::NS == 16 ? s >> 1 : s);
-    for (int c = r; c < 2 * NT; c += 128) {
-        const int t = c >> 1, h = c & 1;
-        const uint32_t dst = base + Slot<NT>::B + core_off(t, h);
-        if (t0 + t < TB) {
-            cp_async16(dst, a.c.x8 + ((size_t)G * TB + t0 + t) * 32 + 16 * h);
-        } else {
-            sts128(dst, 0, 0, 0, 0);
-        }
-    }
-    tp.sx = 0.f;
-    tp.xs = make_int2(0, 0);
-    if (r < NT && t0 + r < TB) {
-        const size_t gi = (size_t)G * TB + t0 + r;
-        tp.sx = __ldg(a.c.xmeta + 2 * gi);
-        tp.xs = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
-    }
+// Q6_K has 16 steps per superblock over 8 activation groups: slot h (0/1) of a superblock holds
+// steps 8h..8h+7; step s there is scale group 8h+s, activation group 4h + (s>>1), half s&1.
+template <int TYPE> __device__ __forceinline__ int step_group(int slot_in_sb, int s) {
+    return StepFmt<TYPE>::NS == 16 ? 4 * slot_in_sb + (s >> 1) : s;
+}
+template <int TYPE> __device__ __forceinline__ int step_bbuf(int s) { // B buffer of step s inside its slot
+    return StepFmt<TYPE>::NS == 16 ? s >> 1 : s;
 }
 
+// One row's eight steps into the slot.  Q4_K/Q5_K take a whole-superblock path: the header is
+// decoded once (the eight 6-bit scale/min pairs with 32-bit operations) and every 32 bytes of qs
+// yield two steps (low and high nibbles); other types go step by step.
+template <int TYPE, int NT>
+__device__ __forceinline__ void unpack_slot(const uint8_t * sb, int h, int r, bool row_ok, uint32_t base) {
+    using F = StepFmt<TYPE>;
+    const uint32_t a0 = base + Slot<NT>::A, ra = base + Slot<NT>::ROWA + 4 * r, rb = base + Slot<NT>::ROWB + 4 * r;
+    if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+        uint4 hdr = make_uint4(0, 0, 0, 0);
+        if (row_ok) {
+            hdr = SmemW::ld128(sb);
+        }
+        const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
+        // (scale, min) bytes of groups 0-3 and 4-7 (get_scale_min_k4, src/common/quant.h:136-144 of the reference)
+        const uint32_t sc[2] = {hdr.y & 0x3F3F3F3Fu, (hdr.w & 0x0F0F0F0Fu) | ((hdr.y & 0xC0C0C0C0u) >> 2)};
+        const uint32_t mn[2] = {hdr.z & 0x3F3F3F3Fu, ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z & 0xC0C0C0C0u) >> 2)};
+        uint32_t hq[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (TYPE == kQ5_K && row_ok) {
+            const uint4 h0 = SmemW::ld128(sb + 16), h1 = SmemW::ld128(sb + 32);
+            hq[0] = h0.x, hq[1] = h0.y, hq[2] = h0.z, hq[3] = h0.w, hq[4] = h1.x, hq[5] = h1.y, hq[6] = h1.z, hq[7] = h1.w;
+        }
+#pragma unroll
+        for (int pr = 0; pr < 4; pr++) { // pair pr: steps 2pr (low nibbles) and 2pr+1 (high nibbles)
+            uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
+            if (row_ok) {
+                const uint8_t * qs = sb + (TYPE == kQ4_K ? 16 : 48) + 32 * pr;
+                q0 = SmemW::ld128(qs);
+                q1 = SmemW::ld128(qs + 16);
+            }
+            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            uint32_t lo[8], hi[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                lo[k] = q[k] & 0x0F0F0F0Fu;
+                hi[k] = (q[k] >> 4) & 0x0F0F0F0Fu;
+                if (TYPE == kQ5_K) { // bit g of qh[i] is the fifth bit of element i of group g
+                    lo[k] |= ((hq[k] >> (2 * pr)) & 0x01010101u) << 4;
+                    hi[k] |= ((hq[k] >> (2 * pr + 1)) & 0x01010101u) << 4;
+                }
+            }
+            const uint32_t al = a0 + (uint32_t)((2 * pr) * kTileM * 32), ah = al + kTileM * 32;
+            sts128(al + core_off(r, 0), lo[0], lo[1], lo[2], lo[3]);
+            sts128(al + core_off(r, 1), lo[4], lo[5], lo[6], lo[7]);
+            sts128(ah + core_off(r, 0), hi[0], hi[1], hi[2], hi[3]);
+            sts128(ah + core_off(r, 1), hi[4], hi[5], hi[6], hi[7]);
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int g = 2 * pr + e;
+                const float scf = (float)((sc[g >> 2] >> (8 * (g & 3))) & 0xFF);
+                const float mnf = (float)((mn[g >> 2] >> (8 * (g & 3))) & 0xFF);
+                sts32(ra + 4 * g * kTileM, __float_as_uint(d * scf));
+                sts32(rb + 4 * g * kTileM, __float_as_uint(dmin * mnf));
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int st = 0; st < kSlotSteps; st++) {
+            uint32_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            float rowA = 0.f, rowB = 0.f;
+            if (row_ok) {
+                unpack_step<TYPE, SmemW>(sb, h * kSlotSteps + st, o, rowA, rowB);
+            }
+            const uint32_t as = a0 + (uint32_t)(st * kTileM * 32);
+            sts128(as + core_off(r, 0), o[0], o[1], o[2], o[3]);
+            sts128(as + core_off(r, 1), o[4], o[5], o[6], o[7]);
+            sts32(ra + 4 * st * kTileM, __float_as_uint(rowA));
+        }
+    }
+    (void)F::NS;
+}
+
+// ---- one tile, one role each ---------------------------------------------------------------
+// Producer group: 128 threads, thread r = weight row r of the tile.  For every slot it owns
+// (slots are dealt to the PG groups in turn) it
+//   * has the row's raw superblock in a private shared-memory buffer (16-byte cp.async copies,
+//     double buffered: the next superblock it needs is in flight while this one is unpacked),
+//   * copies the tokens' int8 groups straight into the slot's B buffers with cp.async,
+//   * unpacks the eight steps' codes into A and publishes the per-row and per-token factors.
 template <int TYPE, int NT, int PG>
 __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                             uint32_t raw_all, int pt, const Bars & bars, uint32_t & git) {
+                                             uint32_t raw_all, int pt, const Bars & bars, uint32_t & gslot) {
     using F = StepFmt<TYPE>;
-    constexpr int SB = Fmt<TYPE>::SB;
-    const int grp = pt >> 7, r = pt & 127; // producer group, weight row this thread unpacks
-    const int nb = a.c.K >> 8, RB = a.raw_bytes;
+    constexpr int SB = Fmt<TYPE>::SB, SPS = F::NS / kSlotSteps; // slots per superblock
+    constexpr int NB = F::NS == 16 ? 4 : 8;                     // activation groups per slot
+    const int grp = pt >> 7, r = pt & 127;
+    const int nb = a.c.K >> 8, RB = a.raw_bytes, TB = a.c.TB;
     const uint32_t D = (uint32_t)bars.depth;
     const bool row_ok = row0 + r < sg.n_rows;
     const uint8_t * wrow = sg.w + (size_t)(row0 + r) * nb * SB;
-    const uint32_t raw = raw_all + (uint32_t)(pt * 2 * RB);
+    // staging is buffer-major: thread pt's buffer `buf` sits at (buf * threads + pt) * RB, so the
+    // threads of a warp are RB bytes apart (an odd number of 16-byte chunks: no bank conflicts)
+    const int BS = 128 * PG * RB;
+    const uint32_t raw = raw_all + (uint32_t)(pt * RB);
     uint8_t * raw_gen = nullptr; // generic pointer to the same bytes, for the decode helpers
     {
         extern __shared__ __align__(128) uint8_t smem_raw[];
         raw_gen = smem_raw + (raw - smem_u32(smem_raw));
     }
-    auto stage_sb = [&](int b) { // this row's superblock b -> raw[b & 1], 16-byte aligned chunks
+    auto stage_sb = [&](int b, int buf) { // this row's superblock b -> raw[buf], 16-byte aligned chunks
         if (row_ok && b < nb) {
             const uintptr_t A = reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB);
             const uintptr_t A0 = A & ~uintptr_t(15);
             const int n = (int)((A + SB + 15 - A0) >> 4);
             for (int i = 0; i < n; i++) {
-                cp_async16(raw + (uint32_t)((b & 1) * RB + 16 * i), reinterpret_cast<const void *>(A0 + 16 * i));
+                cp_async16(raw + (uint32_t)(buf * BS + 16 * i), reinterpret_cast<const void *>(A0 + 16 * i));
             }
         }
         cp_async_commit();
     };
-    const int steps = nb * F::NS;
-    const uint32_t git0 = git;
-    git += (uint32_t)steps; // every role advances the shared step counter by the tile's steps
-    // this group's steps: i = first, first + PG, ...  (first chosen so that (git0 + i) % PG == grp)
-    int i = (int)((grp + PG - (git0 % PG)) % PG);
-    if (i >= steps) {
+    const int slots = nb * SPS;
+    const uint32_t g0 = gslot;
+    gslot += (uint32_t)slots; // every role advances the shared slot counter by the tile's slots
+    int i = (int)((grp + PG - (g0 % PG)) % PG); // this group's first slot of the tile
+    if (i >= slots) {
         return true;
     }
-    int staged = i / F::NS; // highest superblock staged so far
-    stage_sb(staged);
-    {
-        const uint32_t g = git0 + i;
+    int have = i / SPS, buf = 0; // superblock held in raw[buf]
+    stage_sb(have, buf);
+    for (; i < slots; i += PG) {
+        const int b = i / SPS, h = i - b * SPS; // superblock, slot within it
+        const uint32_t g = g0 + i;
+        const uint32_t base = ring + (g % D) * Slot<NT>::BYTES;
+        if (b != have) { // prefetched while the previous slot of this group was unpacked
+            have = b;
+            buf ^= 1;
+        }
         if (!mbar_wait(bars.done + 8 * (g % D), ((g / D) & 1) ^ 1, &g_mma_status)) {
             cp_async_wait<0>();
             return false;
         }
-    }
-    TokPrefetch tp;
-    issue_tokens<TYPE, NT>(a, i / F::NS, i % F::NS, t0, r, ring + ((git0 + i) % D) * Slot<NT>::BYTES, tp);
-    cp_async_commit();
-    for (; i < steps; i += PG) {
-        const int b = i / F::NS, s = i - b * F::NS;
-        const uint32_t g = git0 + i;
-        const uint32_t base = ring + (g % D) * Slot<NT>::BYTES;
-        const TokPrefetch cur = tp;
-        // keep the superblock after the one in use in flight (one commit group per step, maybe empty)
-        if (staged < b + 1) {
-            staged = b + 1;
-            stage_sb(staged);
+        // tokens: the int8 groups this slot's steps meet, straight into the B buffers
+        for (int c = r; c < NB * NT * 2; c += 128) {
+            const int gi = c / (2 * NT), rem = c - gi * 2 * NT, t = rem >> 1, hh = rem & 1;
+            const int G = 8 * b + (F::NS == 16 ? 4 * h + gi : gi);
+            const uint32_t dst = base + Slot<NT>::B + (uint32_t)(gi * NT * 32) + core_off(t, hh);
+            if (t0 + t < TB) {
+                cp_async16(dst, a.c.x8 + ((size_t)G * TB + t0 + t) * 32 + 16 * hh);
+            } else {
+                sts128(dst, 0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+        // prefetch the superblock of this group's next slot (one commit group either way)
+        const int inext = i + PG, bnext = inext / SPS;
+        if (inext < slots && bnext != b) {
+            stage_sb(bnext, buf ^ 1);
         } else {
             cp_async_commit();
         }
-        const int i1 = i + PG;
-        if (i1 < steps) { // this group's next step: its tokens go into its slot once that is released
-            const uint32_t g1 = git0 + i1;
-            if (!mbar_wait(bars.done + 8 * (g1 % D), ((g1 / D) & 1) ^ 1, &g_mma_status)) {
-                cp_async_wait<0>();
-                return false;
+        // per-token factors of the eight steps
+        for (int c = r; c < kSlotSteps * NT; c += 128) {
+            const int st = c / NT, t = c - st * NT;
+            float tokA = 0.f, tokB = 0.f, tokC = 0.f;
+            if (t0 + t < TB) {
+                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
+                tokA = __ldg(a.c.xmeta + 2 * gi);
+                const int2 xs = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
+                tokB = tokA * (float)(xs.x + xs.y);
+                tokC = (float)(32 * ((st & 1) ? xs.y : xs.x));
             }
-            issue_tokens<TYPE, NT>(a, i1 / F::NS, i1 % F::NS, t0, r, ring + (g1 % D) * Slot<NT>::BYTES, tp);
+            sts32(base + Slot<NT>::TOKA + 4 * c, __float_as_uint(tokA));
+            if (F::HAS_MIN) {
+                sts32(base + Slot<NT>::TOKB + 4 * c, __float_as_uint(tokB));
+            }
+            if (F::HAS_C) {
+                sts32(base + Slot<NT>::TOKC + 4 * c, __float_as_uint(tokC));
+            }
         }
-        cp_async_commit();
-        // groups in flight, oldest first: ... [superblock b] [tokens i] | [superblock b+1 or empty] [tokens i+PG]
+        // groups in flight, oldest first: [superblock b] | [tokens] [next superblock or empty]
         cp_async_wait<2>();
-        uint32_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        float rowA = 0.f, rowB = 0.f;
-        if (row_ok) {
-            const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB) & 15);
-            unpack_step<TYPE, SmemW>(raw_gen + (b & 1) * RB + mis, s, o, rowA, rowB);
-        }
-        sts128(base + Slot<NT>::A + core_off(r, 0), o[0], o[1], o[2], o[3]);
-        sts128(base + Slot<NT>::A + core_off(r, 1), o[4], o[5], o[6], o[7]);
-        sts32(base + Slot<NT>::ROWA + 4 * r, __float_as_uint(rowA));
-        sts32(base + Slot<NT>::ROWB + 4 * r, __float_as_uint(rowB));
-        if (r < NT) {
-            sts32(base + Slot<NT>::TOKA + 4 * r, __float_as_uint(cur.sx));
-            sts32(base + Slot<NT>::TOKB + 4 * r, __float_as_uint(cur.sx * (float)(cur.xs.x + cur.xs.y)));
-            sts32(base + Slot<NT>::TOKC + 4 * r, __float_as_uint((float)(32 * ((s & 1) ? cur.xs.y : cur.xs.x))));
-        }
+        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB) & 15);
+        unpack_slot<TYPE, NT>(raw_gen + buf * BS + mis, h, r, row_ok, base);
+        cp_async_wait<1>();  // the tokens have landed; the prefetched superblock may still be in flight
         fence_proxy_async(); // the tensor core reads A and B through the async proxy
         mbar_arrive(bars.full + 8 * (g % D));
     }
@@ -262,24 +330,30 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
 
 template <int TYPE, int NT>
 __device__ __forceinline__ bool mma_tile(const MmaArgs & a, uint32_t ring, uint32_t tmem, const Bars & bars,
-                                         uint32_t & git) {
+                                         uint32_t & gslot, uint32_t & git) {
     using F = StepFmt<TYPE>;
     const uint32_t idesc = idesc_i8(F::A_SIGNED, 1, kTileM, NT);
-    const int steps = (a.c.K >> 8) * F::NS;
+    const int slots = (a.c.K >> 8) * (F::NS / kSlotSteps);
     const uint32_t D = (uint32_t)bars.depth;
-    for (int i = 0; i < steps; i++, git++) {
-        const uint32_t slot = git % D, acc = git % kRing;
-        // operands of this step written, and the accumulator it overwrites drained by the epilogue
-        if (!mbar_wait(bars.full + 8 * slot, (git / D) & 1, &g_mma_status) ||
-            !mbar_wait(bars.acc_empty + 8 * acc, ((git / kRing) & 1) ^ 1, &g_mma_status)) {
+    for (int i = 0; i < slots; i++, gslot++) {
+        const uint32_t slot = gslot % D;
+        if (!mbar_wait(bars.full + 8 * slot, (gslot / D) & 1, &g_mma_status)) {
             return false;
         }
-        tc_fence_after();
         const uint32_t base = ring + slot * Slot<NT>::BYTES;
-        const uint64_t ad = smem_desc_kmajor(base + Slot<NT>::A, a.lbo, a.sbo);
-        const uint64_t bd = smem_desc_kmajor(base + Slot<NT>::B, a.lbo, a.sbo);
-        mma_i8(tmem + (uint32_t)(acc * NT), ad, bd, idesc, 0);
-        mma_commit(bars.acc_full + 8 * acc);
+        for (int st = 0; st < kSlotSteps; st++, git++) {
+            const uint32_t acc = git % acc_ring(NT);
+            // the accumulator this step overwrites must have been drained by the epilogue
+            if (!mbar_wait(bars.acc_empty + 8 * acc, ((git / acc_ring(NT)) & 1) ^ 1, &g_mma_status)) {
+                return false;
+            }
+            tc_fence_after();
+            const uint64_t ad = smem_desc_kmajor(base + Slot<NT>::A + (uint32_t)(st * kTileM * 32), a.lbo, a.sbo);
+            const uint64_t bd =
+                smem_desc_kmajor(base + Slot<NT>::B + (uint32_t)(step_bbuf<TYPE>(st) * NT * 32), a.lbo, a.sbo);
+            mma_i8(tmem + (uint32_t)(acc * NT), ad, bd, idesc, 0);
+            mma_commit(bars.acc_full + 8 * acc);
+        }
     }
     return true;
 }
@@ -307,12 +381,14 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 // Epilogue: this thread owns weight row `row0 + 32*(warp%4) + lane` and NT/EW token columns.
 template <int TYPE, int NT, int EW>
 __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                              uint32_t tmem, const Bars & bars, uint32_t & git) {
+                                              uint32_t tmem, const Bars & bars, uint32_t & gslot, uint32_t & git) {
     using F = StepFmt<TYPE>;
     constexpr int NC = NT / EW; // token columns per thread
+    constexpr uint32_t AR = acc_ring(NT);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rl = 32 * (warp & 3) + lane, c0 = (warp >> 2) * NC;
-    const int steps = (a.c.K >> 8) * F::NS;
+    const int slots = (a.c.K >> 8) * (F::NS / kSlotSteps);
+    const uint32_t D = (uint32_t)bars.depth;
     uint64_t acc[NC / 2];
 #pragma unroll
     for (int i = 0; i < NC / 2; i++) {
@@ -320,61 +396,68 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
     }
     const uint64_t kNegMagic = pack2(-12582912.0f, -12582912.0f);
     bool ok = true;
-    for (int i = 0; i < steps; i++, git++) {
-        const uint32_t slot = git % (uint32_t)bars.depth, accb = git % kRing;
-        if (!mbar_wait(bars.acc_full + 8 * accb, (git / kRing) & 1, &g_mma_status)) {
-            ok = false;
-            break;
-        }
-        tc_fence_after();
+    for (int i = 0; i < slots && ok; i++, gslot++) {
+        const uint32_t slot = gslot % D;
         const uint32_t base = ring + slot * Slot<NT>::BYTES;
-        const float ra = __uint_as_float(lds32(base + Slot<NT>::ROWA + 4 * rl));
-        const uint64_t rowA = pack2(ra, ra);
-        uint64_t nrowB = 0ull;
-        if (F::HAS_MIN) {
-            const float rb = -__uint_as_float(lds32(base + Slot<NT>::ROWB + 4 * rl));
-            nrowB = pack2(rb, rb);
-        }
-        const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(accb * NT + c0);
+#pragma unroll 1
+        for (int st = 0; st < kSlotSteps; st++, git++) {
+            const uint32_t accb = git % AR;
+            if (!mbar_wait(bars.acc_full + 8 * accb, (git / AR) & 1, &g_mma_status)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const float ra = __uint_as_float(lds32(base + Slot<NT>::ROWA + 4 * (st * kTileM + rl)));
+            const uint64_t rowA = pack2(ra, ra);
+            uint64_t nrowB = 0ull;
+            if (F::HAS_MIN) {
+                const float rb = -__uint_as_float(lds32(base + Slot<NT>::ROWB + 4 * (st * kTileM + rl)));
+                nrowB = pack2(rb, rb);
+            }
+            const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(accb * NT + c0);
+            const uint32_t tok = base + 4 * (st * NT + c0);
 #pragma unroll
-        for (int j = 0; j < NC; j += 16) {
-            uint32_t v[16];
-            tmem_ld16(taddr + j, v);
-            tmem_ld_wait();
+            for (int j = 0; j < NC; j += 16) {
+                uint32_t v[16];
+                tmem_ld16(taddr + j, v);
+                tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 16; q += 4) {
-                const uint4 ta = lds128(base + Slot<NT>::TOKA + 4 * (c0 + j + q));
-                const uint64_t sx[2] = {(uint64_t)ta.x | ((uint64_t)ta.y << 32), (uint64_t)ta.z | ((uint64_t)ta.w << 32)};
-                uint64_t tc[2] = {0ull, 0ull}, tb[2] = {0ull, 0ull};
-                if (F::HAS_C) {
-                    const uint4 x = lds128(base + Slot<NT>::TOKC + 4 * (c0 + j + q));
-                    tc[0] = pack2(-__uint_as_float(x.x), -__uint_as_float(x.y));
-                    tc[1] = pack2(-__uint_as_float(x.z), -__uint_as_float(x.w));
-                }
-                if (F::HAS_MIN) {
-                    const uint4 x = lds128(base + Slot<NT>::TOKB + 4 * (c0 + j + q));
-                    tb[0] = (uint64_t)x.x | ((uint64_t)x.y << 32);
-                    tb[1] = (uint64_t)x.z | ((uint64_t)x.w << 32);
-                }
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    // exact int -> float without the conversion unit: |wd| < 2^22
-                    uint64_t w = (uint64_t)(v[q + 2 * e] + 0x4B400000u) | ((uint64_t)(v[q + 2 * e + 1] + 0x4B400000u) << 32);
-                    w = add2(w, kNegMagic);
+                for (int q = 0; q < 16; q += 4) {
+                    const uint4 ta = lds128(tok + Slot<NT>::TOKA + 4 * (j + q));
+                    const uint64_t sx[2] = {(uint64_t)ta.x | ((uint64_t)ta.y << 32), (uint64_t)ta.z | ((uint64_t)ta.w << 32)};
+                    uint64_t tc[2] = {0ull, 0ull}, tb[2] = {0ull, 0ull};
                     if (F::HAS_C) {
-                        w = add2(w, tc[e]);
+                        const uint4 x = lds128(tok + Slot<NT>::TOKC + 4 * (j + q));
+                        tc[0] = pack2(-__uint_as_float(x.x), -__uint_as_float(x.y));
+                        tc[1] = pack2(-__uint_as_float(x.z), -__uint_as_float(x.w));
                     }
-                    uint64_t r = fma2(rowA, mul2(sx[e], w), acc[(j + q) / 2 + e]);
                     if (F::HAS_MIN) {
-                        r = fma2(nrowB, tb[e], r);
+                        const uint4 x = lds128(tok + Slot<NT>::TOKB + 4 * (j + q));
+                        tb[0] = (uint64_t)x.x | ((uint64_t)x.y << 32);
+                        tb[1] = (uint64_t)x.z | ((uint64_t)x.w << 32);
                     }
-                    acc[(j + q) / 2 + e] = r;
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        // exact int -> float without the conversion unit: |wd| < 2^22
+                        uint64_t w = (uint64_t)(v[q + 2 * e] + 0x4B400000u) | ((uint64_t)(v[q + 2 * e + 1] + 0x4B400000u) << 32);
+                        w = add2(w, kNegMagic);
+                        if (F::HAS_C) {
+                            w = add2(w, tc[e]);
+                        }
+                        uint64_t r = fma2(rowA, mul2(sx[e], w), acc[(j + q) / 2 + e]);
+                        if (F::HAS_MIN) {
+                            r = fma2(nrowB, tb[e], r);
+                        }
+                        acc[(j + q) / 2 + e] = r;
+                    }
                 }
             }
+            tc_fence_before();
+            mbar_arrive(bars.acc_empty + 8 * accb); // the accumulator may be overwritten
         }
-        tc_fence_before();
-        mbar_arrive(bars.acc_empty + 8 * accb); // the accumulator may be overwritten
-        mbar_arrive(bars.done + 8 * slot);      // the operand slot and its factors may be refilled
+        if (ok) {
+            mbar_arrive(bars.done + 8 * slot); // the operand slot and its factors may be refilled
+        }
     }
     if (ok) {
         const int row = row0 + rl;
@@ -399,21 +482,20 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
 
 template <int TYPE, int NT, int EW, int PG>
 __device__ __forceinline__ bool run_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                         uint32_t tmem, const Bars & bars, uint32_t & git) {
+                                         uint32_t tmem, const Bars & bars, uint32_t & gslot, uint32_t & git) {
     using R = Roles<NT, EW, PG>;
     const int warp = threadIdx.x >> 5;
     if (warp < R::kEpiWarps) {
-        return epilogue_tile<TYPE, NT, EW>(a, sg, row0, t0, ring, tmem, bars, git);
+        return epilogue_tile<TYPE, NT, EW>(a, sg, row0, t0, ring, tmem, bars, gslot, git);
     }
     if (warp < R::kEpiWarps + R::kProdWarps) {
-        return produce_tile<TYPE, NT, PG>(a, sg, row0, t0, ring, ring + R::kDepth * Slot<NT>::BYTES,
-                                          (int)threadIdx.x - 32 * R::kEpiWarps, bars, git);
+        return produce_tile<TYPE, NT, PG>(a, sg, row0, t0, ring, ring + (uint32_t)bars.depth * Slot<NT>::BYTES,
+                                          (int)threadIdx.x - 32 * R::kEpiWarps, bars, gslot);
     }
     if (threadIdx.x == 32 * (R::kEpiWarps + R::kProdWarps)) {
-        return mma_tile<TYPE, NT>(a, ring, tmem, bars, git);
+        return mma_tile<TYPE, NT>(a, ring, tmem, bars, gslot, git);
     }
-    git += (uint32_t)((a.c.K >> 8) * StepFmt<TYPE>::NS); // idle lanes of the MMA warp keep the count
-    return true;
+    return true; // idle lanes of the MMA warp
 }
 
 template <int NT, int EW, int PG>
@@ -421,16 +503,18 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
     using R = Roles<NT, EW, PG>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t sbase = smem_u32(smem_raw);
-    const Bars bars{sbase, sbase + 128, sbase + 256, sbase + 320, R::kDepth};
+    // mbarriers: full[8] @0, done[8] @64, acc_full[16] @128, acc_empty[16] @256, TMEM address @384
+    static_assert(kMaxDepth <= 8 && acc_ring(NT) <= 16 && kHdr >= 400, "barrier header layout");
+    const Bars bars{sbase, sbase + 64, sbase + 128, sbase + 256, a.depth};
     const uint32_t tmem_slot = sbase + 384, ring = sbase + kHdr;
-    constexpr uint32_t kCols = kRing * NT < 32 ? 32 : kRing * NT; // power of two >= 32
+    constexpr uint32_t kCols = acc_ring(NT) * NT; // 512: a power of two >= 32
     const int warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < R::kDepth; s++) {
-            mbar_init(bars.full + 8 * s, 128); // the one producer group that owns the step
+        for (int s = 0; s < a.depth; s++) {
+            mbar_init(bars.full + 8 * s, 128); // the one producer group that owns the slot
             mbar_init(bars.done + 8 * s, 32 * R::kEpiWarps);
         }
-        for (int s = 0; s < kRing; s++) {
+        for (int s = 0; s < acc_ring(NT); s++) {
             mbar_init(bars.acc_full + 8 * s, 1);
             mbar_init(bars.acc_empty + 8 * s, 32 * R::kEpiWarps);
         }
@@ -445,7 +529,7 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
     const uint32_t tmem = lds32(tmem_slot);
     asm volatile("griddepcontrol.wait;" ::: "memory"); // the activation quantizer's output is read below
 
-    uint32_t git = 0;
+    uint32_t gslot = 0, git = 0;
     bool ok = true;
     const int n_tiles = a.n_tiles_m * a.n_tiles_t;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -457,11 +541,11 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
         const SegDev & sg = a.c.seg[si];
         const int row0 = (tm - (si ? a.tiles_m[si - 1] : 0)) * kTileM, t0 = tt * NT;
         switch (sg.type) {
-        case kQ4_K: ok = run_tile<kQ4_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, git); break;
-        case kQ5_K: ok = run_tile<kQ5_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, git); break;
-        case kQ6_K: ok = run_tile<kQ6_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, git); break;
-        case kIQ4_XS: ok = run_tile<kIQ4_XS, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, git); break;
-        default: ok = run_tile<kQ8_0, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, git); break;
+        case kQ4_K: ok = run_tile<kQ4_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
+        case kQ5_K: ok = run_tile<kQ5_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
+        case kQ6_K: ok = run_tile<kQ6_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
+        case kIQ4_XS: ok = run_tile<kIQ4_XS, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
+        default: ok = run_tile<kQ8_0, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
         }
     }
     // every role falls through to here, also after a wait that ran out: release tensor memory
@@ -475,10 +559,18 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
 // ---- host side ----------------------------------------------------------------------------------
 template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, MmaArgs & a, bool pdl_secondary) {
     using R = Roles<NT, EW, PG>;
-    const size_t smem = kHdr + (size_t)R::kDepth * Slot<NT>::BYTES + (size_t)32 * R::kProdWarps * 2 * a.raw_bytes;
-    if (smem > 227 * 1024) {
+    const size_t raw = (size_t)32 * R::kProdWarps * 2 * a.raw_bytes, budget = 227 * 1024;
+    if (kHdr + 2 * (size_t)Slot<NT>::BYTES + raw > budget) {
         return cudaErrorInvalidConfiguration;
     }
+    int depth = (int)((budget - kHdr - raw) / Slot<NT>::BYTES);
+    depth = depth > kMaxDepth ? kMaxDepth : depth;
+    if (const char * e = getenv("B200Q_MMA_DEPTH")) {
+        const int d = atoi(e);
+        depth = d >= 2 && d <= depth ? d : depth;
+    }
+    a.depth = depth;
+    const size_t smem = kHdr + (size_t)depth * Slot<NT>::BYTES + raw;
     static size_t configured = 0;
     if (configured < smem) {
         cudaError_t e = cudaFuncSetAttribute(gemm_mma_kernel<NT, EW, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -506,21 +598,30 @@ template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, M
 cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     MmaArgs a;
     a.c = c;
-    int tiles = 0, max_sbb = 0;
+    int tiles = 0, need = 0;
     for (int i = 0; i < c.n_segs; i++) {
         tiles += (c.seg[i].n_rows + kTileM - 1) / kTileM;
         a.tiles_m[i] = tiles;
-        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+        // a superblock plus its misalignment, in whole 16-byte chunks (none when the size is a
+        // multiple of 16: tensor bases are 16-byte aligned)
+        const int sbb = sb_bytes(c.seg[i].type);
+        int n = sbb % 16 == 0 ? sbb : ((sbb + 30) / 16) * 16;
+        if (c.seg[i].type == kQ8_0) {
+            n += 16; // the funnel-shifted 2-byte-aligned reads touch one word past the last block
+        }
+        need = need > n ? need : n;
     }
     a.n_tiles_m = tiles;
-    a.raw_bytes = ((max_sbb + 15 + 15) / 16) * 16 + 16; // superblock + misalignment, whole 16-byte chunks
+    // odd number of 16-byte chunks per thread: the threads' 16-byte reads then hit distinct banks
+    a.raw_bytes = (need / 16) % 2 ? need : need + 16;
     a.lbo = 128;
     a.sbo = 256;
-    if (c.TB <= 32) { // batched decode: unpacking dominates; one epilogue warpgroup
-        return launch_nt<32, 1, 2>(s, a, pdl_secondary);
+    const bool pg2 = a.raw_bytes <= (c.TB <= 32 ? 240 : 192); // a second producer group where its staging fits
+    if (c.TB <= 32) { // batched decode: unpacking dominates
+        return pg2 ? launch_nt<32, 2, 2>(s, a, pdl_secondary) : launch_nt<32, 2, 1>(s, a, pdl_secondary);
     }
-    // prefill: the fp32 epilogue dominates; a second producer group only where its staging fits
-    return a.raw_bytes <= 256 ? launch_nt<128, 2, 2>(s, a, pdl_secondary) : launch_nt<128, 2, 1>(s, a, pdl_secondary);
+    // prefill: the fp32 epilogue dominates; two epilogue warpgroups share the token columns
+    return pg2 ? launch_nt<64, 2, 2>(s, a, pdl_secondary) : launch_nt<64, 2, 1>(s, a, pdl_secondary);
 }
 
 cudaError_t read_mma_status(int * status, bool clear) {
