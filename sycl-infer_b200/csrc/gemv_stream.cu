@@ -22,13 +22,11 @@
 #include <cstdlib>
 #include <type_traits>
 
-#include "async.cuh"
 #include "launch.h"
-#include "units.cuh"
+#include "stream_core.cuh"
 
 namespace b200q {
 
-constexpr int kConsumerWarps = 8;
 constexpr int kStreamThreads = 32 * (kConsumerWarps + 1);
 constexpr int kSmemBudget = 110 * 1024;         // two CTAs per SM
 
@@ -41,128 +39,9 @@ struct StreamArgs {
     int32_t stages;
     int32_t contig;     // tiles hold whole rows: one bulk copy per tile, rows packed back to back
     int32_t tile_bytes; // shared bytes reserved per tile
+    CostSplit cost; // the call's cost over the grid, for the row split
     int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
-
-// Build the activation pack of superblocks [sb0, sb0+n) of token 0 (see units.cuh).
-__device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int sb0, int n, int tid, int nthr) {
-    for (int i = tid; i < 8 * n; i += nthr) {
-        const int g = 8 * sb0 + i; // TB == 1: group index == array index
-        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + (size_t)g * 32);
-        const uint4 x0 = __ldg(gx), x1 = __ldg(gx + 1);
-        const float sx = __ldg(c.xmeta + 2 * (size_t)g);
-        const int2 xs = __ldg(reinterpret_cast<const int2 *>(c.xsumq) + g);
-        const uint32_t p = pack_addr(pack, i);
-        sts128(p, x0.x, x0.y, x0.z, x0.w);
-        sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
-        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
-    }
-}
-
-// One warp, RW rows, one tile, one token.  A superblock is H units (Unit1<TYPE>::H); lane l
-// owns unit l % H of superblocks l / H, + 32/H, ...  The superblocks left over after the
-// full passes are handled with the lanes split between the rows when that fills more lanes.
-template <int TYPE, int RW>
-__device__ __forceinline__ void consume_tile1(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                              int sb0, const PackA & as, float (&acc)[RW][1]) {
-    using U = Unit1<TYPE>;
-    constexpr int H = U::H, SPI = 32 / H, SB = Fmt<TYPE>::SB;
-    const int lane = threadIdx.x & 31;
-    const int bl = lane / H, u = lane % H;
-    const int full = kb / SPI, rem = kb - full * SPI;
-    for (int it = 0; it < full; it++) {
-        const int b = it * SPI + bl;
-        typename U::Act a;
-        U::load_act(as, sb0 + b, u, a);
-#pragma unroll
-        for (int r = 0; r < RW; r++) {
-            acc[r][0] += U::term(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * SB), u, a);
-        }
-    }
-    if (rem == 0) {
-        return;
-    }
-    const int m = rem * H; // units per row in the tail, < 32
-    if (RW > 1 && 2 * m <= 32) {
-        const int rpp = min(RW, 32 / m); // rows per pass
-        for (int r0 = 0; r0 < RW; r0 += rpp) {
-            const int rr = lane / m, item = lane - rr * m, row = r0 + rr;
-            const bool valid = rr < rpp && row < RW;
-            float t = 0.f;
-            if (valid) {
-                const int b = full * SPI + item / H, uu = item % H;
-                uint32_t mr = mis[0];
-#pragma unroll
-                for (int r = 1; r < RW; r++) {
-                    mr = row == r ? mis[r] : mr;
-                }
-                typename U::Act a;
-                U::load_act(as, sb0 + b, uu, a);
-                t = U::term(slot0 + row * slot_stride + mr + (uint32_t)(b * SB), uu, a);
-            }
-#pragma unroll
-            for (int r = 0; r < RW; r++) {
-                acc[r][0] += row == r ? t : 0.f;
-            }
-        }
-    } else if (bl < rem) {
-        const int b = full * SPI + bl;
-        typename U::Act a;
-        U::load_act(as, sb0 + b, u, a);
-#pragma unroll
-        for (int r = 0; r < RW; r++) {
-            acc[r][0] += U::term(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * SB), u, a);
-        }
-    }
-}
-
-// 2..8 tokens: quarter-superblock units whose unpacked weights stay in registers for all tokens
-template <int TYPE, int RW, int TT>
-__device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                             int sb0, const GlobA & as, float (&acc)[RW][TT]) {
-    const int lane = threadIdx.x & 31;
-    const int u = lane & 3;
-    for (int b = lane >> 2; b < kb; b += 8) {
-#pragma unroll
-        for (int r = 0; r < RW; r++) {
-            WUnit<TYPE> w;
-            w.load(slot0 + r * slot_stride + mis[r] + (uint32_t)(b * Fmt<TYPE>::SB), u);
-#pragma unroll
-            for (int t = 0; t < TT; t++) {
-                typename WUnit<TYPE>::Act a;
-                load_act<TYPE>(as, sb0 + b, u, min(t, as.TB - 1), a);
-                acc[r][t] += w.term(a);
-            }
-        }
-    }
-}
-template <int TYPE, int RW, int TT>
-__device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                             int sb0, const PackA & as, float (&acc)[RW][TT]) {
-    static_assert(TT == 1, "the activation pack holds one token");
-    consume_tile1<TYPE, RW>(slot0, slot_stride, mis, kb, sb0, as, acc);
-}
-
-// The rows of a call are split among the CTAs in proportion to their bytes: CTA c owns the
-// flattened cost range [total*c/G, total*(c+1)/G), cost = rows x bytes per superblock.
-struct RowRange {
-    int lo, hi;
-};
-__device__ __forceinline__ RowRange cta_rows(const CallDev & c, int si, unsigned long long lo, unsigned long long hi) {
-    unsigned long long c0 = 0;
-    for (int i = 0; i < si; i++) {
-        c0 += (unsigned long long)c.seg[i].n_rows * sb_bytes(c.seg[i].type);
-    }
-    const unsigned long long w = sb_bytes(c.seg[si].type);
-    const unsigned long long c1 = c0 + (unsigned long long)c.seg[si].n_rows * w;
-    const unsigned long long a = lo > c0 ? lo : c0, b = hi < c1 ? hi : c1;
-    RowRange r{0, 0};
-    if (a < b) {
-        r.lo = (int)((a - c0 + w - 1) / w);
-        r.hi = (int)((b - c0 + w - 1) / w);
-    }
-    return r;
-}
 
 template <int TT, int RW>
 __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
@@ -175,12 +54,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     const int nb = a.c.K >> 8;
     const int n_chunks = (nb + a.kb_max - 1) / a.kb_max;
     const int S = a.stages;
-    unsigned long long cost_total = 0;
-    for (int i = 0; i < a.c.n_segs; i++) {
-        cost_total += (unsigned long long)a.c.seg[i].n_rows * sb_bytes(a.c.seg[i].type);
-    }
-    const unsigned long long cost_lo = cost_total * blockIdx.x / gridDim.x;
-    const unsigned long long cost_hi = cost_total * (blockIdx.x + 1) / gridDim.x;
+    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
 
     // Let the next kernel in the stream be scheduled as soon as this grid is resident: its
     // CTAs start on SMs this grid's tail frees, and prefetch weights while it still waits
@@ -387,10 +261,13 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     } else if ((size_t)kRows * nb * max_sbb + 48 <= room) {
         kb = nb;
     } else {
-        kb = (int)((room / kRows - 48) / max_sbb) / 8 * 8;
+        // a single-token pass of a warp covers 16 superblocks of Q4_K/Q5_K/Q6_K (two units each)
+        const int fit = (int)((room / kRows - 48) / max_sbb);
+        const int gran = TT == 1 && fit >= 16 ? 16 : 8;
+        kb = fit / gran * gran;
         kb = kb < 8 ? 8 : kb;
-        const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of 8
-        kb = (((nb + n_chunks - 1) / n_chunks + 7) / 8) * 8;
+        const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of gran
+        kb = (((nb + n_chunks - 1) / n_chunks + gran - 1) / gran) * gran;
     }
     a.kb_max = kb < nb ? kb : nb;
     static const int contig_env = env_int("B200Q_CONTIG", 1);
@@ -433,12 +310,16 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     cfg.attrs = attr;
     static const int pdl_env = env_int("B200Q_PDL", 1);
     cfg.numAttrs = (pdl_secondary || pdl_env) && pdl_env >= 0 ? 1 : 0;
+    if (!cost_split(c, (uint32_t)grid, a.cost)) {
+        return cudaErrorInvalidConfiguration;
+    }
     return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<TT, RW>, a);
 }
 
 bool stream_supported(const CallDev & c) {
     // the single-token activation pack (400 B per superblock) must leave room for two tiles
-    return c.TB >= 1 && c.TB <= 8 && c.K <= 24576;
+    CostSplit cs; // ... and the byte-balanced row split works in 32-bit arithmetic
+    return c.TB >= 1 && c.TB <= 8 && c.K <= 24576 && cost_split(c, 2 * kSMs, cs);
 }
 
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {

@@ -33,6 +33,13 @@ __device__ __forceinline__ uint32_t pack_addr(uint32_t pack, int g) {
     return pack + (uint32_t)((g >> 3) * kPackSB + (g & 7) * kPackGroup);
 }
 
+// four consecutive groups with both 16-value sums each, for a Q6_K half unit
+struct ActG6H {
+    uint32_t x[4][8];
+    float sx[4];
+    int xs[4][2];
+};
+
 struct GroupMeta {
     float sx;
     int xs0, xs1;
@@ -89,6 +96,19 @@ struct PackA { // staged pack, token 0
             a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
             a.sx[i] = __uint_as_float(m.x);
             a.c[i] = __uint_as_float(m.w);
+        }
+    }
+    __device__ __forceinline__ void g6h(int g, ActG6H & a) const { // g a multiple of 4
+        const uint32_t p0 = pack_addr(pack, g);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t p = p0 + i * kPackGroup;
+            const uint4 x0 = lds128(p), x1 = lds128(p + 16), m = lds128(p + 32);
+            a.x[i][0] = x0.x, a.x[i][1] = x0.y, a.x[i][2] = x0.z, a.x[i][3] = x0.w;
+            a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
+            a.sx[i] = __uint_as_float(m.x);
+            a.xs[i][0] = (int)m.y;
+            a.xs[i][1] = (int)m.z;
         }
     }
     __device__ __forceinline__ void g6(int g, int hs, int, ActG6 & a) const {
@@ -367,6 +387,65 @@ template <> struct WUnit<kQ6_K> {
     }
 };
 
+// Half a Q6_K superblock (groups 4h..4h+3, 128 weights) for single-token calls.  Against the
+// quarter unit above it reads every activation group whole (both 16-value halves), so a unit
+// moves 176 bytes of activation for 96 bytes of weights instead of 2 x 128 for 2 x 48: the
+// quarter unit is bound by shared-memory bandwidth, not by HBM.  The int8 block scale is
+// folded in as an integer, sum_half s8 * (wd - 32 * xsum) (below 2^24, so its conversion to
+// fp32 is exact), leaving one conversion and one FMA per group and a single multiply by d.
+struct HalfQ6 {
+    // raw-code sums per 16-value scale group: w[plane][half]
+    static __device__ __forceinline__ void dots(uint32_t sb, int h, const ActG6H & a, int (&w)[4][2]) {
+        const uint32_t sh = (sb & 2u) * 8, q = (sb & ~3u) + 64u * h, qhp = (sb & ~3u) + 128u + 32u * h;
+#pragma unroll
+        for (int hs = 0; hs < 2; hs++) {
+            uint32_t wa[5], wb[5], wh[5];
+#pragma unroll
+            for (int k = 0; k < 5; k++) { // aligned words; the block is only 2-byte aligned
+                wa[k] = lds32(q + 16 * hs + 4 * k);
+                wb[k] = lds32(q + 32 + 16 * hs + 4 * k);
+                wh[k] = lds32(qhp + 16 * hs + 4 * k);
+            }
+            int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t qa = __funnelshift_r(wa[k], wa[k + 1], sh), qb = __funnelshift_r(wb[k], wb[k + 1], sh);
+                const uint32_t hh = __funnelshift_r(wh[k], wh[k + 1], sh);
+                s0 = dp4a_us((qa & 0x0F0F0F0Fu) | ((hh << 4) & 0x30303030u), a.x[0][4 * hs + k], s0);
+                s1 = dp4a_us((qb & 0x0F0F0F0Fu) | ((hh << 2) & 0x30303030u), a.x[1][4 * hs + k], s1);
+                s2 = dp4a_us(((qa >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u), a.x[2][4 * hs + k], s2);
+                s3 = dp4a_us(((qb >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u), a.x[3][4 * hs + k], s3);
+            }
+            w[0][hs] = s0, w[1][hs] = s1, w[2][hs] = s2, w[3][hs] = s3;
+        }
+    }
+    static __device__ __forceinline__ float term(uint32_t sb, int h, const ActG6H & a) {
+        int w[4][2];
+        dots(sb, h, a, w);
+        // the half's eight int8 scales: scales[8h + 2*plane + half]
+        const uint32_t sh = (sb & 2u) * 8, sp = (sb & ~3u) + 192u + 8u * h;
+        const uint32_t c0 = lds32(sp), c1 = lds32(sp + 4), c2 = lds32(sp + 8);
+        const uint32_t sc[2] = {__funnelshift_r(c0, c1, sh), __funnelshift_r(c1, c2, sh)};
+        float r = 0.f;
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const int sa = (int)(int8_t)(sc[p >> 1] >> (16 * (p & 1))), sb8 = (int)(int8_t)(sc[p >> 1] >> (16 * (p & 1) + 8));
+            const int t = sa * (w[p][0] - 32 * a.xs[p][0]) + sb8 * (w[p][1] - 32 * a.xs[p][1]);
+            r = fmaf(a.sx[p], (float)t, r);
+        }
+        return h2f((uint16_t)lds16(sb + 208)) * r;
+    }
+    static __device__ __forceinline__ void exact(uint32_t sb, int h, const ActG6H & a, int G, int32_t * wd) {
+        int w[4][2];
+        dots(sb, h, a, w);
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            wd[2 * (G + p)] = w[p][0];
+            wd[2 * (G + p) + 1] = w[p][1];
+        }
+    }
+};
+
 // ----------------------------------------------------------------------------- IQ4_XS
 // Codebook kvalues_iq4nl (src/common/quant.h:417 of the reference) as four little-endian words.
 // A 32-bit word of eight 4-bit indices n0..n7 is looked up with byte permutes whose
@@ -531,6 +610,17 @@ template <int TYPE> struct Unit1K45 {
     }
     static __device__ __forceinline__ void exact(uint32_t sb, int sbi, int u, const Act & a, int32_t * wd) {
         HalfK45<TYPE>::exact(sb, u, a, 8 * sbi + 4 * u, wd);
+    }
+};
+template <> struct Unit1<kQ6_K> {
+    static constexpr int H = 2;
+    using Act = ActG6H;
+    static __device__ __forceinline__ void load_act(const PackA & as, int sbi, int u, Act & a) {
+        as.g6h(8 * sbi + 4 * u, a);
+    }
+    static __device__ __forceinline__ float term(uint32_t sb, int u, const Act & a) { return HalfQ6::term(sb, u, a); }
+    static __device__ __forceinline__ void exact(uint32_t sb, int sbi, int u, const Act & a, int32_t * wd) {
+        HalfQ6::exact(sb, u, a, 8 * sbi + 4 * u, wd);
     }
 };
 template <> struct Unit1<kQ4_K> : Unit1K45<kQ4_K> {};

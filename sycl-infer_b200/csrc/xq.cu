@@ -12,13 +12,9 @@
 #include <cstdlib>
 
 #include "launch.h"
+#include "xq.cuh"
 
 namespace b200q {
-
-__device__ __forceinline__ float silu_exact(float a) {
-    const float e = (float)exp((double)(-a));
-    return __fdiv_rn(a, __fadd_rn(1.0f, e));
-}
 
 // One warp per (token, group); lane i owns element i.
 __global__ void __launch_bounds__(256) xq_kernel(const float * __restrict__ x, const float * __restrict__ up,
@@ -40,16 +36,13 @@ __global__ void __launch_bounds__(256) xq_kernel(const float * __restrict__ x, c
     if (up) {
         a = __fmul_rn(silu_exact(a), up[(size_t)t * up_stride + g * 32 + lane]);
     }
-    const float mx = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(a))));
-    const float inv = mx > 0.0f ? __fdiv_rn(127.0f, mx) : 0.0f;
-    const float r = fminf(127.0f, fmaxf(-127.0f, roundf(__fmul_rn(a, inv))));
-    const int q = (int)r;
-    const int s0 = __reduce_add_sync(0xFFFFFFFFu, lane < 16 ? q : 0);
-    const int s1 = __reduce_add_sync(0xFFFFFFFFu, lane < 16 ? 0 : q);
+    float scale;
+    int s0, s1;
+    const int q = xq_group(a, lane, scale, s0, s1);
     const size_t gi = (size_t)g * TB + t;
     x8[gi * 32 + lane] = (int8_t)q;
     if (lane == 0) {
-        xmeta[gi * 2] = h2f(f2h_trunc(mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 0.0f));
+        xmeta[gi * 2] = scale;
         xmeta[gi * 2 + 1] = 0.0f;
         xsumq[gi * 2] = s0;
         xsumq[gi * 2 + 1] = s1;
