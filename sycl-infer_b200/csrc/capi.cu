@@ -115,6 +115,13 @@ cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
         const char * e = getenv("B200Q_KERNEL");
         return e && strcmp(e, "rows") == 0;
     }();
+    static const int mma_from = [] { // fewest tokens that take the tensor-core kernel
+        const char * e = getenv("B200Q_MMA_FROM");
+        return e && *e ? atoi(e) : 9;
+    }();
+    if (!force_rows && c.TB >= mma_from) {
+        return launch_gemm_mma(s, c, pdl_secondary);
+    }
     if (!force_rows && stream_supported(c)) {
         return launch_gemv_stream(s, c, pdl_secondary);
     }

@@ -32,16 +32,109 @@ constexpr int kSmemBudget = 110 * 1024;         // two CTAs per SM
 
 __device__ int g_device_status = 0;
 
+struct SegTile {
+    int16_t kb_max;     // superblocks per tile along K
+    int16_t contig;     // tiles hold whole rows: one bulk copy per tile, rows packed back to back
+    int32_t slot_bytes; // shared bytes reserved per row of a tile (when not contiguous)
+};
+
 struct StreamArgs {
     CallDev c;
-    int32_t kb_max;     // superblocks per tile along K
-    int32_t slot_bytes; // shared bytes reserved per row of a tile
+    SegTile seg_tile[B200Q_MAX_SEGS]; // tile shape per segment (a tile never spans segments)
     int32_t stages;
-    int32_t contig;     // tiles hold whole rows: one bulk copy per tile, rows packed back to back
-    int32_t tile_bytes; // shared bytes reserved per tile
+    int32_t tile_bytes; // shared bytes reserved per tile (the largest segment's)
     CostSplit cost; // the call's cost over the grid, for the row split
     int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
+
+// Position in the shared-memory ring: slot and the parity of its full barrier.
+struct RingPos {
+    int stage;
+    uint32_t phase;
+};
+
+// One consumer warp's share of one segment: rows RW*warp.. of every tile of the CTA's row range.
+template <int TYPE, int TT, int RW, class AS>
+__device__ __forceinline__ bool consume_segment(const StreamArgs & a, int si, const RowRange rr, uint32_t tiles,
+                                                uint32_t bar_full, uint32_t bar_empty, const AS & as, RingPos & pos) {
+    constexpr int kRows = kConsumerWarps * RW, SB = Fmt<TYPE>::SB;
+    const SegDev & sg = a.c.seg[si];
+    const SegTile st = a.seg_tile[si];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = a.c.K >> 8, S = a.stages;
+    // bytes between consecutive rows of a tile: rows back to back, or one slot per row segment
+    const uint32_t stride = st.contig ? (uint32_t)(nb * SB) : (uint32_t)st.slot_bytes;
+    const uint32_t wbase = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w) & 15);
+    const uint32_t warp_off = (uint32_t)(warp * RW) * stride;
+    for (int tile_row0 = rr.lo; tile_row0 < rr.hi; tile_row0 += kRows) {
+        const int row0 = tile_row0 + warp * RW;
+        // where a row's bytes start inside its slot: its own misalignment, or in contiguous
+        // mode the misalignment of the tile's first row (only the low four address bits matter)
+        uint32_t mis0[RW];
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+            const uint32_t rx = (uint32_t)(st.contig ? tile_row0 : row0 + r);
+            mis0[r] = wbase + rx * (uint32_t)(nb * SB);
+        }
+        float acc[RW][TT];
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                acc[r][t] = 0.f;
+            }
+        }
+        for (int sb0 = 0; sb0 < nb; sb0 += st.kb_max) {
+            if (!mbar_wait(bar_full + 8 * pos.stage, pos.phase, &g_device_status)) {
+                return false;
+            }
+            if (row0 < rr.hi && !a.dry) { // rows past the range hold stale bytes: their results are dropped
+                const int kb = min((int)st.kb_max, nb - sb0);
+                const uint32_t slot0 = tiles + (uint32_t)(pos.stage * a.tile_bytes) + warp_off;
+                uint32_t mis[RW];
+#pragma unroll
+                for (int r = 0; r < RW; r++) {
+                    mis[r] = (mis0[r] + (uint32_t)(sb0 * SB)) & 15;
+                }
+                consume_tile<TYPE, RW, TT>(slot0, stride, mis, kb, sb0, as, acc);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_empty + 8 * pos.stage);
+            }
+            if (++pos.stage == S) {
+                pos.stage = 0;
+                pos.phase ^= 1;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                acc[r][t] = warp_sum(acc[r][t]);
+            }
+        }
+        // lane (r*TT + t) stores row r, token t
+        float mine = 0.f;
+#pragma unroll
+        for (int r = 0; r < RW; r++) {
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                mine = lane == r * TT + t ? acc[r][t] : mine;
+            }
+        }
+        const int r = lane / TT, t = lane % TT;
+        if (lane < RW * TT && row0 + r < rr.hi && t < a.c.TB) {
+            const size_t o = (size_t)t * sg.out_stride + row0 + r;
+            float v = sg.alpha * mine;
+            if (sg.residual) {
+                v += sg.residual[o];
+            }
+            store_out(a.c, &sg.out[o], v);
+        }
+    }
+    return true;
+}
 
 template <int TT, int RW>
 __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __grid_constant__ StreamArgs a) {
@@ -52,7 +145,6 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     const uint32_t pack = tiles + (uint32_t)(a.stages * a.tile_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = a.c.K >> 8;
-    const int n_chunks = (nb + a.kb_max - 1) / a.kb_max;
     const int S = a.stages;
     const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
 
@@ -71,23 +163,22 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer
-        uint32_t it = 0;
+        int stage = 0;
+        uint32_t par = 1; // parity of the empty barrier: a fresh slot is free
         bool alive = true;
         for (int si = 0; si < a.c.n_segs && alive; si++) {
             const SegDev & sg = a.c.seg[si];
+            const SegTile st = a.seg_tile[si];
             const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
             const int sbb = sb_bytes(sg.type);
             const size_t row_bytes = (size_t)nb * sbb;
             for (int row0 = rr.lo; row0 < rr.hi && alive; row0 += kRows) {
                 const int rows = min(kRows, rr.hi - row0);
-                for (int ch = 0; ch < n_chunks && alive; ch++, it++) {
-                    const int stage = it % S;
-                    const uint32_t par = ((it / S) & 1) ^ 1;
-                    const int sb0 = ch * a.kb_max;
-                    const int kb = min(a.kb_max, nb - sb0);
+                for (int sb0 = 0; sb0 < nb && alive; sb0 += st.kb_max) {
+                    const int kb = min((int)st.kb_max, nb - sb0);
                     uint32_t len = 0;
                     const uint8_t * src = nullptr;
-                    if (a.contig) {
+                    if (st.contig) {
                         if (lane == 0) { // the tile's rows are one contiguous byte range
                             const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
                             const uintptr_t A0 = A & ~uintptr_t(15);
@@ -116,8 +207,12 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
                     }
                     __syncwarp();
                     if (len) {
-                        bulk_g2s(tiles + (uint32_t)(stage * a.tile_bytes + (a.contig ? 0 : lane * a.slot_bytes)), src,
+                        bulk_g2s(tiles + (uint32_t)(stage * a.tile_bytes + (st.contig ? 0 : lane * st.slot_bytes)), src,
                                  len, bar_full + 8 * stage);
+                    }
+                    if (++stage == S) {
+                        stage = 0;
+                        par ^= 1;
                     }
                 }
             }
@@ -143,81 +238,19 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
         as.TB = a.c.TB;
     }
 
-    uint32_t it = 0;
+    RingPos pos{0, 0};
     for (int si = 0; si < a.c.n_segs; si++) {
-        const SegDev & sg = a.c.seg[si];
         const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
-        const int sbb = sb_bytes(sg.type);
-        for (int tile_row0 = rr.lo; tile_row0 < rr.hi; tile_row0 += kRows) {
-            const int row0 = tile_row0 + warp * RW;
-            // where a row's bytes start inside its slot: its own misalignment, or in contiguous
-            // mode the misalignment of the tile's first row
-            uint32_t mis0[RW];
-#pragma unroll
-            for (int r = 0; r < RW; r++) {
-                const int rx = a.contig ? tile_row0 : row0 + r;
-                mis0[r] = (uint32_t)(reinterpret_cast<uintptr_t>(sg.w + (size_t)rx * nb * sbb) & 15);
-            }
-            float acc[RW][TT];
-#pragma unroll
-            for (int r = 0; r < RW; r++) {
-#pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    acc[r][t] = 0.f;
-                }
-            }
-            for (int ch = 0; ch < n_chunks; ch++, it++) {
-                const int stage = it % S;
-                if (!mbar_wait(bar_full + 8 * stage, (it / S) & 1, &g_device_status)) {
-                    return;
-                }
-                const int sb0 = ch * a.kb_max;
-                const int kb = min(a.kb_max, nb - sb0);
-                if (row0 < rr.hi && !a.dry) { // rows past the range hold stale bytes: their results are dropped
-                    const uint32_t slot0 = tiles + (uint32_t)(stage * a.tile_bytes + warp * RW * a.slot_bytes);
-                    uint32_t mis[RW];
-#pragma unroll
-                    for (int r = 0; r < RW; r++) {
-                        mis[r] = (mis0[r] + (uint32_t)sb0 * sbb) & 15;
-                    }
-                    switch (sg.type) {
-                    case kQ4_K: consume_tile<kQ4_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                    case kQ5_K: consume_tile<kQ5_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                    case kQ6_K: consume_tile<kQ6_K, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                    case kIQ4_XS: consume_tile<kIQ4_XS, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                    default: consume_tile<kQ8_0, RW, TT>(slot0, a.slot_bytes, mis, kb, sb0, as, acc); break;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_empty + 8 * stage);
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < RW; r++) {
-#pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    acc[r][t] = warp_sum(acc[r][t]);
-                }
-            }
-            // lane (r*TT + t) stores row r, token t
-            float mine = 0.f;
-#pragma unroll
-            for (int r = 0; r < RW; r++) {
-#pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    mine = lane == r * TT + t ? acc[r][t] : mine;
-                }
-            }
-            const int r = lane / TT, t = lane % TT;
-            if (lane < RW * TT && row0 + r < rr.hi && t < a.c.TB) {
-                const size_t o = (size_t)t * sg.out_stride + row0 + r;
-                float v = sg.alpha * mine;
-                if (sg.residual) {
-                    v += sg.residual[o];
-                }
-                store_out(a.c, &sg.out[o], v);
-            }
+        bool ok;
+        switch (a.c.seg[si].type) { // one decoder per segment: the tile and chunk loops are specialised
+        case kQ4_K: ok = consume_segment<kQ4_K, TT, RW>(a, si, rr, tiles, bar_full, bar_empty, as, pos); break;
+        case kQ5_K: ok = consume_segment<kQ5_K, TT, RW>(a, si, rr, tiles, bar_full, bar_empty, as, pos); break;
+        case kQ6_K: ok = consume_segment<kQ6_K, TT, RW>(a, si, rr, tiles, bar_full, bar_empty, as, pos); break;
+        case kIQ4_XS: ok = consume_segment<kIQ4_XS, TT, RW>(a, si, rr, tiles, bar_full, bar_empty, as, pos); break;
+        default: ok = consume_segment<kQ8_0, TT, RW>(a, si, rr, tiles, bar_full, bar_empty, as, pos); break;
+        }
+        if (!ok) {
+            return;
         }
     }
 }
@@ -244,44 +277,41 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     const CallDev & c = a.c;
     constexpr int kRows = kConsumerWarps * RW;
     const int nb = c.K >> 8;
-    int groups = 0, max_sbb = 0;
+    int groups = 0;
     for (int i = 0; i < c.n_segs; i++) {
         groups += (c.seg[i].n_rows + kRows - 1) / kRows;
-        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
     }
-    // Superblocks per tile along K.  Copies are efficient when large (the copy engine spends
-    // about as long on a copy's fixed cost as on 750 bytes), so take whole rows when two
-    // tiles of whole rows fit, else the largest multiple of 8 superblocks (all 32 lanes
-    // busy) that leaves room for two tiles.
+    // Superblocks per tile along K, per segment.  Copies are efficient when large (the copy
+    // engine spends about as long on a copy's fixed cost as on 750 bytes), so take whole rows
+    // - one copy per tile - when two tiles of whole rows fit, else per row the largest run of
+    // superblocks that leaves room for two tiles, in multiples of what one pass of a warp covers.
     const size_t pack_probe = TT == 1 ? (size_t)nb * kPackSB : 0;
     const size_t room = (kSmemBudget - 128 - pack_probe) / 2; // bytes per tile with two stages
-    int kb;
-    if (kb_env > 0) {
-        kb = kb_env;
-    } else if ((size_t)kRows * nb * max_sbb + 48 <= room) {
-        kb = nb;
-    } else {
-        // a single-token pass of a warp covers 16 superblocks of Q4_K/Q5_K/Q6_K (two units each)
-        const int fit = (int)((room / kRows - 48) / max_sbb);
-        const int gran = TT == 1 && fit >= 16 ? 16 : 8;
-        kb = fit / gran * gran;
-        kb = kb < 8 ? 8 : kb;
-        const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of gran
-        kb = (((nb + n_chunks - 1) / n_chunks + gran - 1) / gran) * gran;
-    }
-    a.kb_max = kb < nb ? kb : nb;
     static const int contig_env = env_int("B200Q_CONTIG", 1);
-    bool same_type = true;
-    for (int i = 1; i < c.n_segs; i++) {
-        same_type = same_type && c.seg[i].type == c.seg[0].type;
-    }
-    a.contig = (contig_env && a.kb_max == nb && same_type) ? 1 : 0;
-    if (a.contig) {
-        a.slot_bytes = nb * max_sbb;
-        a.tile_bytes = ((kRows * a.slot_bytes + 32 + 15) / 16) * 16;
-    } else {
-        a.slot_bytes = ((a.kb_max * max_sbb + 32 + 15) / 16) * 16;
-        a.tile_bytes = kRows * a.slot_bytes;
+    a.tile_bytes = 0;
+    for (int i = 0; i < c.n_segs; i++) {
+        const int type = c.seg[i].type, sbb = sb_bytes((uint32_t)type);
+        SegTile & st = a.seg_tile[i];
+        int kb;
+        if (kb_env > 0) {
+            kb = kb_env;
+        } else if ((size_t)kRows * nb * sbb + 48 <= room) {
+            kb = nb;
+        } else {
+            // a single-token pass of a warp covers 16 superblocks of Q4_K/Q5_K/Q6_K (two units each)
+            const int fit = (int)((room / kRows - 48) / sbb);
+            const bool half_units = type == kQ4_K || type == kQ5_K || type == kQ6_K;
+            const int gran = TT == 1 && half_units && fit >= 16 ? 16 : 8;
+            kb = fit / gran * gran;
+            kb = kb < 8 ? 8 : kb;
+            const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of gran
+            kb = (((nb + n_chunks - 1) / n_chunks + gran - 1) / gran) * gran;
+        }
+        st.kb_max = (int16_t)(kb < nb ? kb : nb);
+        st.contig = (contig_env && st.kb_max == nb) ? 1 : 0;
+        st.slot_bytes = ((st.kb_max * sbb + 32 + 15) / 16) * 16;
+        const int tile = st.contig ? ((kRows * nb * sbb + 32 + 15) / 16) * 16 : kRows * st.slot_bytes;
+        a.tile_bytes = a.tile_bytes > tile ? a.tile_bytes : tile;
     }
     const size_t pack_bytes = TT == 1 ? (size_t)nb * kPackSB : 0;
     const size_t fixed = 128 + pack_bytes;

@@ -50,8 +50,9 @@ __device__ __forceinline__ void consume_tile1(uint32_t slot0, uint32_t slot_stri
     if (RW > 1 && 2 * m <= 32) {
         const int rpp = min(RW, 32 / m); // rows per pass
         for (int r0 = 0; r0 < RW; r0 += rpp) {
-            const int rr = lane / m, item = lane - rr * m, row = r0 + rr;
-            const bool valid = rr < rpp && row < RW;
+            const int rr = (lane >= m ? 1 : 0) + (lane >= 2 * m ? 1 : 0); // lane / m, or 2 = beyond the pass
+            const int item = lane - rr * m, row = r0 + rr;
+            const bool valid = rr < rpp && rr < 2 && row < RW;
             float t = 0.f;
             if (valid) {
                 const int b = full * SPI + item / H, uu = item % H;
