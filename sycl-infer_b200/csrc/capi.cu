@@ -110,23 +110,32 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
 
 // Kernel choice: 1..8 tokens stream the weights once through shared memory; larger
 // token counts take the general rows kernel.  B200Q_KERNEL=rows forces the latter (A/B).
-cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
-    static const bool force_rows = [] {
+static bool force_rows() {
+    static const bool v = [] {
         const char * e = getenv("B200Q_KERNEL");
         return e && strcmp(e, "rows") == 0;
     }();
-    static const int mma_from = [] { // fewest tokens that take the tensor-core kernel
+    return v;
+}
+static int mma_from() { // fewest tokens that take the tensor-core kernel
+    static const int v = [] {
         const char * e = getenv("B200Q_MMA_FROM");
         return e && *e ? atoi(e) : 9;
     }();
-    if (!force_rows && c.TB >= mma_from) {
+    return v;
+}
+bool gemv_takes_stream(const CallDev & c) {
+    return !force_rows() && c.TB < mma_from() && stream_supported(c);
+}
+cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
+    if (!force_rows() && c.TB >= mma_from()) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
-    if (!force_rows && stream_supported(c)) {
+    if (gemv_takes_stream(c)) {
         return launch_gemv_stream(s, c, pdl_secondary);
     }
     // more than 8 tokens: one tcgen05 int8 MMA per 32-value group (B200Q_KERNEL=rows: dp4a)
-    if (!force_rows && c.TB > 8) {
+    if (!force_rows() && c.TB > 8) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
     return launch_gemv_rows(s, c, pdl_secondary);
@@ -203,6 +212,10 @@ int b200q_quant_gemv(void * stream, const b200q_seg * segs, int n_segs, int TB, 
             set_error("b200q_quant_gemv: segment %d does not share the call's activation", i);
             return B200Q_EINVAL;
         }
+    }
+    if (gemv_takes_stream(c) && stream_quantizes(c, s0.act_up)) { // one launch: the GEMV quantizes in its prologue
+        B200Q_CUDA_OK(launch_gemv_stream((cudaStream_t)stream, c, true, s0.x));
+        return B200Q_OK;
     }
     B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
                             s0.K, true));

@@ -44,6 +44,7 @@ struct StreamArgs {
     int32_t stages;
     int32_t tile_bytes; // shared bytes reserved per tile (the largest segment's)
     CostSplit cost; // the call's cost over the grid, for the row split
+    const float * xq_x; // single token: when set, every CTA quantizes this fp32 activation itself
     int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
 
@@ -224,7 +225,11 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     // The weight copies above do not depend on the activation quantizer; all below does.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if constexpr (TT == 1) {
-        stage_pack(pack, a.c, 0, nb, threadIdx.x, 32 * kConsumerWarps);
+        if (a.xq_x) {
+            stage_pack_quant(pack, a.c, a.xq_x, 8 * nb, threadIdx.x, 32 * kConsumerWarps, blockIdx.x == 0);
+        } else {
+            stage_pack(pack, a.c, 0, nb, threadIdx.x, 32 * kConsumerWarps);
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory");
     }
     using AS = typename std::conditional<TT == 1, PackA, GlobA>::type;
@@ -352,9 +357,17 @@ bool stream_supported(const CallDev & c) {
     return c.TB >= 1 && c.TB <= 8 && c.K <= 24576 && cost_split(c, 2 * kSMs, cs);
 }
 
-cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
+bool stream_quantizes(const CallDev & c, const float * act_up) {
+    // every CTA repeats the quantizer: worth it for short plain activations only (the fused
+    // silu(x)*up form evaluates a double-precision exp per value)
+    static const int lim = env_int("B200Q_FUSE_XQ_MAX_K", 8192);
+    return c.TB == 1 && !act_up && c.K <= lim && stream_supported(c);
+}
+
+cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary, const float * xq_x) {
     StreamArgs a;
     a.c = c;
+    a.xq_x = xq_x;
     static const int rw_env = env_int("B200Q_RW", 0);
     if (c.TB == 1) {
         // two rows per warp share every activation load; one row per warp gives twice the

@@ -8,7 +8,9 @@ cudaError_t launch_xq(cudaStream_t s, const float * x, const float * up, int x_s
                       float * xmeta, int32_t * xsumq, int TB, int K, bool pdl_primary);
 cudaError_t launch_gemv_rows(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 bool stream_supported(const CallDev & call);
-cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary);
+// xq_x != nullptr (single token, see stream_quantizes): the kernel quantizes that fp32 activation itself
+cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary, const float * xq_x = nullptr);
+bool stream_quantizes(const CallDev & call, const float * act_up);
 cudaError_t read_device_status(int * status, bool clear);
 cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 cudaError_t read_mma_status(int * status, bool clear);
@@ -36,5 +38,6 @@ cudaError_t read_peer_status(int * status, bool clear);
 int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, const float * xmeta,
                const int32_t * xsumq, CallDev & c);
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary);
+bool gemv_takes_stream(const CallDev & c);
 
 } // namespace b200q

@@ -3,6 +3,7 @@
 #pragma once
 #include "async.cuh"
 #include "units.cuh"
+#include "xq.cuh"
 
 namespace b200q {
 
@@ -20,6 +21,38 @@ __device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int
         sts128(p, x0.x, x0.y, x0.z, x0.w);
         sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
         sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
+    }
+}
+
+// The same pack straight from the fp32 activation: every CTA quantizes the whole vector
+// itself (one thread per 32-value group, the standalone quantizer's arithmetic), which removes
+// a kernel and a global round trip from the critical path between two GEMV calls.  CTA 0 also
+// writes the caller's scratch views, so they hold the quantized activation as after b200q_xq.
+__device__ __forceinline__ void stage_pack_quant(uint32_t pack, const CallDev & c, const float * x, int n_groups,
+                                                 int tid, int nthr, bool write_views) {
+    for (int g = tid; g < n_groups; g += nthr) {
+        float v[32];
+        const float4 * src = reinterpret_cast<const float4 *>(x + (size_t)g * 32);
+#pragma unroll
+        for (int i = 0; i < 8; i++) { // a thread's eight loads share one 128-byte line
+            const float4 f = src[i];
+            v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+        }
+        uint32_t q[8];
+        float sx;
+        int s0, s1;
+        xq_group_thread(v, q, sx, s0, s1);
+        const uint32_t p = pack_addr(pack, g);
+        sts128(p, q[0], q[1], q[2], q[3]);
+        sts128(p + 16, q[4], q[5], q[6], q[7]);
+        sts128(p + 32, __float_as_uint(sx), (uint32_t)s0, (uint32_t)s1, __float_as_uint(sx * (float)(s0 + s1)));
+        if (write_views) {
+            uint4 * d8 = reinterpret_cast<uint4 *>(const_cast<int8_t *>(c.x8) + (size_t)g * 32);
+            d8[0] = make_uint4(q[0], q[1], q[2], q[3]);
+            d8[1] = make_uint4(q[4], q[5], q[6], q[7]);
+            reinterpret_cast<float2 *>(const_cast<float *>(c.xmeta))[g] = make_float2(sx, 0.0f);
+            reinterpret_cast<int2 *>(const_cast<int32_t *>(c.xsumq))[g] = make_int2(s0, s1);
+        }
     }
 }
 

@@ -26,4 +26,36 @@ __device__ __forceinline__ int xq_group(float a, int lane, float & scale, int & 
     return q;
 }
 
+// The same arithmetic with one THREAD per group: v[0..31] in registers, no warp-wide
+// reductions (max and integer sums are exact in any order).  Returns the 32 codes packed four
+// per word (element i in byte i%4 of word i/4).
+__device__ __forceinline__ void xq_group_thread(const float (&v)[32], uint32_t (&codes)[8], float & scale, int & s0,
+                                                int & s1) {
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        mx = fmaxf(mx, fabsf(v[i]));
+    }
+    const float inv = mx > 0.0f ? __fdiv_rn(127.0f, mx) : 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const float r = fminf(127.0f, fmaxf(-127.0f, roundf(__fmul_rn(v[4 * w + b], inv))));
+            word |= ((uint32_t)(int)r & 0xFFu) << (8 * b);
+        }
+        codes[w] = word;
+    }
+    int a = 0, b = 0;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        a = __dp4a((int)codes[w], 0x01010101, a);
+        b = __dp4a((int)codes[4 + w], 0x01010101, b);
+    }
+    s0 = a;
+    s1 = b;
+    scale = h2f(f2h_trunc(mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 0.0f));
+}
+
 } // namespace b200q

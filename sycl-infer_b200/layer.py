@@ -95,4 +95,6 @@ class DenseLayer:
         return out
 
     def launches_per_step(self):
-        return 8  # 4 calls x (activation quantizer + GEMV)
+        # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue (one launch
+        # each), down keeps the separate silu(gate)*up quantizer; otherwise a quantizer + GEMV per call
+        return 5 if self.TB == 1 and self.arena is None else 8

@@ -242,3 +242,28 @@ def test_errors_are_reported_not_swallowed(be, pkg):
 def test_zy_no_device_side_wait_ran_out(be):
     """Every mbarrier wait in the streaming kernel is bounded; none may have expired."""
     assert be.device_status() == 0
+
+
+@pytest.mark.parametrize("t,K,N", [(12, 1024, 300), (14, 5120, 77), (23, 2048, 64), (13, 8192, 40)])
+def test_quant_gemv_single_token_quantizes_in_kernel(be, orc, pkg, t, K, N):
+    """One token, plain activation, short K: the GEMV kernel quantizes in its prologue (one
+    launch).  Outputs against the oracle; the scratch views must hold the quantizer's exact
+    codes, scales and sums all the same."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    x = pkg.synth.make_activation(1, K, 900 + t)
+    res = pkg.synth.make_activation(1, N, 901)
+    w = pkg.synth.make_weight(t, N, K, 902 + t)
+    a = orc.xq(x)
+    x8, xm, xs = alloc_act(1, K)
+    o = torch.zeros(N, dtype=torch.float32, device="cuda")
+    seg = gemv_seg(w=dev(w), type=t, K=K, n_rows=N, x=dev(x), x_stride=K, out=o, out_stride=N, residual=dev(res),
+                   alpha=0.5, x8=x8, xmeta=xm, xsumq=xs)
+    be.quant_gemv([seg], 1)
+    be.synchronize()
+    assert be.device_status() == 0
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    assert np.array_equal(xm.cpu().numpy(), a.xmeta)
+    assert np.array_equal(xs.cpu().numpy(), a.xsumq)
+    ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=0.5)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=0.5) + np.abs(res)
+    assert rel_err(o.cpu().numpy().reshape(1, N), ref, ab) <= TOL
