@@ -97,4 +97,6 @@ class DenseLayer:
     def launches_per_step(self):
         # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue (one launch
         # each), down keeps the separate silu(gate)*up quantizer; otherwise a quantizer + GEMV per call
-        return 5 if self.TB == 1 and self.arena is None else 8
+        if self.arena is not None:
+            return 12  # quantizer + GEMV with peer stores + flag barrier, per call
+        return 5 if self.TB == 1 else 8
