@@ -251,8 +251,8 @@ template <> struct WUnit<kQ5_K> : WUnitK45<kQ5_K> {};
 // four 6-bit (scale, min) pairs of a half unpack with a handful of 32-bit operations
 // (bytes 0-3 / 4-7 hold groups 0-3 directly; groups 4-7 take four bits from bytes 8-11 and
 // two from the top of bytes 0-7), and the fp32 work is factored as
-//   d * sum_g sc_g * (sx_g * wd_g)  -  dmin * sum_g m_g * (sx_g * xsum_g)
-// so only two multiplies per superblock half touch d and dmin.
+//   d * sum_g sx_g * float(sc_g * wd_g)  -  dmin * sum_g m_g * (sx_g * xsum_g)
+// (sc_g * wd_g is an exact integer) so only two multiplies per superblock half touch d and dmin.
 template <int TYPE> struct HalfK45 {
     static constexpr int kHiShift = TYPE == kQ4_K ? 4 : 3;
     static constexpr float kHiScale = TYPE == kQ4_K ? 0.0625f : 0.125f;
@@ -305,14 +305,16 @@ template <int TYPE> struct HalfK45 {
         float ve = 0.f, vo = 0.f, ms = 0.f;
 #pragma unroll
         for (int g = 0; g < 4; g++) {
-            const float scf = (float)((sc >> (8 * g)) & 0xFF), mnf = (float)((mn >> (8 * g)) & 0xFF);
-            const float u = a.sx[g] * (float)w[g];
+            // the 6-bit scale times the group's sum as an integer (below 2^22, times 16 for odd
+            // groups: exactly representable), so one conversion and one FMA apply the scale
+            const int scg = (int)__byte_perm(sc, 0, 0x4440 + g), mng = (int)__byte_perm(mn, 0, 0x4440 + g);
+            const float t = (float)(scg * w[g]);
             if (g & 1) {
-                vo = fmaf(scf, u, vo);
+                vo = fmaf(a.sx[g], t, vo);
             } else {
-                ve = fmaf(scf, u, ve);
+                ve = fmaf(a.sx[g], t, ve);
             }
-            ms = fmaf(mnf, a.c[g], ms);
+            ms = fmaf((float)mng, a.c[g], ms);
         }
         const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
         return d * fmaf(vo, kHiScale, ve) - dmin * ms;
