@@ -202,6 +202,54 @@ __device__ __forceinline__ void unpack_slot(const uint8_t * sb, int h, int r, bo
                 sts32(rb + 4 * g * kTileM, __float_as_uint(dmin * mnf));
             }
         }
+    } else if constexpr (TYPE == kQ6_K) {
+        // half h of the superblock: ql[64h..], qh[32h..], scales[8h..]; step 2*plane + hs holds
+        // the 16 codes of plane `plane`, elements 16hs..16hs+15, in its half of the operand
+        // row and zeros in the other half (the block is 2-byte aligned: aligned words, funnel shift)
+        const uint32_t sa = smem_u32(sb);
+        const uint32_t sh = (sa & 2u) * 8, q = (sa & ~3u) + 64u * h, qhp = (sa & ~3u) + 128u + 32u * h;
+#pragma unroll
+        for (int hs = 0; hs < 2; hs++) {
+            uint32_t v[4][4] = {};
+            if (row_ok) {
+                uint32_t wa[5], wb[5], wh[5];
+#pragma unroll
+                for (int k = 0; k < 5; k++) {
+                    wa[k] = lds32(q + 16 * hs + 4 * k);
+                    wb[k] = lds32(q + 32 + 16 * hs + 4 * k);
+                    wh[k] = lds32(qhp + 16 * hs + 4 * k);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const uint32_t qa = __funnelshift_r(wa[k], wa[k + 1], sh), qb = __funnelshift_r(wb[k], wb[k + 1], sh);
+                    const uint32_t hh = __funnelshift_r(wh[k], wh[k + 1], sh);
+                    v[0][k] = (qa & 0x0F0F0F0Fu) | ((hh << 4) & 0x30303030u);
+                    v[1][k] = (qb & 0x0F0F0F0Fu) | ((hh << 2) & 0x30303030u);
+                    v[2][k] = ((qa >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u);
+                    v[3][k] = ((qb >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u);
+                }
+            }
+#pragma unroll
+            for (int pl = 0; pl < 4; pl++) {
+                const uint32_t as = a0 + (uint32_t)((2 * pl + hs) * kTileM * 32);
+                sts128(as + core_off(r, hs), v[pl][0], v[pl][1], v[pl][2], v[pl][3]);
+                sts128(as + core_off(r, 1 - hs), 0, 0, 0, 0);
+            }
+        }
+        float d = 0.f;
+        uint32_t sc[2] = {0, 0};
+        if (row_ok) {
+            const uint32_t sp = (sa & ~3u) + 192u + 8u * h;
+            const uint32_t c0 = lds32(sp), c1 = lds32(sp + 4), c2 = lds32(sp + 8);
+            sc[0] = __funnelshift_r(c0, c1, sh);
+            sc[1] = __funnelshift_r(c1, c2, sh);
+            d = h2f((uint16_t)lds16(sa + 208));
+        }
+#pragma unroll
+        for (int st = 0; st < kSlotSteps; st++) { // scales[8h + st] belongs to step st
+            const int s8 = (int)(int8_t)(sc[st >> 2] >> (8 * (st & 3)));
+            sts32(ra + 4 * st * kTileM, __float_as_uint(d * (float)s8));
+        }
     } else {
 #pragma unroll 1
         for (int st = 0; st < kSlotSteps; st++) {
@@ -416,13 +464,18 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
             }
             const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(accb * NT + c0);
             const uint32_t tok = base + 4 * (st * NT + c0);
+            constexpr int CH = NC >= 16 ? 16 : 8; // columns per tensor-memory read
 #pragma unroll
-            for (int j = 0; j < NC; j += 16) {
-                uint32_t v[16];
-                tmem_ld16(taddr + j, v);
+            for (int j = 0; j < NC; j += CH) {
+                uint32_t v[CH];
+                if constexpr (CH == 16) {
+                    tmem_ld16(taddr + j, v);
+                } else {
+                    tmem_ld8(taddr + j, v);
+                }
                 tmem_ld_wait();
 #pragma unroll
-                for (int q = 0; q < 16; q += 4) {
+                for (int q = 0; q < CH; q += 4) {
                     const uint4 ta = lds128(tok + Slot<NT>::TOKA + 4 * (j + q));
                     const uint64_t sx[2] = {(uint64_t)ta.x | ((uint64_t)ta.y << 32), (uint64_t)ta.z | ((uint64_t)ta.w << 32)};
                     uint64_t tc[2] = {0ull, 0ull}, tb[2] = {0ull, 0ull};
@@ -617,6 +670,13 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     a.lbo = 128;
     a.sbo = 256;
     const bool pg2 = a.raw_bytes <= (c.TB <= 32 ? 240 : 192); // a second producer group where its staging fits
+    // token tile: the fp32 epilogue costs in proportion to its width, so it is as narrow as the call allows
+    if (c.TB <= 8) {
+        return pg2 ? launch_nt<8, 1, 2>(s, a, pdl_secondary) : launch_nt<8, 1, 1>(s, a, pdl_secondary);
+    }
+    if (c.TB <= 16) {
+        return pg2 ? launch_nt<16, 1, 2>(s, a, pdl_secondary) : launch_nt<16, 1, 1>(s, a, pdl_secondary);
+    }
     if (c.TB <= 32) { // batched decode: unpacking dominates
         return pg2 ? launch_nt<32, 2, 2>(s, a, pdl_secondary) : launch_nt<32, 2, 1>(s, a, pdl_secondary);
     }
