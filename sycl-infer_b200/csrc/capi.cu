@@ -108,8 +108,9 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
     return B200Q_OK;
 }
 
-// Kernel choice: 1..8 tokens stream the weights once through shared memory; larger
-// token counts take the general rows kernel.  B200Q_KERNEL=rows forces the latter (A/B).
+// Kernel choice: one or two tokens (three for the types without a fast tensor-core unpack)
+// stream the weights once through shared memory and dp4a; more tokens take the tcgen05
+// kernel.  B200Q_KERNEL=rows forces the general warp-per-row kernel (A/B).
 static bool force_rows() {
     static const bool v = [] {
         const char * e = getenv("B200Q_KERNEL");
@@ -117,18 +118,31 @@ static bool force_rows() {
     }();
     return v;
 }
-static int mma_from() { // fewest tokens that take the tensor-core kernel
-    static const int v = [] {
+// Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
+// needs 35 us for two tokens and 64 / 132 / 330 us for three / four / eight (every token repeats the
+// dp4a work), the tensor-core kernel a flat 41 us up to eight tokens (Q4_K; Q5_K, IQ4_XS and
+// Q8_0 cross over at three tokens as well; Q6_K: 33 / 92 us against 94 us).  B200Q_MMA_FROM overrides.
+static int mma_from(const CallDev & c) {
+    static const int env = [] {
         const char * e = getenv("B200Q_MMA_FROM");
-        return e && *e ? atoi(e) : 9;
+        return e && *e ? atoi(e) : 0;
     }();
-    return v;
+    if (env > 0) {
+        return env;
+    }
+    int from = 3;
+    for (int i = 0; i < c.n_segs; i++) {
+        if (c.seg[i].type == kQ6_K) {
+            from = 4; // twice the MMA steps per superblock: the crossover is one token later
+        }
+    }
+    return from;
 }
 bool gemv_takes_stream(const CallDev & c) {
-    return !force_rows() && c.TB < mma_from() && stream_supported(c);
+    return !force_rows() && c.TB < mma_from(c) && stream_supported(c);
 }
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
-    if (!force_rows() && c.TB >= mma_from()) {
+    if (!force_rows() && c.TB >= mma_from(c)) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
     if (gemv_takes_stream(c)) {
@@ -408,6 +422,9 @@ int b200q_device_status(int * status, int clear) {
     int peer = 0;
     B200Q_CUDA_OK(read_peer_status(&peer, clear != 0));
     *status = *status ? *status : peer;
+    int moe = 0;
+    B200Q_CUDA_OK(read_moe_status(&moe, clear != 0));
+    *status = *status ? *status : moe;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

@@ -13,35 +13,57 @@
 namespace b200q {
 
 // ---- router --------------------------------------------------------------------------------
-// One CTA per token.  logits are given or computed as gate_inp . x with double accumulation.
-__global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
-                                                        int x_stride, int n_embd, int n_expert, int top_k,
-                                                        float * __restrict__ logits, int32_t * __restrict__ ids,
-                                                        float * __restrict__ wts) {
+// Logits gate_inp . x with double accumulation: one warp per expert, up to kRouteTok tokens per
+// pass, so a router row is read once for all of them and the grid covers the experts (a CTA
+// per token would leave most SMs idle and re-read the whole router for every token).
+constexpr int kRouteTok = 16;
+__global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
+                                                         int x_stride, int n_tok, int n_embd, int n_expert,
+                                                         float * __restrict__ logits) {
+    const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (e >= n_expert) {
+        return;
+    }
+    const float * w = gate_inp + (size_t)e * n_embd;
+    for (int t0 = 0; t0 < n_tok; t0 += kRouteTok) {
+        double a[kRouteTok];
+#pragma unroll
+        for (int i = 0; i < kRouteTok; i++) {
+            a[i] = 0.0;
+        }
+        for (int k = lane; k < n_embd; k += 32) {
+            const double wk = (double)__ldg(w + k);
+#pragma unroll
+            for (int i = 0; i < kRouteTok; i++) {
+                if (t0 + i < n_tok) { // uniform
+                    a[i] += wk * (double)__ldg(x + (size_t)(t0 + i) * x_stride + k);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kRouteTok; i++) {
+            for (int o = 16; o > 0; o >>= 1) {
+                a[i] += __shfl_xor_sync(0xFFFFFFFFu, a[i], o);
+            }
+            if (lane == 0 && t0 + i < n_tok) {
+                logits[(size_t)(t0 + i) * n_expert + e] = (float)a[i];
+            }
+        }
+    }
+}
+
+// Softmax and top-k of one token's logits (one CTA per token); the logits come from memory.
+__global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ x, int x_stride, int n_embd,
+                                                        int n_expert, int top_k, float * __restrict__ logits,
+                                                        int32_t * __restrict__ ids, float * __restrict__ wts) {
     extern __shared__ float p[]; // n_expert probabilities, then n_expert selection flags
     int * sel = reinterpret_cast<int *>(p + n_expert);
     __shared__ float s_max, s_inv, s_den;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     float * lg = logits + (size_t)t * n_expert;
-    if (gate_inp) {
-        const float * xr = x + (size_t)t * x_stride;
-        for (int e = warp; e < n_expert; e += nw) {
-            const float * w = gate_inp + (size_t)e * n_embd;
-            double a = 0.0;
-            for (int k = lane; k < n_embd; k += 32) {
-                a += (double)w[k] * (double)xr[k];
-            }
-            for (int o = 16; o > 0; o >>= 1) {
-                a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
-            }
-            if (lane == 0) {
-                p[e] = (float)a;
-            }
-        }
-    } else {
-        for (int e = tid; e < n_expert; e += blockDim.x) {
-            p[e] = lg[e];
-        }
+    (void)x, (void)x_stride, (void)n_embd, (void)lane, (void)warp, (void)nw;
+    for (int e = tid; e < n_expert; e += blockDim.x) {
+        p[e] = lg[e];
     }
     __syncthreads();
     if (tid == 0) {
@@ -103,31 +125,35 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
 __global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict__ ids, int n_pairs, int n_expert,
                                                       int32_t * off, int32_t * pair, int32_t * active,
                                                       int32_t * n_active) {
+    extern __shared__ int32_t cnt[]; // n_expert + 1 counts, then their exclusive prefix in place
     for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
-        off[e] = 0;
+        cnt[e] = 0;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
         const int e = ids[i];
         if (e >= 0 && e < n_expert) {
-            atomicAdd(&off[e + 1], 1);
+            atomicAdd(&cnt[e + 1], 1); // integer counts: order does not matter
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0) { // n_expert is a few hundred: a serial pass over shared memory is short
         int na = 0;
         for (int e = 0; e < n_expert; e++) {
-            if (off[e + 1] > 0) {
+            if (cnt[e + 1] > 0) {
                 active[na++] = e;
             }
-            off[e + 1] += off[e];
+            cnt[e + 1] += cnt[e];
         }
         *n_active = na;
     }
     __syncthreads();
+    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
+        off[e] = cnt[e];
+    }
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) { // deterministic fill in pair order
-        int o = off[e];
-        const int end = off[e + 1];
+        int o = cnt[e];
+        const int end = cnt[e + 1];
         for (int i = 0; i < n_pairs && o < end; i++) {
             if (ids[i] == e) {
                 pair[o++] = i;
@@ -256,14 +282,18 @@ __global__ void __launch_bounds__(256) moe_reduce_kernel(const float * __restric
 // ---- launchers -----------------------------------------------------------------------------------
 cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
                              int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts) {
-    moe_route_kernel<<<n_tok, 256, (size_t)n_expert * 8, s>>>(gate_inp, x, x_stride, n_embd, n_expert, top_k, logits,
-                                                              ids, wts);
+    if (gate_inp) {
+        moe_logits_kernel<<<(unsigned)((n_expert + 7) / 8), 256, 0, s>>>(gate_inp, x, x_stride, n_tok, n_embd, n_expert,
+                                                                         logits);
+    }
+    moe_route_kernel<<<n_tok, 256, (size_t)n_expert * 8, s>>>(x, x_stride, n_embd, n_expert, top_k, logits, ids, wts);
     return cudaGetLastError();
 }
 
 cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
                            int32_t * pair, int32_t * active, int32_t * n_active) {
-    moe_csr_kernel<<<1, 256, 0, s>>>(ids, n_pairs, n_expert, off, pair, active, n_active);
+    moe_csr_kernel<<<1, 256, (size_t)(n_expert + 1) * sizeof(int32_t), s>>>(ids, n_pairs, n_expert, off, pair, active,
+                                                                            n_active);
     return cudaGetLastError();
 }
 
@@ -272,6 +302,12 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
                             const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                             const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
                             float * out, int out_stride, int fuse_silu) {
+    // decode (at most a few routed tokens per expert on average): the streaming kernel
+    const long long n_pairs = top_k > 0 ? (long long)TB * top_k : TB;
+    if (n_pairs <= 4LL * n_act_max && moe_stream_supported(type_a, type_b, K, n_rows, fuse_silu)) {
+        return launch_moe_stream(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max,
+                                 x8, xmeta, xsumq, TB, top_k, K, n_rows, out, out_stride, fuse_silu);
+    }
     MoeArgs m;
     m.bank_a = static_cast<const uint8_t *>(bank_a);
     m.bank_b = static_cast<const uint8_t *>(bank_b);

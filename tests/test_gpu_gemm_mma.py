@@ -24,7 +24,8 @@ def _gemm(be, t, w, K, N, act, TB, residual=None, alpha=1.0):
 
 
 @pytest.mark.parametrize("t", (12, 13, 14, 8, 23))
-@pytest.mark.parametrize("TB,N,K", [(16, 128, 256), (32, 200, 512), (9, 37, 1024), (130, 260, 512), (256, 128, 768)])
+@pytest.mark.parametrize("TB,N,K", [(16, 128, 256), (32, 200, 512), (9, 37, 1024), (130, 260, 512), (256, 128, 768),
+                                    (4, 300, 512), (8, 129, 1280), (5, 64, 256)])
 def test_mma_gemm_parity(be, orc, pkg, t, TB, N, K):
     w = pkg.synth.make_weight(t, N, K, 1200 + t)
     a = orc.xq(pkg.synth.make_activation(TB, K, 1201), None, TB)
