@@ -13,17 +13,19 @@
 namespace b200q {
 
 // ---- router --------------------------------------------------------------------------------
-// Logits gate_inp . x with double accumulation: one warp per expert, up to kRouteTok tokens per
-// pass, so a router row is read once for all of them and the grid covers the experts (a CTA
-// per token would leave most SMs idle and re-read the whole router for every token).
+// Logits gate_inp . x with double accumulation: one CTA per expert, its warps splitting K, up to
+// kRouteTok tokens per pass - a router row is read once for all tokens, every load of a pass is
+// independent, and the grid covers the experts (a CTA per token would leave most SMs idle and
+// re-read the whole router for every token).
 constexpr int kRouteTok = 16;
 __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
                                                          int x_stride, int n_tok, int n_embd, int n_expert,
                                                          float * __restrict__ logits) {
-    const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (e >= n_expert) {
-        return;
-    }
+    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ double part[8][kRouteTok];
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float * w = gate_inp + (size_t)e * n_embd;
     for (int t0 = 0; t0 < n_tok; t0 += kRouteTok) {
         double a[kRouteTok];
@@ -31,7 +33,7 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
         for (int i = 0; i < kRouteTok; i++) {
             a[i] = 0.0;
         }
-        for (int k = lane; k < n_embd; k += 32) {
+        for (int k = threadIdx.x; k < n_embd; k += 256) {
             const double wk = (double)__ldg(w + k);
 #pragma unroll
             for (int i = 0; i < kRouteTok; i++) {
@@ -45,10 +47,19 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
             for (int o = 16; o > 0; o >>= 1) {
                 a[i] += __shfl_xor_sync(0xFFFFFFFFu, a[i], o);
             }
-            if (lane == 0 && t0 + i < n_tok) {
-                logits[(size_t)(t0 + i) * n_expert + e] = (float)a[i];
+            if (lane == 0) {
+                part[warp][i] = a[i];
             }
         }
+        __syncthreads();
+        if (threadIdx.x < kRouteTok && t0 + (int)threadIdx.x < n_tok) {
+            double sum = 0.0;
+            for (int j = 0; j < 8; j++) { // fixed order
+                sum += part[j][threadIdx.x];
+            }
+            logits[(size_t)(t0 + threadIdx.x) * n_expert + e] = (float)sum;
+        }
+        __syncthreads();
     }
 }
 
@@ -56,6 +67,9 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
 __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ x, int x_stride, int n_embd,
                                                         int n_expert, int top_k, float * __restrict__ logits,
                                                         int32_t * __restrict__ ids, float * __restrict__ wts) {
+    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ float p[]; // n_expert probabilities, then n_expert selection flags
     int * sel = reinterpret_cast<int *>(p + n_expert);
     __shared__ float s_max, s_inv, s_den;
@@ -124,38 +138,65 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
 // increasing pair order; active[0..n_active) lists the experts with at least one pair.
 __global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict__ ids, int n_pairs, int n_expert,
                                                       int32_t * off, int32_t * pair, int32_t * active,
-                                                      int32_t * n_active) {
-    extern __shared__ int32_t cnt[]; // n_expert + 1 counts, then their exclusive prefix in place
+                                                      int32_t * n_active, int ids_in_smem) {
+    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    extern __shared__ int32_t cnt[]; // n_expert + 1 counts -> their prefix; then the active flags' prefix; then ids
+    int32_t * act = cnt + n_expert + 1;
+    int32_t * sid = act + n_expert + 1;
     for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
         cnt[e] = 0;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
         const int e = ids[i];
+        if (ids_in_smem) {
+            sid[i] = e;
+        }
         if (e >= 0 && e < n_expert) {
             atomicAdd(&cnt[e + 1], 1); // integer counts: order does not matter
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) { // n_expert is a few hundred: a serial pass over shared memory is short
-        int na = 0;
-        for (int e = 0; e < n_expert; e++) {
-            if (cnt[e + 1] > 0) {
-                active[na++] = e;
+    if (threadIdx.x < 32) { // warp 0: inclusive scans of the counts and of the "has pairs" flags, 32 at a time
+        int carry = 0, acarry = 0;
+        for (int e0 = 0; e0 < n_expert; e0 += 32) {
+            const int e = e0 + threadIdx.x;
+            const int c = e < n_expert ? cnt[e + 1] : 0;
+            int v = c, f = c > 0 ? 1 : 0;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xFFFFFFFFu, v, o), g = __shfl_up_sync(0xFFFFFFFFu, f, o);
+                if ((int)threadIdx.x >= o) {
+                    v += u;
+                    f += g;
+                }
             }
-            cnt[e + 1] += cnt[e];
+            if (e < n_expert) {
+                cnt[e + 1] = carry + v;
+                act[e + 1] = acarry + f; // experts with pairs among 0..e
+            }
+            carry += __shfl_sync(0xFFFFFFFFu, v, 31);
+            acarry += __shfl_sync(0xFFFFFFFFu, f, 31);
         }
-        *n_active = na;
+        if (threadIdx.x == 0) {
+            act[0] = 0;
+            *n_active = acarry;
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
         off[e] = cnt[e];
     }
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) { // deterministic fill in pair order
+    const int32_t * idv = ids_in_smem ? sid : ids;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        if (act[e + 1] > act[e]) {
+            active[act[e]] = e; // increasing expert order
+        }
         int o = cnt[e];
         const int end = cnt[e + 1];
-        for (int i = 0; i < n_pairs && o < end; i++) {
-            if (ids[i] == e) {
+        for (int i = 0; i < n_pairs && o < end; i++) { // deterministic fill in pair order
+            if (idv[i] == e) {
                 pair[o++] = i;
             }
         }
@@ -266,6 +307,9 @@ __global__ void __launch_bounds__(256) moe_rows_kernel(const __grid_constant__ M
 __global__ void __launch_bounds__(256) moe_reduce_kernel(const float * __restrict__ acc, const float * __restrict__ wts,
                                                          int top_k, int n_tok, int n_embd, int acc_stride, float * out,
                                                          int out_stride) {
+    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)n_tok * n_embd) {
         return;
@@ -280,21 +324,42 @@ __global__ void __launch_bounds__(256) moe_reduce_kernel(const float * __restric
 }
 
 // ---- launchers -----------------------------------------------------------------------------------
+// every launch is programmatically chained to its predecessor in the stream (the kernels wait
+// for it themselves before reading its results)
+template <class... KArgs, class... Args>
+static cudaError_t launch_chained(cudaStream_t s, void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
+}
+
 cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
                              int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts) {
     if (gate_inp) {
-        moe_logits_kernel<<<(unsigned)((n_expert + 7) / 8), 256, 0, s>>>(gate_inp, x, x_stride, n_tok, n_embd, n_expert,
-                                                                         logits);
+        cudaError_t e = launch_chained(s, moe_logits_kernel, dim3((unsigned)n_expert), dim3(256), 0, gate_inp, x, x_stride, n_tok,
+                                       n_embd, n_expert, logits);
+        if (e != cudaSuccess) {
+            return e;
+        }
     }
-    moe_route_kernel<<<n_tok, 256, (size_t)n_expert * 8, s>>>(x, x_stride, n_embd, n_expert, top_k, logits, ids, wts);
-    return cudaGetLastError();
+    return launch_chained(s, moe_route_kernel, dim3((unsigned)n_tok), dim3(256), (size_t)n_expert * 8, x, x_stride, n_embd,
+                          n_expert, top_k, logits, ids, wts);
 }
 
 cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
                            int32_t * pair, int32_t * active, int32_t * n_active) {
-    moe_csr_kernel<<<1, 256, (size_t)(n_expert + 1) * sizeof(int32_t), s>>>(ids, n_pairs, n_expert, off, pair, active,
-                                                                            n_active);
-    return cudaGetLastError();
+    const int in_smem = n_pairs <= 8192 ? 1 : 0;
+    const size_t smem = (size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) * sizeof(int32_t);
+    return launch_chained(s, moe_csr_kernel, dim3(1), dim3(256), smem, ids, n_pairs, n_expert, off, pair, active, n_active,
+                          in_smem);
 }
 
 cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
@@ -304,7 +369,7 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
                             float * out, int out_stride, int fuse_silu) {
     // decode (at most a few routed tokens per expert on average): the streaming kernel
     const long long n_pairs = top_k > 0 ? (long long)TB * top_k : TB;
-    if (n_pairs <= 4LL * n_act_max && moe_stream_supported(type_a, type_b, K, n_rows, fuse_silu)) {
+    if (n_pairs <= 4LL * n_act_max && n_act_max <= 1023 && moe_stream_supported(type_a, type_b, K, n_rows, fuse_silu)) {
         return launch_moe_stream(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max,
                                  x8, xmeta, xsumq, TB, top_k, K, n_rows, out, out_stride, fuse_silu);
     }
@@ -337,9 +402,8 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
 cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
                               int acc_stride, float * out, int out_stride) {
     const long long n = (long long)n_tok * n_embd;
-    moe_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(acc, wts, top_k, n_tok, n_embd, acc_stride, out,
-                                                                 out_stride);
-    return cudaGetLastError();
+    return launch_chained(s, moe_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, acc, wts, top_k, n_tok, n_embd,
+                          acc_stride, out, out_stride);
 }
 
 } // namespace b200q

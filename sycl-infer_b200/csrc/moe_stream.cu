@@ -46,6 +46,7 @@ struct MoeStreamArgs {
     int32_t rows_per_tile, tiles_per_expert;
     int32_t half_bytes;     // shared bytes of one plane's part of a tile
     int32_t tile_bytes, stages;
+    int32_t max_active;     // bound on the active experts (sizes the shared prefix array)
     int32_t units_per_row;  // down, short K: lanes cover (row, unit); 0 = two rows per warp over all of K
 };
 
@@ -64,9 +65,8 @@ __device__ __forceinline__ void stage_pack_tok(uint32_t pack, const MoeStreamArg
     }
 }
 
-__device__ __forceinline__ float moe_silu(float g) { // x / (1 + expf(-x)), expf rounded once
-    const float e = (float)exp((double)(-g));
-    return __fdiv_rn(g, __fadd_rn(1.0f, e));
+__device__ __forceinline__ float moe_silu(float g) { // x / (1 + expf(-x)); expf is within an ulp of the host's
+    return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
 }
 
 // one row over all of K against the pack (any type)
@@ -134,15 +134,87 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_stream_kernel(const __grid
     __syncthreads();
     // the expert lists come from the CSR kernel, the activation from the quantizer
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t n_act = (uint32_t)*a.n_active;
-    const uint32_t T = n_act * (uint32_t)a.tiles_per_expert;
-    const uint32_t t_lo = T * blockIdx.x / gridDim.x, t_hi = T * (blockIdx.x + 1) / gridDim.x;
+    // Work split.  A tile costs as many decode passes as its expert has routed tokens, so the
+    // CTAs take equal shares of cost = sum over tiles of (pairs of the tile's expert), not of tiles.
+    // pre[s] = pairs of active experts 0..s-1 (built by every CTA; a few hundred entries).
+    const int n_act = min(*a.n_active, a.max_active);
+    int32_t * pre = reinterpret_cast<int32_t *>(smem_raw + (packs - base) + kMoeTok * pack_bytes);
+    if (warp == 0) {
+        int carry = 0;
+        for (int s0 = 0; s0 < n_act; s0 += 32) {
+            const int sl = s0 + lane;
+            int v = 0;
+            if (sl < n_act) {
+                const int e = a.active[sl];
+                v = a.off[e + 1] - a.off[e];
+            }
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xFFFFFFFFu, v, o);
+                if (lane >= o) {
+                    v += u;
+                }
+            }
+            if (sl < n_act) {
+                pre[sl + 1] = carry + v;
+            }
+            carry += __shfl_sync(0xFFFFFFFFu, v, 31);
+        }
+        if (lane == 0) {
+            pre[0] = 0;
+        }
+    }
+    __syncthreads();
+    const int tpe = a.tiles_per_expert;
+    const unsigned long long C = (unsigned long long)pre[n_act] * tpe;
+    const uint32_t c_lo = (uint32_t)(C * blockIdx.x / gridDim.x), c_hi = (uint32_t)(C * (blockIdx.x + 1) / gridDim.x);
+    // first tile whose starting cost is >= c_lo: expert slot by bisection, tile by division
+    int slot0 = 0, tile0 = 0;
+    {
+        int lo = 0, hi = n_act; // largest s with pre[s] * tpe <= c_lo
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((uint32_t)pre[mid] * (uint32_t)tpe <= c_lo) {
+                lo = mid;
+            } else {
+                hi = mid;
+            }
+        }
+        slot0 = lo;
+        if (n_act > 0) {
+            const uint32_t cnt = (uint32_t)(pre[lo + 1] - pre[lo]), rel = c_lo - (uint32_t)pre[lo] * (uint32_t)tpe;
+            tile0 = (int)((rel + cnt - 1) / cnt);
+            if (tile0 >= tpe) {
+                slot0++;
+                tile0 = 0;
+            }
+        }
+    }
+    // walks the CTA's tiles: (slot, j) with starting cost c, until c >= c_hi
+    struct Walk {
+        int slot, j;
+        uint32_t c;
+    };
+    auto walk_begin = [&]() {
+        Walk w{slot0, tile0, 0};
+        if (slot0 < n_act) {
+            w.c = (uint32_t)pre[slot0] * (uint32_t)tpe + (uint32_t)tile0 * (uint32_t)(pre[slot0 + 1] - pre[slot0]);
+        }
+        return w;
+    };
+    auto walk_valid = [&](const Walk & w) { return w.slot < n_act && w.c < c_hi; };
+    auto walk_next = [&](Walk & w) {
+        w.c += (uint32_t)(pre[w.slot + 1] - pre[w.slot]);
+        if (++w.j == tpe) {
+            w.j = 0;
+            w.slot++;
+        }
+    };
     int stage = 0;
     uint32_t phase = 0;
 
     if (warp == kConsumerWarps) { // ------------------------------------------------------ producer
-        for (uint32_t t = t_lo; t < t_hi; t++) {
-            const int slot = (int)(t / (uint32_t)a.tiles_per_expert), j = (int)(t - (uint32_t)slot * a.tiles_per_expert);
+        for (Walk w = walk_begin(); walk_valid(w); walk_next(w)) {
+            const int slot = w.slot, j = w.j;
             const int e = a.active[slot];
             const int r0 = j * a.rows_per_tile, rows = min(a.rows_per_tile, a.n_rows - r0);
             bool alive = mbar_wait(bar_empty + 8 * stage, phase ^ 1, &g_moe_status);
@@ -171,8 +243,8 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_stream_kernel(const __grid
 
     // ---------------------------------------------------------------------------------- consumers
     int staged_e = -1, staged_q = -1;
-    for (uint32_t t = t_lo; t < t_hi; t++) {
-        const int slot = (int)(t / (uint32_t)a.tiles_per_expert), j = (int)(t - (uint32_t)slot * a.tiles_per_expert);
+    for (Walk w = walk_begin(); walk_valid(w); walk_next(w)) {
+        const int slot = w.slot, j = w.j;
         const int e = a.active[slot];
         const int r0 = j * a.rows_per_tile, rows = min(a.rows_per_tile, a.n_rows - r0);
         const int p0 = a.off[e], p1 = a.off[e + 1];
@@ -198,19 +270,24 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_stream_kernel(const __grid
                 as.pack = packs + (uint32_t)i * pack_bytes;
                 const size_t orow = (size_t)a.pair[q0 + i] * a.out_stride;
                 if (FUSE) {
-                    if (warp < rows) { // warp w: gate row r0+w and up row r0+w
+                    float hv = 0.f; // lane k keeps the k-th result of this warp: one parallel silu at the end
+                    int n = 0;
+                    for (int r = warp; r < rows; r += kConsumerWarps, n++) { // gate row r0+r and up row r0+r
                         float g, u;
                         if (a.type_a == a.type_b) {
-                            row_dot2(a.type_a, tile + (uint32_t)(warp * a.row_bytes_a), (uint32_t)a.half_bytes, a.nb, as, g, u);
+                            row_dot2(a.type_a, tile + (uint32_t)(r * a.row_bytes_a), (uint32_t)a.half_bytes, a.nb, as, g, u);
                         } else {
-                            g = row_dot(a.type_a, tile + (uint32_t)(warp * a.row_bytes_a), a.nb, as);
-                            u = row_dot(a.type_b, tile + (uint32_t)(a.half_bytes + warp * a.row_bytes_b), a.nb, as);
+                            g = row_dot(a.type_a, tile + (uint32_t)(r * a.row_bytes_a), a.nb, as);
+                            u = row_dot(a.type_b, tile + (uint32_t)(a.half_bytes + r * a.row_bytes_b), a.nb, as);
                         }
                         g = warp_sum(g);
                         u = warp_sum(u);
-                        if (lane == 0) {
-                            a.out[orow + r0 + warp] = __fmul_rn(moe_silu(g), u);
-                        }
+                        // lanes n (gate) and 16 + n (up) take the sums
+                        hv = lane == n ? g : (lane == 16 + n ? u : hv);
+                    }
+                    const float uu = __shfl_down_sync(0xFFFFFFFFu, hv, 16);
+                    if (lane < n) {
+                        a.out[orow + r0 + warp + lane * kConsumerWarps] = __fmul_rn(moe_silu(hv), uu);
                     }
                 } else if (a.units_per_row > 0) { // short K: lane = (row, unit), several rows per pass
                     const int U = a.units_per_row, rp = 32 / U;
@@ -265,7 +342,7 @@ bool moe_stream_supported(int type_a, int type_b, int K, int n_rows, int fuse_si
         return false;
     }
     // two stages of at least eight row pairs (gate|up) / sixteen rows, plus kMoeTok packs, must fit
-    const size_t packs = (size_t)kMoeTok * nb * kPackSB;
+    const size_t packs = (size_t)kMoeTok * nb * kPackSB + 4096; // + the cost prefix of up to 1023 active experts
     const size_t tile = fuse_silu ? (size_t)8 * (ra + rb) + 64 : (size_t)16 * ra + 32;
     return kMoeHdr + packs + 2 * tile <= (size_t)kMoeSmem;
 }
@@ -275,8 +352,8 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
                               const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                               const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
                               float * out, int out_stride, int fuse_silu) {
-    (void)n_act_max;
     MoeStreamArgs a;
+    a.max_active = n_act_max;
     a.bank_a = static_cast<const uint8_t *>(bank_a);
     a.bank_b = static_cast<const uint8_t *>(bank_b);
     a.plane_a = plane_a;
@@ -300,7 +377,11 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
     a.row_bytes_b = fuse_silu ? a.nb * sb_bytes((uint32_t)type_b) : 0;
     a.units_per_row = 0;
     if (fuse_silu) {
-        a.rows_per_tile = kConsumerWarps; // one (gate, up) pair per warp
+        // (gate, up) row pairs per tile: two per warp when two such tiles fit, to spread a tile's fixed cost
+        const size_t packs_b = (size_t)kMoeTok * a.nb * kPackSB + 4096;
+        const size_t pair16 = (size_t)2 * (2 * kConsumerWarps * (a.row_bytes_a > a.row_bytes_b ? a.row_bytes_a : a.row_bytes_b) + 32);
+        a.rows_per_tile = (kMoeHdr + packs_b + 2 * pair16 <= (size_t)kMoeSmem && n_rows >= 2 * kConsumerWarps) ? 2 * kConsumerWarps
+                                                                                                       : kConsumerWarps;
         const int big = a.row_bytes_a > a.row_bytes_b ? a.row_bytes_a : a.row_bytes_b;
         a.half_bytes = ((a.rows_per_tile * big + 15) / 16) * 16 + 16;
         a.tile_bytes = 2 * a.half_bytes;
@@ -311,7 +392,7 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
             a.units_per_row = U;
             a.rows_per_tile = kConsumerWarps * (32 / U);
             // short rows make small tiles: take several passes per tile while the copy stays below 32 KB
-            while (a.rows_per_tile * 2 * a.row_bytes_a <= 32 * 1024 && a.rows_per_tile * 2 <= n_rows) {
+            while (a.rows_per_tile * 2 * a.row_bytes_a <= 44 * 1024 && a.rows_per_tile * 2 <= n_rows) {
                 a.rows_per_tile *= 2;
             }
         } else {
@@ -321,7 +402,7 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
         a.tile_bytes = a.half_bytes;
     }
     a.tiles_per_expert = (n_rows + a.rows_per_tile - 1) / a.rows_per_tile;
-    const size_t packs = (size_t)kMoeTok * a.nb * kPackSB;
+    const size_t packs = (size_t)kMoeTok * a.nb * kPackSB + ((size_t)(n_act_max + 1) * 4 + 15) / 16 * 16; // + the cost prefix
     int stages = (int)((kMoeSmem - kMoeHdr - packs) / (size_t)a.tile_bytes);
     if (stages < 2) {
         return cudaErrorInvalidConfiguration;
