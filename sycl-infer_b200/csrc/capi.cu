@@ -271,6 +271,10 @@ int b200q_quant_gemv_scatter(void * stream, const b200q_seg * segs, int n_segs, 
         }
         c.peer_delta[i] = peers->out_delta[i];
     }
+    if (gemv_takes_stream(c) && stream_quantizes(c, s0.act_up)) { // one launch: the GEMV quantizes in its prologue
+        B200Q_CUDA_OK(launch_gemv_stream((cudaStream_t)stream, c, true, s0.x));
+        return B200Q_OK;
+    }
     B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
                             s0.K, true));
     B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));

@@ -97,6 +97,6 @@ class DenseLayer:
     def launches_per_step(self):
         # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue (one launch
         # each), down keeps the separate silu(gate)*up quantizer; otherwise a quantizer + GEMV per call
-        if self.arena is not None:
-            return 12  # quantizer + GEMV with peer stores + flag barrier, per call
+        if self.arena is not None:  # GEMV with peer stores (+ quantizer where it is a kernel of its own) + flag barrier
+            return 9 if self.TB == 1 else 12
         return 5 if self.TB == 1 else 8
