@@ -8,17 +8,18 @@
 // and the epilogue warps read it back (tcgen05.ld) and fold it into fp32 registers.  The
 // design is therefore epilogue-bound by construction; the tensor core only has to stay ahead.
 //
-// Roles in a CTA (416 threads, one CTA per SM, persistent over (row tile, token tile)):
-//   warps 0-7   epilogue: warp w reads TMEM lanes 32*(w%4).. (its weight rows) and the token
-//               columns of half w/4; accumulators stay in registers for the whole K loop
-//   warps 8-11  producers: thread = weight row; unpack the group's 32 codes from the raw GGUF
-//               block into the K-major core-matrix layout the MMA reads, copy the tokens'
-//               int8 group the same way, publish the per-row / per-token fp32 factors
-//   warp 12     one thread issues the MMAs and commits them to mbarriers; it owns TMEM
+// Roles in a CTA (one CTA per SM, persistent over (row tile, token tile)); the mix <NT, EW, PG>
+// follows the token count:
+//   4*EW epilogue warps   warp w reads TMEM lanes 32*(w%4).. (its weight rows) and the NT/EW token
+//                         columns of group w/4; its fp32 sums stay in registers for the whole K loop
+//   4*PG producer warps   thread = weight row; unpack a superblock's codes from the raw GGUF
+//                         block into the K-major core-matrix layout the MMA reads, copy the tokens'
+//                         int8 groups the same way, publish the per-row / per-token fp32 factors
+//   1 MMA warp            one thread issues the MMAs and commits them to mbarriers; it owns TMEM
 // Operands travel in slots of eight steps (one superblock): one producer/consumer handshake per
 // slot.  mbarrier arrays: full (producers -> MMA) and done (epilogue -> producers) per slot,
 // acc_full (MMA -> epilogue) and acc_empty (epilogue -> MMA) per tensor-memory accumulator, of
-// which all 512 columns are used as a ring.  All waits are bounded; TMEM is always released.
+// which up to 16 form a ring.  All waits are bounded; TMEM is always released.
 #include <cstdlib>
 
 #include "async.cuh"
@@ -34,6 +35,11 @@ constexpr int kTileM = 128;
 // round trip is latency-bound, so the deeper the ring the more steps overlap)
 __host__ __device__ constexpr int acc_ring(int NT) {
     return 512 / NT < 16 ? 512 / NT : 16;
+}
+// MMA steps handled together by the epilogue and signalled by ONE barrier pair (the sums of a
+// batch live in registers: NC columns x batch <= 64): per-step handshakes are mostly latency
+__host__ __device__ constexpr int epi_batch(int NC) {
+    return NC <= 8 ? 8 : (NC <= 16 ? 4 : 1);
 }
 constexpr int kHdr = 512;  // bytes of mbarriers + the TMEM address at the start of shared memory
 // Role mix per instantiation <NT, EW, PG>: EW epilogue warpgroups (each covers all 128 TMEM
@@ -51,6 +57,7 @@ struct MmaArgs {
     int32_t n_tiles_m, n_tiles_t;
     int32_t raw_bytes; // per-thread staging bytes for one raw superblock (16-byte units)
     int32_t depth;     // operand slots in the shared-memory ring
+    int32_t dbg;      // timing experiments (results wrong): 1 no unpack, 2 no token copies/factors, 4 no raw staging
     int32_t lbo, sbo; // operand descriptor strides (bytes): K-adjacent core matrices, 8-row groups
 };
 
@@ -295,7 +302,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         raw_gen = smem_raw + (raw - smem_u32(smem_raw));
     }
     auto stage_sb = [&](int b, int buf) { // this row's superblock b -> raw[buf], 16-byte aligned chunks
-        if (row_ok && b < nb) {
+        if (row_ok && b < nb && !(a.dbg & 4)) {
             const uintptr_t A = reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB);
             const uintptr_t A0 = A & ~uintptr_t(15);
             const int n = (int)((A + SB + 15 - A0) >> 4);
@@ -327,7 +334,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
             return false;
         }
         // tokens: the int8 groups this slot's steps meet, straight into the B buffers
-        for (int c = r; c < NB * NT * 2; c += 128) {
+        for (int c = r; c < NB * NT * 2 && !(a.dbg & 2); c += 128) {
             const int gi = c / (2 * NT), rem = c - gi * 2 * NT, t = rem >> 1, hh = rem & 1;
             const int G = 8 * b + (F::NS == 16 ? 4 * h + gi : gi);
             const uint32_t dst = base + Slot<NT>::B + (uint32_t)(gi * NT * 32) + core_off(t, hh);
@@ -346,7 +353,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
             cp_async_commit();
         }
         // per-token factors of the eight steps
-        for (int c = r; c < kSlotSteps * NT; c += 128) {
+        for (int c = r; c < kSlotSteps * NT && !(a.dbg & 2); c += 128) {
             const int st = c / NT, t = c - st * NT;
             float tokA = 0.f, tokB = 0.f, tokC = 0.f;
             if (t0 + t < TB) {
@@ -367,7 +374,9 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         // groups in flight, oldest first: [superblock b] | [tokens] [next superblock or empty]
         cp_async_wait<2>();
         const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB) & 15);
-        unpack_slot<TYPE, NT>(raw_gen + buf * BS + mis, h, r, row_ok, base);
+        if (!(a.dbg & 1)) {
+            unpack_slot<TYPE, NT>(raw_gen + buf * BS + mis, h, r, row_ok, base);
+        }
         cp_async_wait<1>();  // the tokens have landed; the prefetched superblock may still be in flight
         fence_proxy_async(); // the tensor core reads A and B through the async proxy
         mbar_arrive(bars.full + 8 * (g % D));
@@ -376,10 +385,11 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
     return true;
 }
 
-template <int TYPE, int NT>
+template <int TYPE, int NT, int EW>
 __device__ __forceinline__ bool mma_tile(const MmaArgs & a, uint32_t ring, uint32_t tmem, const Bars & bars,
                                          uint32_t & gslot, uint32_t & git) {
     using F = StepFmt<TYPE>;
+    constexpr int GB = epi_batch(NT / EW), AR = acc_ring(NT), NG = AR / GB; // steps per barrier group, groups in the ring
     const uint32_t idesc = idesc_i8(F::A_SIGNED, 1, kTileM, NT);
     const int slots = (a.c.K >> 8) * (F::NS / kSlotSteps);
     const uint32_t D = (uint32_t)bars.depth;
@@ -389,18 +399,23 @@ __device__ __forceinline__ bool mma_tile(const MmaArgs & a, uint32_t ring, uint3
             return false;
         }
         const uint32_t base = ring + slot * Slot<NT>::BYTES;
-        for (int st = 0; st < kSlotSteps; st++, git++) {
-            const uint32_t acc = git % acc_ring(NT);
-            // the accumulator this step overwrites must have been drained by the epilogue
-            if (!mbar_wait(bars.acc_empty + 8 * acc, ((git / acc_ring(NT)) & 1) ^ 1, &g_mma_status)) {
+        for (int st0 = 0; st0 < kSlotSteps; st0 += GB, git += GB) {
+            const uint32_t grp = (git / GB) % NG;
+            // the accumulators this group overwrites must have been drained by the epilogue
+            if (!mbar_wait(bars.acc_empty + 8 * grp, (((git / GB) / NG) & 1) ^ 1, &g_mma_status)) {
                 return false;
             }
             tc_fence_after();
-            const uint64_t ad = smem_desc_kmajor(base + Slot<NT>::A + (uint32_t)(st * kTileM * 32), a.lbo, a.sbo);
-            const uint64_t bd =
-                smem_desc_kmajor(base + Slot<NT>::B + (uint32_t)(step_bbuf<TYPE>(st) * NT * 32), a.lbo, a.sbo);
-            mma_i8(tmem + (uint32_t)(acc * NT), ad, bd, idesc, 0);
-            mma_commit(bars.acc_full + 8 * acc);
+#pragma unroll
+            for (int b = 0; b < GB; b++) {
+                const int st = st0 + b;
+                const uint32_t acc = (git + b) % AR;
+                const uint64_t ad = smem_desc_kmajor(base + Slot<NT>::A + (uint32_t)(st * kTileM * 32), a.lbo, a.sbo);
+                const uint64_t bd =
+                    smem_desc_kmajor(base + Slot<NT>::B + (uint32_t)(step_bbuf<TYPE>(st) * NT * 32), a.lbo, a.sbo);
+                mma_i8(tmem + (uint32_t)(acc * NT), ad, bd, idesc, 0);
+            }
+            mma_commit(bars.acc_full + 8 * grp); // arrives when every MMA issued so far has completed
         }
     }
     return true;
@@ -444,69 +459,81 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
     }
     const uint64_t kNegMagic = pack2(-12582912.0f, -12582912.0f);
     bool ok = true;
+    // Steps are taken in batches: wait for the batch's MMAs, start all their tensor-memory reads,
+    // wait once, hand the accumulators back, then fold.  The wait -> read -> fold -> release chain
+    // of a single step is almost pure latency (mbarrier wake-up + tensor-memory read), so with few
+    // token columns per thread a whole batch costs little more than one step.
+    constexpr int CH = NC >= 16 ? 16 : 8;                        // columns per tensor-memory read
+    constexpr int BATCH = epi_batch(NC), NG = (int)AR / BATCH;   // steps per batch, barrier groups in the ring
     for (int i = 0; i < slots && ok; i++, gslot++) {
         const uint32_t slot = gslot % D;
         const uint32_t base = ring + slot * Slot<NT>::BYTES;
 #pragma unroll 1
-        for (int st = 0; st < kSlotSteps; st++, git++) {
-            const uint32_t accb = git % AR;
-            if (!mbar_wait(bars.acc_full + 8 * accb, (git / AR) & 1, &g_mma_status)) {
+        for (int st0 = 0; st0 < kSlotSteps; st0 += BATCH, git += BATCH) {
+            uint32_t v[BATCH][NC];
+            const uint32_t grp = (git / BATCH) % NG;
+            if (!mbar_wait(bars.acc_full + 8 * grp, ((git / BATCH) / NG) & 1, &g_mma_status)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const float ra = __uint_as_float(lds32(base + Slot<NT>::ROWA + 4 * (st * kTileM + rl)));
-            const uint64_t rowA = pack2(ra, ra);
-            uint64_t nrowB = 0ull;
-            if (F::HAS_MIN) {
-                const float rb = -__uint_as_float(lds32(base + Slot<NT>::ROWB + 4 * (st * kTileM + rl)));
-                nrowB = pack2(rb, rb);
-            }
-            const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(accb * NT + c0);
-            const uint32_t tok = base + 4 * (st * NT + c0);
-            constexpr int CH = NC >= 16 ? 16 : 8; // columns per tensor-memory read
 #pragma unroll
-            for (int j = 0; j < NC; j += CH) {
-                uint32_t v[CH];
-                if constexpr (CH == 16) {
-                    tmem_ld16(taddr + j, v);
-                } else {
-                    tmem_ld8(taddr + j, v);
+            for (int b = 0; b < BATCH; b++) {
+                const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(((git + b) % AR) * NT + c0);
+#pragma unroll
+                for (int j = 0; j < NC; j += CH) {
+                    if constexpr (CH == 16) {
+                        tmem_ld16(taddr + j, *reinterpret_cast<uint32_t(*)[16]>(&v[b][j]));
+                    } else {
+                        tmem_ld8(taddr + j, *reinterpret_cast<uint32_t(*)[8]>(&v[b][j]));
+                    }
                 }
-                tmem_ld_wait();
+            }
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bars.acc_empty + 8 * grp); // the batch's accumulators may be overwritten
 #pragma unroll
-                for (int q = 0; q < CH; q += 4) {
-                    const uint4 ta = lds128(tok + Slot<NT>::TOKA + 4 * (j + q));
+            for (int b = 0; b < BATCH; b++) {
+                const int st = st0 + b;
+                const float ra = __uint_as_float(lds32(base + Slot<NT>::ROWA + 4 * (st * kTileM + rl)));
+                const uint64_t rowA = pack2(ra, ra);
+                uint64_t nrowB = 0ull;
+                if (F::HAS_MIN) {
+                    const float rb = -__uint_as_float(lds32(base + Slot<NT>::ROWB + 4 * (st * kTileM + rl)));
+                    nrowB = pack2(rb, rb);
+                }
+                const uint32_t tok = base + 4 * (st * NT + c0);
+#pragma unroll
+                for (int q = 0; q < NC; q += 4) {
+                    const uint4 ta = lds128(tok + Slot<NT>::TOKA + 4 * q);
                     const uint64_t sx[2] = {(uint64_t)ta.x | ((uint64_t)ta.y << 32), (uint64_t)ta.z | ((uint64_t)ta.w << 32)};
                     uint64_t tc[2] = {0ull, 0ull}, tb[2] = {0ull, 0ull};
                     if (F::HAS_C) {
-                        const uint4 x = lds128(tok + Slot<NT>::TOKC + 4 * (j + q));
+                        const uint4 x = lds128(tok + Slot<NT>::TOKC + 4 * q);
                         tc[0] = pack2(-__uint_as_float(x.x), -__uint_as_float(x.y));
                         tc[1] = pack2(-__uint_as_float(x.z), -__uint_as_float(x.w));
                     }
                     if (F::HAS_MIN) {
-                        const uint4 x = lds128(tok + Slot<NT>::TOKB + 4 * (j + q));
+                        const uint4 x = lds128(tok + Slot<NT>::TOKB + 4 * q);
                         tb[0] = (uint64_t)x.x | ((uint64_t)x.y << 32);
                         tb[1] = (uint64_t)x.z | ((uint64_t)x.w << 32);
                     }
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         // exact int -> float without the conversion unit: |wd| < 2^22
-                        uint64_t w = (uint64_t)(v[q + 2 * e] + 0x4B400000u) | ((uint64_t)(v[q + 2 * e + 1] + 0x4B400000u) << 32);
+                        uint64_t w = (uint64_t)(v[b][q + 2 * e] + 0x4B400000u) | ((uint64_t)(v[b][q + 2 * e + 1] + 0x4B400000u) << 32);
                         w = add2(w, kNegMagic);
                         if (F::HAS_C) {
                             w = add2(w, tc[e]);
                         }
-                        uint64_t r = fma2(rowA, mul2(sx[e], w), acc[(j + q) / 2 + e]);
+                        uint64_t r = fma2(rowA, mul2(sx[e], w), acc[q / 2 + e]);
                         if (F::HAS_MIN) {
                             r = fma2(nrowB, tb[e], r);
                         }
-                        acc[(j + q) / 2 + e] = r;
+                        acc[q / 2 + e] = r;
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(bars.acc_empty + 8 * accb); // the accumulator may be overwritten
         }
         if (ok) {
             mbar_arrive(bars.done + 8 * slot); // the operand slot and its factors may be refilled
@@ -546,7 +573,7 @@ __device__ __forceinline__ bool run_tile(const MmaArgs & a, const SegDev & sg, i
                                           (int)threadIdx.x - 32 * R::kEpiWarps, bars, gslot);
     }
     if (threadIdx.x == 32 * (R::kEpiWarps + R::kProdWarps)) {
-        return mma_tile<TYPE, NT>(a, ring, tmem, bars, gslot, git);
+        return mma_tile<TYPE, NT, EW>(a, ring, tmem, bars, gslot, git);
     }
     return true; // idle lanes of the MMA warp
 }
@@ -669,6 +696,11 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     a.raw_bytes = (need / 16) % 2 ? need : need + 16;
     a.lbo = 128;
     a.sbo = 256;
+    static const int dbg_env = [] {
+        const char * e = getenv("B200Q_MMA_DBG");
+        return e && *e ? atoi(e) : 0;
+    }();
+    a.dbg = dbg_env;
     const bool pg2 = a.raw_bytes <= (c.TB <= 32 ? 240 : 192); // a second producer group where its staging fits
     // token tile: the fp32 epilogue costs in proportion to its width, so it is as narrow as the call allows
     if (c.TB <= 8) {
