@@ -329,6 +329,24 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
             have = b;
             buf ^= 1;
         }
+        // the per-token factors of the eight steps come from global memory: start those loads
+        // before waiting for the slot, they do not depend on it
+        // (wide token tiles keep the loads after the wait: their registers are needed elsewhere)
+        constexpr int NI = (kSlotSteps * NT + 127) / 128;
+        constexpr bool kHoist = NT <= 32;
+        float f_sx[NI];
+        int2 f_xs[NI];
+#pragma unroll
+        for (int k = 0; k < NI; k++) {
+            const int c = r + 128 * k, st = c / NT, t = c - st * NT;
+            f_sx[k] = 0.f;
+            f_xs[k] = make_int2(0, 0);
+            if (kHoist && c < kSlotSteps * NT && t0 + t < TB && !(a.dbg & 2)) {
+                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
+                f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
+                f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
+            }
+        }
         if (!mbar_wait(bars.done + 8 * (g % D), ((g / D) & 1) ^ 1, &g_mma_status)) {
             cp_async_wait<0>();
             return false;
@@ -352,23 +370,22 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         } else {
             cp_async_commit();
         }
-        // per-token factors of the eight steps
-        for (int c = r; c < kSlotSteps * NT && !(a.dbg & 2); c += 128) {
-            const int st = c / NT, t = c - st * NT;
-            float tokA = 0.f, tokB = 0.f, tokC = 0.f;
-            if (t0 + t < TB) {
+#pragma unroll
+        for (int k = 0; k < NI; k++) {
+            const int c = r + 128 * k, st = c / NT, t = c - st * NT;
+            if (!kHoist && c < kSlotSteps * NT && t0 + t < TB && !(a.dbg & 2)) {
                 const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
-                tokA = __ldg(a.c.xmeta + 2 * gi);
-                const int2 xs = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
-                tokB = tokA * (float)(xs.x + xs.y);
-                tokC = (float)(32 * ((st & 1) ? xs.y : xs.x));
+                f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
+                f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
             }
-            sts32(base + Slot<NT>::TOKA + 4 * c, __float_as_uint(tokA));
-            if (F::HAS_MIN) {
-                sts32(base + Slot<NT>::TOKB + 4 * c, __float_as_uint(tokB));
-            }
-            if (F::HAS_C) {
-                sts32(base + Slot<NT>::TOKC + 4 * c, __float_as_uint(tokC));
+            if (c < kSlotSteps * NT) {
+                sts32(base + Slot<NT>::TOKA + 4 * c, __float_as_uint(f_sx[k]));
+                if (F::HAS_MIN) {
+                    sts32(base + Slot<NT>::TOKB + 4 * c, __float_as_uint(f_sx[k] * (float)(f_xs[k].x + f_xs[k].y)));
+                }
+                if (F::HAS_C) {
+                    sts32(base + Slot<NT>::TOKC + 4 * c, __float_as_uint((float)(32 * ((st & 1) ? f_xs[k].y : f_xs[k].x))));
+                }
             }
         }
         // groups in flight, oldest first: [superblock b] | [tokens] [next superblock or empty]
