@@ -57,7 +57,6 @@ struct MmaArgs {
     int32_t n_tiles_m, n_tiles_t;
     int32_t raw_bytes; // per-thread staging bytes for one raw superblock (16-byte units)
     int32_t depth;     // operand slots in the shared-memory ring
-    int32_t dbg;      // timing experiments (results wrong): 1 no unpack, 2 no token copies/factors, 4 no raw staging
     int32_t lbo, sbo; // operand descriptor strides (bytes): K-adjacent core matrices, 8-row groups
 };
 
@@ -302,7 +301,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         raw_gen = smem_raw + (raw - smem_u32(smem_raw));
     }
     auto stage_sb = [&](int b, int buf) { // this row's superblock b -> raw[buf], 16-byte aligned chunks
-        if (row_ok && b < nb && !(a.dbg & 4)) {
+        if (row_ok && b < nb) {
             const uintptr_t A = reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB);
             const uintptr_t A0 = A & ~uintptr_t(15);
             const int n = (int)((A + SB + 15 - A0) >> 4);
@@ -341,7 +340,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
             const int c = r + 128 * k, st = c / NT, t = c - st * NT;
             f_sx[k] = 0.f;
             f_xs[k] = make_int2(0, 0);
-            if (kHoist && c < kSlotSteps * NT && t0 + t < TB && !(a.dbg & 2)) {
+            if (kHoist && c < kSlotSteps * NT && t0 + t < TB) {
                 const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
                 f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
                 f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
@@ -352,7 +351,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
             return false;
         }
         // tokens: the int8 groups this slot's steps meet, straight into the B buffers
-        for (int c = r; c < NB * NT * 2 && !(a.dbg & 2); c += 128) {
+        for (int c = r; c < NB * NT * 2; c += 128) {
             const int gi = c / (2 * NT), rem = c - gi * 2 * NT, t = rem >> 1, hh = rem & 1;
             const int G = 8 * b + (F::NS == 16 ? 4 * h + gi : gi);
             const uint32_t dst = base + Slot<NT>::B + (uint32_t)(gi * NT * 32) + core_off(t, hh);
@@ -373,7 +372,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
 #pragma unroll
         for (int k = 0; k < NI; k++) {
             const int c = r + 128 * k, st = c / NT, t = c - st * NT;
-            if (!kHoist && c < kSlotSteps * NT && t0 + t < TB && !(a.dbg & 2)) {
+            if (!kHoist && c < kSlotSteps * NT && t0 + t < TB) {
                 const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
                 f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
                 f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
@@ -391,9 +390,7 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         // groups in flight, oldest first: [superblock b] | [tokens] [next superblock or empty]
         cp_async_wait<2>();
         const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(wrow + (size_t)b * SB) & 15);
-        if (!(a.dbg & 1)) {
-            unpack_slot<TYPE, NT>(raw_gen + buf * BS + mis, h, r, row_ok, base);
-        }
+        unpack_slot<TYPE, NT>(raw_gen + buf * BS + mis, h, r, row_ok, base);
         cp_async_wait<1>();  // the tokens have landed; the prefetched superblock may still be in flight
         fence_proxy_async(); // the tensor core reads A and B through the async proxy
         mbar_arrive(bars.full + 8 * (g % D));
@@ -416,6 +413,8 @@ __device__ __forceinline__ bool mma_tile(const MmaArgs & a, uint32_t ring, uint3
             return false;
         }
         const uint32_t base = ring + slot * Slot<NT>::BYTES;
+        const uint64_t ad0 = smem_desc_kmajor(base + Slot<NT>::A, a.lbo, a.sbo);
+        const uint64_t bd0 = smem_desc_kmajor(base + Slot<NT>::B, a.lbo, a.sbo);
         for (int st0 = 0; st0 < kSlotSteps; st0 += GB, git += GB) {
             const uint32_t grp = (git / GB) % NG;
             // the accumulators this group overwrites must have been drained by the epilogue
@@ -423,13 +422,14 @@ __device__ __forceinline__ bool mma_tile(const MmaArgs & a, uint32_t ring, uint3
                 return false;
             }
             tc_fence_after();
+            // the issuing thread is a serial resource (one MMA per 32-value group): descriptors of
+            // a slot differ only in their address field, so a step costs two additions and the MMA
 #pragma unroll
             for (int b = 0; b < GB; b++) {
                 const int st = st0 + b;
                 const uint32_t acc = (git + b) % AR;
-                const uint64_t ad = smem_desc_kmajor(base + Slot<NT>::A + (uint32_t)(st * kTileM * 32), a.lbo, a.sbo);
-                const uint64_t bd =
-                    smem_desc_kmajor(base + Slot<NT>::B + (uint32_t)(step_bbuf<TYPE>(st) * NT * 32), a.lbo, a.sbo);
+                const uint64_t ad = ad0 + (uint64_t)((st * kTileM * 32) >> 4);
+                const uint64_t bd = bd0 + (uint64_t)((step_bbuf<TYPE>(st) * NT * 32) >> 4);
                 mma_i8(tmem + (uint32_t)(acc * NT), ad, bd, idesc, 0);
             }
             mma_commit(bars.acc_full + 8 * grp); // arrives when every MMA issued so far has completed
@@ -713,11 +713,6 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     a.raw_bytes = (need / 16) % 2 ? need : need + 16;
     a.lbo = 128;
     a.sbo = 256;
-    static const int dbg_env = [] {
-        const char * e = getenv("B200Q_MMA_DBG");
-        return e && *e ? atoi(e) : 0;
-    }();
-    a.dbg = dbg_env;
     const bool pg2 = a.raw_bytes <= (c.TB <= 32 ? 240 : 192); // a second producer group where its staging fits
     // token tile: the fp32 epilogue costs in proportion to its width, so it is as narrow as the call allows
     if (c.TB <= 8) {
