@@ -125,6 +125,13 @@ int b200q_peer_barrier(void * stream, uint32_t * const * flags /*host*/, int wor
 int b200q_moe_route(void * stream, const float * gate_inp, const float * x, int x_stride, int n_tok, int n_embd,
                     int n_expert, int top_k, float * logits, int32_t * ids, float * wts);
 
+/* b200q_moe_route followed by b200q_moe_csr as one launch sequence without the CSR kernel: the
+ * router CTA that finishes last builds the lists (same results).  Calls of this entry point on
+ * one device must not overlap (they share a completion counter). */
+int b200q_moe_route_csr(void * stream, const float * gate_inp, const float * x, int x_stride, int n_tok, int n_embd,
+                        int n_expert, int top_k, float * logits, int32_t * ids, float * wts, int32_t * off,
+                        int32_t * pair, int32_t * active, int32_t * n_active);
+
 /* moe_csr_clear/count/prefix/scatter_launch (kernels.h:604-609) in one launch: off[n_expert+1],
  * pair[n_pairs] (pairs of an expert in increasing pair order), active[n_expert], n_active[1]. */
 int b200q_moe_csr(void * stream, const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,

@@ -43,6 +43,8 @@ _SIGS = {
     "b200q_quant_gemv_scatter": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(Peers)]),
     "b200q_peer_barrier": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, C.c_uint32]),
     "b200q_moe_route": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_moe_route_csr": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp,
+                                      _vp, _vp]),
     "b200q_moe_csr": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "b200q_moe_gate_up": (C.c_int, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp,
                                     C.c_int, _vp, _vp, _vp, C.c_int, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),

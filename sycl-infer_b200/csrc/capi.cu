@@ -334,6 +334,23 @@ int b200q_moe_route(void * stream, const float * gate_inp, const float * x, int 
     return B200Q_OK;
 }
 
+int b200q_moe_route_csr(void * stream, const float * gate_inp, const float * x, int x_stride, int n_tok, int n_embd,
+                        int n_expert, int top_k, float * logits, int32_t * ids, float * wts, int32_t * off,
+                        int32_t * pair, int32_t * active, int32_t * n_active) {
+    if (!logits || !ids || !wts || (gate_inp && !x) || !off || !pair || !active || !n_active) {
+        set_error("b200q_moe_route_csr: logits, ids, wts, off, pair, active, n_active (and x with gate_inp) must be non-null");
+        return B200Q_EINVAL;
+    }
+    if (n_tok < 1 || n_expert < 1 || n_expert > 4096 || top_k < 1 || top_k > n_expert || (gate_inp && n_embd < 1)) {
+        set_error("b200q_moe_route_csr: bad shape (n_tok=%d n_expert=%d top_k=%d n_embd=%d)", n_tok, n_expert, top_k,
+                  n_embd);
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_moe_route((cudaStream_t)stream, gate_inp, x, x_stride, n_tok, n_embd, n_expert, top_k, logits,
+                                   ids, wts, off, pair, active, n_active));
+    return B200Q_OK;
+}
+
 int b200q_moe_csr(void * stream, const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,
                   int32_t * active, int32_t * n_active) {
     if (!ids || !off || !pair || !active || !n_active || n_pairs < 1 || n_expert < 1) {

@@ -20,7 +20,9 @@ cudaError_t launch_block_dots(cudaStream_t s, const uint8_t * w, int type, int K
                               int TB, int t, int32_t * wd);
 
 cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
-                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts);
+                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts,
+                             int32_t * off = nullptr, int32_t * pair = nullptr, int32_t * active = nullptr,
+                             int32_t * n_active = nullptr);
 cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
                            int32_t * pair, int32_t * active, int32_t * n_active);
 cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,

@@ -33,7 +33,27 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
         for (int i = 0; i < kRouteTok; i++) {
             a[i] = 0.0;
         }
-        for (int k = threadIdx.x; k < n_embd; k += 256) {
+        // four values per load, every load of a sweep independent of the others: the kernel is
+        // bound by memory latency, not by the fp64 pipe
+        const bool vec = (n_embd & 3) == 0 && (x_stride & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+        const int n_vec = vec ? n_embd : 0;
+        for (int k = 4 * threadIdx.x; k < n_vec; k += 4 * 256) {
+            const float4 wk = __ldg(reinterpret_cast<const float4 *>(w + k));
+            float4 xv[kRouteTok];
+#pragma unroll
+            for (int i = 0; i < kRouteTok; i++) {
+                xv[i] = t0 + i < n_tok ? __ldg(reinterpret_cast<const float4 *>(x + (size_t)(t0 + i) * x_stride + k))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kRouteTok; i++) { // element order k, k+1, k+2, k+3 within a thread
+                a[i] += (double)wk.x * (double)xv[i].x;
+                a[i] += (double)wk.y * (double)xv[i].y;
+                a[i] += (double)wk.z * (double)xv[i].z;
+                a[i] += (double)wk.w * (double)xv[i].w;
+            }
+        }
+        for (int k = n_vec + threadIdx.x; k < n_embd; k += 256) {
             const double wk = (double)__ldg(w + k);
 #pragma unroll
             for (int i = 0; i < kRouteTok; i++) {
@@ -63,10 +83,92 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
     }
 }
 
+// ---- token -> expert CSR (one CTA) -----------------------------------------------------------
+// off[e]..off[e+1] index `pair`, which lists the (token, slot) pair ids routed to expert e in
+// increasing pair order; active[0..n_active) lists the experts with at least one pair.
+// cnt: shared memory, 2 * (n_expert + 1) words (+ n_pairs when ids_in_smem): n_expert + 1 counts ->
+// their prefix; then the active flags' prefix; then the ids.
+__device__ __forceinline__ void csr_build(const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,
+                                          int32_t * active, int32_t * n_active, int ids_in_smem, int32_t * cnt) {
+    int32_t * act = cnt + n_expert + 1;
+    int32_t * sid = act + n_expert + 1;
+    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
+        cnt[e] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = __ldcg(ids + i); // may have been written by other CTAs of this launch
+        if (ids_in_smem) {
+            sid[i] = e;
+        }
+        if (e >= 0 && e < n_expert) {
+            atomicAdd(&cnt[e + 1], 1); // integer counts: order does not matter
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) { // warp 0: inclusive scans of the counts and of the "has pairs" flags, 32 at a time
+        int carry = 0, acarry = 0;
+        for (int e0 = 0; e0 < n_expert; e0 += 32) {
+            const int e = e0 + threadIdx.x;
+            const int c = e < n_expert ? cnt[e + 1] : 0;
+            int v = c, f = c > 0 ? 1 : 0;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xFFFFFFFFu, v, o), g = __shfl_up_sync(0xFFFFFFFFu, f, o);
+                if ((int)threadIdx.x >= o) {
+                    v += u;
+                    f += g;
+                }
+            }
+            if (e < n_expert) {
+                cnt[e + 1] = carry + v;
+                act[e + 1] = acarry + f; // experts with pairs among 0..e
+            }
+            carry += __shfl_sync(0xFFFFFFFFu, v, 31);
+            acarry += __shfl_sync(0xFFFFFFFFu, f, 31);
+        }
+        if (threadIdx.x == 0) {
+            act[0] = 0;
+            *n_active = acarry;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
+        off[e] = cnt[e];
+    }
+    const int32_t * idv = ids_in_smem ? sid : ids;
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        if (act[e + 1] > act[e]) {
+            active[act[e]] = e; // increasing expert order
+        }
+        int o = cnt[e];
+        const int end = cnt[e + 1];
+        for (int i = 0; i < n_pairs && o < end; i++) { // deterministic fill in pair order
+            if (idv[i] == e) {
+                pair[o++] = i;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict__ ids, int n_pairs, int n_expert,
+                                                      int32_t * off, int32_t * pair, int32_t * active,
+                                                      int32_t * n_active, int ids_in_smem) {
+    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    extern __shared__ int32_t cnt[];
+    csr_build(ids, n_pairs, n_expert, off, pair, active, n_active, ids_in_smem, cnt);
+}
+
 // Softmax and top-k of one token's logits (one CTA per token); the logits come from memory.
+// With `off` set, the CTA that finishes last also builds the token -> expert CSR (one launch less).
+__device__ unsigned int g_route_done = 0;
 __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ x, int x_stride, int n_embd,
                                                         int n_expert, int top_k, float * __restrict__ logits,
-                                                        int32_t * __restrict__ ids, float * __restrict__ wts) {
+                                                        int32_t * ids, float * __restrict__ wts, int32_t * off,
+                                                        int32_t * pair, int32_t * active, int32_t * n_active,
+                                                        int ids_in_smem) {
     // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -131,74 +233,21 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
             wts[(size_t)t * top_k + sel[e]] = __fdiv_rn(p[e], s_den);
         }
     }
-}
-
-// ---- token -> expert CSR (one CTA) -----------------------------------------------------------
-// off[e]..off[e+1] index `pair`, which lists the (token, slot) pair ids routed to expert e in
-// increasing pair order; active[0..n_active) lists the experts with at least one pair.
-__global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict__ ids, int n_pairs, int n_expert,
-                                                      int32_t * off, int32_t * pair, int32_t * active,
-                                                      int32_t * n_active, int ids_in_smem) {
-    // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    extern __shared__ int32_t cnt[]; // n_expert + 1 counts -> their prefix; then the active flags' prefix; then ids
-    int32_t * act = cnt + n_expert + 1;
-    int32_t * sid = act + n_expert + 1;
-    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
-        cnt[e] = 0;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const int e = ids[i];
-        if (ids_in_smem) {
-            sid[i] = e;
-        }
-        if (e >= 0 && e < n_expert) {
-            atomicAdd(&cnt[e + 1], 1); // integer counts: order does not matter
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x < 32) { // warp 0: inclusive scans of the counts and of the "has pairs" flags, 32 at a time
-        int carry = 0, acarry = 0;
-        for (int e0 = 0; e0 < n_expert; e0 += 32) {
-            const int e = e0 + threadIdx.x;
-            const int c = e < n_expert ? cnt[e + 1] : 0;
-            int v = c, f = c > 0 ? 1 : 0;
-            for (int o = 1; o < 32; o <<= 1) {
-                const int u = __shfl_up_sync(0xFFFFFFFFu, v, o), g = __shfl_up_sync(0xFFFFFFFFu, f, o);
-                if ((int)threadIdx.x >= o) {
-                    v += u;
-                    f += g;
-                }
+    if (off) {
+        __shared__ int s_last;
+        __syncthreads(); // this CTA's ids are written
+        if (tid == 0) {
+            __threadfence();
+            s_last = atomicAdd(&g_route_done, 1u) == gridDim.x - 1;
+            if (s_last) {
+                g_route_done = 0; // ready for the next launch
+                __threadfence();
             }
-            if (e < n_expert) {
-                cnt[e + 1] = carry + v;
-                act[e + 1] = acarry + f; // experts with pairs among 0..e
-            }
-            carry += __shfl_sync(0xFFFFFFFFu, v, 31);
-            acarry += __shfl_sync(0xFFFFFFFFu, f, 31);
         }
-        if (threadIdx.x == 0) {
-            act[0] = 0;
-            *n_active = acarry;
-        }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e <= n_expert; e += blockDim.x) {
-        off[e] = cnt[e];
-    }
-    const int32_t * idv = ids_in_smem ? sid : ids;
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
-        if (act[e + 1] > act[e]) {
-            active[act[e]] = e; // increasing expert order
-        }
-        int o = cnt[e];
-        const int end = cnt[e + 1];
-        for (int i = 0; i < n_pairs && o < end; i++) { // deterministic fill in pair order
-            if (idv[i] == e) {
-                pair[o++] = i;
-            }
+        __syncthreads();
+        if (s_last) {
+            csr_build(ids, (int)gridDim.x * top_k, n_expert, off, pair, active, n_active, ids_in_smem,
+                      reinterpret_cast<int32_t *>(p));
         }
     }
 }
@@ -341,8 +390,15 @@ static cudaError_t launch_chained(cudaStream_t s, void (*k)(KArgs...), dim3 grid
     return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
 }
 
+static size_t csr_smem(int n_pairs, int n_expert, int & in_smem) {
+    in_smem = n_pairs <= 8192 ? 1 : 0;
+    return (size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) * sizeof(int32_t);
+}
+
+// off != nullptr: the CSR is built by the router's last CTA
 cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float * x, int x_stride, int n_tok,
-                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts) {
+                             int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts,
+                             int32_t * off, int32_t * pair, int32_t * active, int32_t * n_active) {
     if (gate_inp) {
         cudaError_t e = launch_chained(s, moe_logits_kernel, dim3((unsigned)n_expert), dim3(256), 0, gate_inp, x, x_stride, n_tok,
                                        n_embd, n_expert, logits);
@@ -350,14 +406,20 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
             return e;
         }
     }
-    return launch_chained(s, moe_route_kernel, dim3((unsigned)n_tok), dim3(256), (size_t)n_expert * 8, x, x_stride, n_embd,
-                          n_expert, top_k, logits, ids, wts);
+    int in_smem = 0;
+    size_t smem = (size_t)n_expert * 8;
+    if (off) {
+        const size_t c = csr_smem(n_tok * top_k, n_expert, in_smem);
+        smem = smem > c ? smem : c;
+    }
+    return launch_chained(s, moe_route_kernel, dim3((unsigned)n_tok), dim3(256), smem, x, x_stride, n_embd, n_expert, top_k,
+                          logits, ids, wts, off, pair, active, n_active, in_smem);
 }
 
 cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int n_expert, int32_t * off,
                            int32_t * pair, int32_t * active, int32_t * n_active) {
-    const int in_smem = n_pairs <= 8192 ? 1 : 0;
-    const size_t smem = (size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) * sizeof(int32_t);
+    int in_smem = 0;
+    const size_t smem = csr_smem(n_pairs, n_expert, in_smem);
     return launch_chained(s, moe_csr_kernel, dim3(1), dim3(256), smem, ids, n_pairs, n_expert, off, pair, active, n_active,
                           in_smem);
 }

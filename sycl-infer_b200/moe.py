@@ -73,6 +73,16 @@ def moe_router_launch(be, gate_inp, gp_type, x, x_stride, n_tok, n_embd, n_exper
                                   _ptr(logits), _ptr(ids), _ptr(wts)))
 
 
+def moe_router_csr_launch(be, gate_inp, gp_type, x, x_stride, n_tok, n_embd, n_expert, top_k, logits, ids, wts, off,
+                          pair, active, n_active):
+    """moe_router_launch + moe_csr_launch; the router's last CTA builds the CSR (one kernel less)."""
+    if gate_inp is not None and gp_type != 0:
+        raise RuntimeError("moe_router_csr_launch: only an F32 router (ggml type 0) is implemented")
+    be.lib.check(be.lib.moe_route_csr(be._s(), _ptr(gate_inp), _ptr(x), x_stride, n_tok, n_embd, n_expert, top_k,
+                                      _ptr(logits), _ptr(ids), _ptr(wts), _ptr(off), _ptr(pair), _ptr(active),
+                                      _ptr(n_active)))
+
+
 def moe_csr_launch(be, ids, n_pairs, n_expert, off, pair, active, n_active):
     """moe_csr_clear/count/prefix/scatter_launch of the reference in one launch."""
     be.lib.check(be.lib.moe_csr(be._s(), _ptr(ids), n_pairs, n_expert, _ptr(off), _ptr(pair), _ptr(active),
@@ -107,12 +117,11 @@ def moe_reduce_launch(be, acc, wts, top_k, n_tok, n_embd, acc_stride, out, out_s
 
 
 def moe_call(be, M: moe_t, S: MoeScratch, x, n_tok, out, logits_given=False):
-    """One routed-MoE FFN: out[t] += sum_j w[t,j] * expert_{ids[t,j]}(x[t]).  Ten launches."""
+    """One routed-MoE FFN: out[t] += sum_j w[t,j] * expert_{ids[t,j]}(x[t])."""
     n_pairs = n_tok * M.top_k
     n_act_max = min(M.n_expert, n_pairs)
-    moe_router_launch(be, None if logits_given else M.gate_inp, 0, x, x.shape[1], n_tok, M.n_embd, M.n_expert,
-                      M.top_k, S.logits, S.ids, S.wts)
-    moe_csr_launch(be, S.ids, n_pairs, M.n_expert, S.off, S.pair, S.active, S.n_active)
+    moe_router_csr_launch(be, None if logits_given else M.gate_inp, 0, x, x.shape[1], n_tok, M.n_embd, M.n_expert,
+                          M.top_k, S.logits, S.ids, S.wts, S.off, S.pair, S.active, S.n_active)
     moe_actq_launch(be, x, x.shape[1], n_tok, M.n_embd, *S.xq)
     moe_grp_gate_up_launch(be, M, S.off, S.pair, S.active, S.n_active, n_act_max, *S.xq, n_tok, S.h, M.n_ff_exp)
     moe_actq_launch(be, S.h, M.n_ff_exp, n_pairs, M.n_ff_exp, *S.hq)

@@ -125,3 +125,37 @@ def test_moe_config3_full_size(be, orc, pkg):
     """256 experts, top-8, hidden 2048, expert FFN 512, Q4_K, 16 tokens."""
     n = _run_moe(be, orc, pkg, E=256, top_k=8, n_embd=2048, n_ff=512, n_tok=16, types=(12, 12, 12), seed=0xB3)
     assert 60 <= n <= 128
+
+
+@pytest.mark.parametrize("n_tok,E,top_k", [(16, 256, 8), (3, 32, 4)])
+def test_csr_separate_and_fused_agree(be, pkg, n_tok, E, top_k):
+    """Router + CSR as two entry points and as the fused one (the router's last CTA builds the
+    lists): identical ids, offsets, pair lists and active experts; the lists are checked against a
+    host construction as well."""
+    from sycl_infer_b200.moe import moe_csr_launch, moe_router_csr_launch, moe_router_launch
+    lg = pkg.synth.make_router_logits(n_tok, E, 123 + E)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    res = []
+    for fused in (False, True):
+        logits = torch.from_numpy(lg.copy()).cuda()
+        ids, wts = torch.zeros(n_tok, top_k, **i32), torch.zeros(n_tok, top_k, device="cuda")
+        off, pair = torch.zeros(E + 1, **i32), torch.zeros(n_tok * top_k, **i32)
+        active, n_active = torch.zeros(E, **i32), torch.zeros(1, **i32)
+        for rep in range(2):  # twice: the fused form's completion counter must return to zero
+            if fused:
+                moe_router_csr_launch(be, None, 0, None, 0, n_tok, 0, E, top_k, logits, ids, wts, off, pair, active, n_active)
+            else:
+                moe_router_launch(be, None, 0, None, 0, n_tok, 0, E, top_k, logits, ids, wts)
+                moe_csr_launch(be, ids, n_tok * top_k, E, off, pair, active, n_active)
+            be.synchronize()
+            if rep == 0:
+                logits.copy_(torch.from_numpy(lg))  # the router leaves probabilities in its logits scratch
+        na = int(n_active.cpu()[0])
+        res.append((ids.cpu().numpy(), off.cpu().numpy(), pair.cpu().numpy(), active.cpu().numpy()[:na], na))
+    for a, b in zip(res[0], res[1]):
+        assert np.array_equal(a, b)
+    ids, off, pair, active, na = res[0]
+    flat = ids.reshape(-1)
+    assert na == len(np.unique(flat)) and np.array_equal(active, np.unique(flat))
+    for e in range(E):
+        assert np.array_equal(pair[off[e]:off[e + 1]], np.nonzero(flat == e)[0])
