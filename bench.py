@@ -142,9 +142,15 @@ def gpu_arm(args):
         arena = PeerArena(L * 65536 + 8192, rank, world)
     layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1, rank=rank, world=world, arena=arena) for i in range(L)]
     hidden = layers[0].hidden
-    xs = [torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)).cuda() for i in range(L)]
-    attn = torch.from_numpy(pkg.synth.make_activation(1, layers[0].q_dim, 3)).cuda()
-    for ly in layers:
+    # a step's two inputs (hidden state and attention output) share one device buffer per weight
+    # set, so the end-to-end loop moves them with ONE host-to-device copy
+    q_dim = layers[0].q_dim
+    xin = [torch.zeros(hidden + q_dim, dtype=torch.float32, device="cuda") for _ in range(L)]
+    xs = [b[:hidden].view(1, hidden) for b in xin]
+    attn = torch.from_numpy(pkg.synth.make_activation(1, q_dim, 3)).cuda()
+    for i, ly in enumerate(layers):
+        xs[i].copy_(torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)))
+        ly.attn = xin[i][hidden:].view(1, q_dim)
         ly.attn.copy_(attn)
     out = arena.alloc(1, hidden) if arena is not None else torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
     full_bytes = pkg.synth.layer_weight_bytes("Q4_K_M") + 4 * (
@@ -194,15 +200,14 @@ def gpu_arm(args):
     ms = e0.elapsed_time(e1)
     # the device-resident loop is short; keep sampling clocks through the e2e loop as well
     # ---- e2e: host buffers, pinned H2D of the step's activations, D2H of its output
-    hx = [torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)).pin_memory() for i in range(L)]
-    hattn = attn.cpu().pin_memory()
+    hx = [torch.cat([torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)).view(-1), attn.cpu().view(-1)]).pin_memory()
+          for i in range(L)]
     hout = torch.zeros(1, hidden, dtype=torch.float32).pin_memory()
     dx = torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
 
     def e2e_step(i):
         ly = layers[i % L]
-        xs[i % L].copy_(hx[i % L], non_blocking=True)
-        ly.attn.copy_(hattn, non_blocking=True)
+        xin[i % L].copy_(hx[i % L], non_blocking=True)
         if graphs:
             graphs[i % L].replay()
         else:
