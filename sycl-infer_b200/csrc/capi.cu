@@ -108,9 +108,8 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
     return B200Q_OK;
 }
 
-// Kernel choice: one or two tokens (three for the types without a fast tensor-core unpack)
-// stream the weights once through shared memory and dp4a; more tokens take the tcgen05
-// kernel.  B200Q_KERNEL=rows forces the general warp-per-row kernel (A/B).
+// Kernel choice: up to four tokens stream the weights once through shared memory and dp4a; more
+// tokens (or activation packs that do not fit) take the tcgen05 kernel.  B200Q_KERNEL=rows forces the general warp-per-row kernel (A/B).
 static bool force_rows() {
     static const bool v = [] {
         const char * e = getenv("B200Q_KERNEL");
@@ -119,24 +118,17 @@ static bool force_rows() {
     return v;
 }
 // Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
-// needs 35 us for two tokens and 64 / 132 / 330 us for three / four / eight (every token repeats the
-// dp4a work), the tensor-core kernel a flat 41 us up to eight tokens (Q4_K; Q5_K, IQ4_XS and
-// Q8_0 cross over at three tokens as well; Q6_K: 33 / 92 us against 94 us).  B200Q_MMA_FROM overrides.
+// (one shared-memory activation pack per token, weights unpacked once per unit) needs 14.6 / 27.2 /
+// 27.7 us for two / three / four tokens of Q4_K against a flat 28 us of the tensor-core kernel up to
+// eight tokens; Q6_K 21.8 / 39.7 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.  Calls of up to
+// four tokens whose packs fit therefore stream; B200Q_MMA_FROM overrides.
 static int mma_from(const CallDev & c) {
     static const int env = [] {
         const char * e = getenv("B200Q_MMA_FROM");
         return e && *e ? atoi(e) : 0;
     }();
-    if (env > 0) {
-        return env;
-    }
-    int from = 3;
-    for (int i = 0; i < c.n_segs; i++) {
-        if (c.seg[i].type == kQ6_K) {
-            from = 4; // twice the MMA steps per superblock: the crossover is one token later
-        }
-    }
-    return from;
+    (void)c;
+    return env > 0 ? env : 5;
 }
 bool gemv_takes_stream(const CallDev & c) {
     return !force_rows() && c.TB < mma_from(c) && stream_supported(c);
@@ -148,8 +140,8 @@ cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     if (gemv_takes_stream(c)) {
         return launch_gemv_stream(s, c, pdl_secondary);
     }
-    // more than 8 tokens: one tcgen05 int8 MMA per 32-value group (B200Q_KERNEL=rows: dp4a)
-    if (!force_rows() && c.TB > 8) {
+    // a small batch the streaming kernel cannot hold (long K): the tensor-core kernel as well
+    if (!force_rows() && c.TB > 1) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
     return launch_gemv_rows(s, c, pdl_secondary);

@@ -232,14 +232,18 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
         }
         asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory");
     }
-    using AS = typename std::conditional<TT == 1, PackA, GlobA>::type;
+    using AS = typename std::conditional<TT == 1, PackA, PackT>::type;
     AS as;
     if constexpr (TT == 1) {
         as.pack = pack;
-    } else {
-        as.x8 = a.c.x8;
-        as.xmeta = a.c.xmeta;
-        as.xsumq = a.c.xsumq;
+    } else { // a pack per token: the activations are read from shared memory, as for one token
+        const uint32_t stride = (uint32_t)(nb * kPackSB);
+        for (int t = 0; t < a.c.TB; t++) {
+            stage_pack_token(pack + (uint32_t)t * stride, a.c, t, nb, threadIdx.x, 32 * kConsumerWarps);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory");
+        as.pack = pack;
+        as.stride = stride;
         as.TB = a.c.TB;
     }
 
@@ -290,7 +294,7 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     // engine spends about as long on a copy's fixed cost as on 750 bytes), so take whole rows
     // - one copy per tile - when two tiles of whole rows fit, else per row the largest run of
     // superblocks that leaves room for two tiles, in multiples of what one pass of a warp covers.
-    const size_t pack_probe = TT == 1 ? (size_t)nb * kPackSB : 0;
+    const size_t pack_probe = (size_t)TT * nb * kPackSB;
     const size_t room = (kSmemBudget - 128 - pack_probe) / 2; // bytes per tile with two stages
     static const int contig_env = env_int("B200Q_CONTIG", 1);
     a.tile_bytes = 0;
@@ -318,7 +322,7 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
         const int tile = st.contig ? ((kRows * nb * sbb + 32 + 15) / 16) * 16 : kRows * st.slot_bytes;
         a.tile_bytes = a.tile_bytes > tile ? a.tile_bytes : tile;
     }
-    const size_t pack_bytes = TT == 1 ? (size_t)nb * kPackSB : 0;
+    const size_t pack_bytes = (size_t)TT * nb * kPackSB;
     const size_t fixed = 128 + pack_bytes;
     if (fixed + 2 * (size_t)a.tile_bytes > (size_t)kSmemBudget) {
         return cudaErrorInvalidConfiguration;
@@ -352,9 +356,10 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
 }
 
 bool stream_supported(const CallDev & c) {
-    // the single-token activation pack (400 B per superblock) must leave room for two tiles
+    // the activation packs (400 B per superblock and token) must leave room for two tiles ...
+    const int nb = c.K >> 8, tt = c.TB == 1 ? 1 : (c.TB == 2 ? 2 : 4);
     CostSplit cs; // ... and the byte-balanced row split works in 32-bit arithmetic
-    return c.TB >= 1 && c.TB <= 8 && c.K <= 24576 && cost_split(c, 2 * kSMs, cs);
+    return c.TB >= 1 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 && cost_split(c, 2 * kSMs, cs);
 }
 
 bool stream_quantizes(const CallDev & c, const float * act_up) {
@@ -388,10 +393,7 @@ cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secon
     if (c.TB == 2) {
         return launch_stream_tt<2, 2>(s, a, pdl_secondary);
     }
-    if (c.TB <= 4) {
-        return launch_stream_tt<4, 1>(s, a, pdl_secondary);
-    }
-    return launch_stream_tt<8, 1>(s, a, pdl_secondary);
+    return launch_stream_tt<4, 1>(s, a, pdl_secondary);
 }
 
 cudaError_t read_device_status(int * status, bool clear) {

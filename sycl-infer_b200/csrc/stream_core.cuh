@@ -24,6 +24,21 @@ __device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int
     }
 }
 
+// Pack of token `tok` of a TB-token activation (group-major views).
+__device__ __forceinline__ void stage_pack_token(uint32_t pack, const CallDev & c, int tok, int n_sb, int tid, int nthr) {
+    for (int g = tid; g < 8 * n_sb; g += nthr) {
+        const size_t gi = (size_t)g * c.TB + tok;
+        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + gi * 32);
+        const uint4 x0 = __ldg(gx), x1 = __ldg(gx + 1);
+        const float sx = __ldg(c.xmeta + 2 * gi);
+        const int2 xs = __ldg(reinterpret_cast<const int2 *>(c.xsumq) + gi);
+        const uint32_t p = pack_addr(pack, g);
+        sts128(p, x0.x, x0.y, x0.z, x0.w);
+        sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
+        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
+    }
+}
+
 // The same pack straight from the fp32 activation: every CTA quantizes the whole vector
 // itself (one thread per 32-value group, the standalone quantizer's arithmetic), which removes
 // a kernel and a global round trip from the critical path between two GEMV calls.  CTA 0 also
@@ -34,8 +49,8 @@ __device__ __forceinline__ void stage_pack_quant(uint32_t pack, const CallDev & 
         float v[32];
         const float4 * src = reinterpret_cast<const float4 *>(x + (size_t)g * 32);
 #pragma unroll
-        for (int i = 0; i < 8; i++) { // a thread's eight loads share one 128-byte line
-            const float4 f = src[i];
+        for (int i = 0; i < 8; i++) { // a thread's eight loads share one 128-byte line; through L2 when peers store x
+            const float4 f = c.n_peers > 0 ? __ldcg(src + i) : src[i];
             v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
         }
         uint32_t q[8];
@@ -114,10 +129,10 @@ __device__ __forceinline__ void consume_tile1(uint32_t slot0, uint32_t slot_stri
     }
 }
 
-// 2..8 tokens: quarter-superblock units whose unpacked weights stay in registers for all tokens
-template <int TYPE, int RW, int TT>
+// 2..4 tokens: quarter-superblock units whose unpacked weights stay in registers for all tokens
+template <int TYPE, int RW, int TT, class AS>
 __device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                             int sb0, const GlobA & as, float (&acc)[RW][TT]) {
+                                             int sb0, const AS & as, float (&acc)[RW][TT]) {
     const int lane = threadIdx.x & 31;
     const int u = lane & 3;
     for (int b = lane >> 2; b < kb; b += 8) {

@@ -123,40 +123,14 @@ struct PackA { // staged pack, token 0
     }
 };
 
-struct GlobA { // the caller's group-major arrays, any token count, read through L1
-    const int8_t * x8;
-    const float * xmeta;
-    const int32_t * xsumq;
+struct PackT { // staged packs of several tokens, `stride` bytes apart
+    uint32_t pack, stride;
     int TB;
-    __device__ __forceinline__ void meta(size_t gi, GroupMeta & m) const {
-        const float2 s = __ldg(reinterpret_cast<const float2 *>(xmeta) + gi);
-        const int2 q = __ldg(reinterpret_cast<const int2 *>(xsumq) + gi);
-        m.sx = s.x;
-        m.xs0 = q.x;
-        m.xs1 = q.y;
-        m.xsf = (float)(q.x + q.y);
-    }
     __device__ __forceinline__ void g2(int g, int t, ActG2 & a) const {
-        const size_t ga = (size_t)g * TB + t, gb = ga + TB;
-        const uint4 * pa = reinterpret_cast<const uint4 *>(x8 + ga * 32);
-        const uint4 * pb = reinterpret_cast<const uint4 *>(x8 + gb * 32);
-        const uint4 a0 = __ldg(pa), a1 = __ldg(pa + 1), b0 = __ldg(pb), b1 = __ldg(pb + 1);
-        a.xa[0] = a0.x, a.xa[1] = a0.y, a.xa[2] = a0.z, a.xa[3] = a0.w;
-        a.xa[4] = a1.x, a.xa[5] = a1.y, a.xa[6] = a1.z, a.xa[7] = a1.w;
-        a.xb[0] = b0.x, a.xb[1] = b0.y, a.xb[2] = b0.z, a.xb[3] = b0.w;
-        a.xb[4] = b1.x, a.xb[5] = b1.y, a.xb[6] = b1.z, a.xb[7] = b1.w;
-        meta(ga, a.ma);
-        meta(gb, a.mb);
+        PackA{pack + (uint32_t)t * stride}.g2(g, 0, a);
     }
     __device__ __forceinline__ void g6(int g, int hs, int t, ActG6 & a) const {
-#pragma unroll
-        for (int p = 0; p < 4; p++) {
-            const size_t gi = (size_t)(g + p) * TB + t;
-            const uint4 x = __ldg(reinterpret_cast<const uint4 *>(x8 + gi * 32 + 16 * hs));
-            a.x[p][0] = x.x, a.x[p][1] = x.y, a.x[p][2] = x.z, a.x[p][3] = x.w;
-            a.sx[p] = __ldg(xmeta + 2 * gi);
-            a.xs[p] = __ldg(xsumq + 2 * gi + hs);
-        }
+        PackA{pack + (uint32_t)t * stride}.g6(g, hs, 0, a);
     }
 };
 
