@@ -106,3 +106,25 @@ def test_layer_split_world2():
     for layer in range(6):
         v = 2 * v + layer
     assert np.all(res[1][1] == v)  # the last rank holds the result of all six layers
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_config1_layer_shards_at_every_bench_width(pkg, world):
+    """Every projection of the benchmark layer splits into equal 16-row-aligned shards at 2, 4
+    and 8 ranks, and the shards tile the rows exactly (what bench.py --gpus N relies on)."""
+    from sycl_infer_b200.sharding import shard_rows
+    for name, t, n, K in pkg.synth.dense_layer_shapes("Q4_K_M", hidden=5120, n_head=40, n_kv=8, head_dim=128, n_ff=17408):
+        edges = [shard_rows(n, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+        assert len({hi - lo for lo, hi in edges}) == 1 and (edges[0][1] - edges[0][0]) % 16 == 0
+
+
+def test_gather_rows_world4():
+    res = _spawn(_gather_case, world=4)
+    for rank in range(4):
+        for TB in (1, 3):
+            got = res[rank][TB]
+            for t in range(TB):
+                assert np.array_equal(got[t, 32:96], np.arange(64, dtype=np.float32) + 1000 * t)
+                assert np.all(got[t, :32] == -1) and np.all(got[t, 96:] == -1)
