@@ -118,9 +118,9 @@ static bool force_rows() {
     return v;
 }
 // Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
-// (one shared-memory activation pack per token, weights unpacked once per unit) needs 14.6 / 27.2 /
+// (one shared-memory activation pack per token, weights unpacked once per unit) needs 14.6 / 23.0 /
 // 27.7 us for two / three / four tokens of Q4_K against a flat 28 us of the tensor-core kernel up to
-// eight tokens; Q6_K 21.8 / 39.7 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.  Calls of up to
+// eight tokens; Q6_K 21.8 / 33.0 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.  Calls of up to
 // four tokens whose packs fit therefore stream; B200Q_MMA_FROM overrides.
 static int mma_from(const CallDev & c) {
     static const int env = [] {

@@ -357,7 +357,7 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
 
 bool stream_supported(const CallDev & c) {
     // the activation packs (400 B per superblock and token) must leave room for two tiles ...
-    const int nb = c.K >> 8, tt = c.TB == 1 ? 1 : (c.TB == 2 ? 2 : 4);
+    const int nb = c.K >> 8, tt = c.TB;
     CostSplit cs; // ... and the byte-balanced row split works in 32-bit arithmetic
     return c.TB >= 1 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 && cost_split(c, 2 * kSMs, cs);
 }
@@ -392,6 +392,9 @@ cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secon
     }
     if (c.TB == 2) {
         return launch_stream_tt<2, 2>(s, a, pdl_secondary);
+    }
+    if (c.TB == 3) {
+        return launch_stream_tt<3, 1>(s, a, pdl_secondary);
     }
     return launch_stream_tt<4, 1>(s, a, pdl_secondary);
 }
