@@ -356,10 +356,18 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
 }
 
 bool stream_supported(const CallDev & c) {
-    // the activation packs (400 B per superblock and token) must leave room for two tiles ...
+    // the activation packs (400 B per superblock and token) must leave room for two tiles of
+    // at least eight superblocks per row ...
     const int nb = c.K >> 8, tt = c.TB;
+    int max_sbb = 0;
+    for (int i = 0; i < c.n_segs; i++) {
+        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+    }
+    const size_t rows = c.TB == 2 ? 2 * kConsumerWarps : kConsumerWarps; // the two-token kernel takes two rows per warp
+    const size_t min_tile = rows * (size_t)(((8 * max_sbb + 32 + 15) / 16) * 16);
     CostSplit cs; // ... and the byte-balanced row split works in 32-bit arithmetic
-    return c.TB >= 1 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 && cost_split(c, 2 * kSMs, cs);
+    return c.TB >= 1 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 &&
+           128 + (size_t)tt * nb * kPackSB + 2 * min_tile <= (size_t)kSmemBudget && cost_split(c, 2 * kSMs, cs);
 }
 
 bool stream_quantizes(const CallDev & c, const float * act_up) {

@@ -132,6 +132,22 @@ def test_gemm_parity(be, orc, pkg, t, TB):
     assert rel_err(got, ref, ab) <= TOL
 
 
+@pytest.mark.parametrize("t", (12, 14, 8))
+@pytest.mark.parametrize("TB,K", [(2, 17408), (4, 17408), (3, 8192), (4, 5120)])
+def test_small_batch_long_k(be, orc, pkg, t, TB, K):
+    """Two to four tokens with long rows: activation packs that fill half of shared memory
+    (2 x 17408), packs that do not fit (4 x 17408: the tensor-core kernel takes the call), and
+    the three- and four-token instantiations of the streaming kernel."""
+    N = 70
+    w = pkg.synth.make_weight(t, N, K, 650 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 651), None, TB)
+    ref = orc.gemm(t, w, K, N, a, alpha=0.25)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=0.25)
+    got = gpu_gemm(be, t, w, K, N, a, TB, alpha=0.25)
+    assert be.device_status() == 0
+    assert rel_err(got, ref, ab) <= TOL
+
+
 @pytest.mark.parametrize("t", (12, 14))
 def test_residual_alias_and_wide_stride(be, orc, pkg, t):
     """residual may alias out (in-place residual add, src/engine/graph.cpp:299,355 of the
