@@ -1,10 +1,10 @@
 """Micro-benchmark of one GEMV shape through the C ABI: rotating weight copies (larger than L2
 in total), a CUDA graph of back-to-back launches, CUDA-event timing.
 
-    python sycl-infer_b200/microbench.py --type 12 --rows 17408 --K 5120 [--TB 1] [--fused 1]
+    python bench_gemv.py --type 12 --rows 17408 --K 5120 [--TB 1] [--fused 1]
 """
 import argparse, sys, os, numpy as np, torch
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import __graft_entry__ as g
 pkg = g.load_package()
 from sycl_infer_b200.backend import gemv_seg, alloc_act

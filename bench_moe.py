@@ -2,10 +2,10 @@
 grouped down, reduce) through the C ABI: CUDA graph of back-to-back calls over rotating expert
 banks (larger than L2 in total), CUDA-event timing.
 
-    python sycl-infer_b200/microbench_moe.py [--tokens 16] [--experts 256] [--topk 8] [--embd 2048] [--ff 512]
+    python bench_moe.py [--tokens 16] [--experts 256] [--topk 8] [--embd 2048] [--ff 512]
 """
 import argparse, sys, os, numpy as np, torch
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import __graft_entry__ as g
 pkg = g.load_package()
 from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_call

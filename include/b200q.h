@@ -4,8 +4,18 @@
  * backend-operator interface.  Every entry point names the reference interface
  * it replaces (paths inside the reference project).  All pointers are DEVICE
  * pointers unless a parameter says "host"; the caller owns every buffer; the
- * library allocates nothing, keeps no state beyond a thread-local error string,
- * and never falls back to the CPU: an unsupported request is an error.
+ * library allocates nothing and never falls back to the CPU: an unsupported
+ * request is an error.  State the library keeps: a thread-local error string;
+ * per GPU a few device words (the status words behind b200q_device_status, the
+ * completion counter of b200q_moe_route_csr) and the 48 KB scratch array of
+ * b200q_quant_gemv_static; per process a cache of per-device kernel attributes.
+ *
+ * Launch chaining.  GEMV launches use programmatic stream serialization: a kernel
+ * may start streaming WEIGHTS while the previous kernel of the stream (when that
+ * is one of this library's) is still finishing, and waits for it before it reads
+ * an activation or writes an output.  Weights must therefore not be produced by a
+ * b200q call that directly precedes their use in the same stream (they never are:
+ * no entry point writes weights).
  *
  * `stream` is a cudaStream_t passed as void* (NULL = the legacy default
  * stream).  Calls only enqueue work; they do not synchronize.
@@ -90,6 +100,37 @@ int b200q_i8_gemm(void * stream, const b200q_seg * segs /*host*/, int n_segs, in
 int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
                      int32_t * xsumq);
 
+/* Options of b200q_quant_gemv_ex. */
+#define B200Q_OPT_PREQUANTIZED 1u /* the scratch already holds the call's quantized activation: no quantizer runs */
+
+/* Where a gate|up call leaves the NEXT call's activation.  The reference quantizes
+ * silu(gate)*up in front of the down projection (act_up, src/engine/graph.cpp:355-357;
+ * quantizer src/backend/cpu/kernels/xq.cpp:21-26); with this set, the GEMV that computes gate
+ * and up emits that quantized activation itself (one token), so the down call can run with
+ * B200Q_OPT_PREQUANTIZED and no quantizer launch lies between the two.  The call must be
+ * exactly two segments (gate, up) of equal n_rows, a multiple of 32.  group_counters:
+ * n_rows/32 words, zero before the first call; every call leaves them zero again.  Calls
+ * that share group_counters must not overlap on the GPU. */
+typedef struct b200q_next_act {
+    int8_t * x8;      /* [n_rows] codes of silu(gate)*up */
+    float * xmeta;    /* [n_rows/32][2] */
+    int32_t * xsumq;  /* [n_rows/32][2] */
+    int32_t * group_counters;
+} b200q_next_act;
+
+struct b200q_peers;
+typedef struct b200q_call_opts {
+    uint32_t flags;                  /* B200Q_OPT_* */
+    const struct b200q_peers * peers; /* host; NULL = outputs stay on this GPU (see b200q_quant_gemv_scatter) */
+    const b200q_next_act * next;     /* host; NULL = off */
+} b200q_call_opts;
+
+/* b200q_quant_gemv with options: the general form of the fused decode launch
+ * (i8_grp_quant_gemv_launch, src/backend/gpu/kernels/kernels.h:216-219; call site
+ * src/engine/graph.cpp:1513-1550, which fuses the quantizer and every segment of a call). */
+int b200q_quant_gemv_ex(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
+                        int32_t * xsumq, const b200q_call_opts * opts /*host, may be NULL*/);
+
 /* ---- row-sharded calls across the GPUs of one box (new relative to the reference, which has no
  * tensor parallelism: its only multi-device mode is the layer split, src/engine/engine.cpp:3505-3570).
  * Every rank owns a contiguous slice of each weight's rows and all ranks need the whole output.
@@ -162,7 +203,7 @@ int b200q_moe_reduce(void * stream, const float * acc, const float * wts, int to
  * it: an engine that committed all device memory to its weight blob and arena up front, a
  * plugin that must not call cudaMalloc in its host process, a call site where allocation is
  * illegal.  They cannot provide the int8 activation scratch b200q_quant_gemv asks for, so
- * this entry point uses a scratch array built into the library image (56 KB on every GPU
+ * this entry point uses a scratch array built into the library image (48 KB on every GPU
  * that loads the library, for the life of the process).  It allocates nothing and calls no
  * allocating routine.  Limits and rules:
  *  - one token per call (TB = 1) and K <= B200Q_STATIC_MAX_K; larger K is refused with
@@ -178,7 +219,10 @@ int b200q_quant_gemv_static(void * stream, const b200q_seg * segs /*host*/, int 
 /* Parity instrument: the exact int32 per-group dot products the reference forms inside
  * q4k/q5k/q6k_i8_block (src/backend/cpu/kernels/i8.cpp:57,117,149) for token t.
  * wd[row*D + j], D = K/32 (K/16 for Q6_K: raw codes 0..63, 16-value scale groups).
- * Uses the same device unpack + dp4a code as the GEMV kernels. */
+ * The sums are formed by the code that serves a call of TB tokens: the dp4a decoders of
+ * the streaming kernels up to four tokens, and from five tokens on the tcgen05 kernel
+ * itself (same operand unpack, same MMAs, same tensor-memory loads; its epilogue stores
+ * the int32 accumulators instead of folding them). */
 int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int n_rows, const int8_t * x8, int TB,
                         int t, int32_t * wd);
 

@@ -123,6 +123,23 @@ class cuda_backend:
         s0 = segs[0] if not isinstance(segs, gemv_seg) else segs
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
+    def quant_gemv_ex(self, segs, TB=1, prequantized=False, peers=None, next_act=None, counters=None):
+        """quant_gemv with options: `prequantized` skips the quantizer (the segments' scratch holds
+        the activation already); `peers` scatters the outputs; `next_act` = (x8, xmeta, xsumq) and
+        `counters` make a gate|up call emit the quantized silu(gate)*up of the following call."""
+        from .capi import CallOpts, NextAct, OPT_PREQUANTIZED
+        arr, n = _pack(segs)
+        s0 = segs[0]
+        opts = CallOpts()
+        opts.flags = OPT_PREQUANTIZED if prequantized else 0
+        if peers is not None:
+            opts.peers = C.pointer(peers)
+        if next_act is not None:
+            na = NextAct(_ptr(next_act[0]), _ptr(next_act[1]), _ptr(next_act[2]), _ptr(counters))
+            opts.next = C.pointer(na)
+        self.lib.check(self.lib.quant_gemv_ex(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq),
+                                              C.byref(opts)))
+
     def quant_gemv_scatter(self, segs, TB, peers):
         """quant_gemv whose outputs are also stored into the peers' copies of the output arena."""
         arr, n = _pack(segs)

@@ -25,6 +25,19 @@ class Peers(C.Structure):
     _fields_ = [("n_peers", C.c_int32), ("out_delta", C.c_int64 * 7)]
 
 
+class NextAct(C.Structure):
+    """struct b200q_next_act."""
+    _fields_ = [("x8", _vp), ("xmeta", _vp), ("xsumq", _vp), ("group_counters", _vp)]
+
+
+class CallOpts(C.Structure):
+    """struct b200q_call_opts."""
+    _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct))]
+
+
+OPT_PREQUANTIZED = 1
+
+
 class Seg(C.Structure):
     """struct b200q_seg, field for field."""
     _fields_ = [("w", _vp), ("type", C.c_uint32), ("K", C.c_int32), ("n_rows", C.c_int32), ("x", _vp),
@@ -40,6 +53,7 @@ _SIGS = {
     "b200q_i8_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_gemm": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int]),
     "b200q_quant_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp]),
+    "b200q_quant_gemv_ex": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(CallOpts)]),
     "b200q_quant_gemv_scatter": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(Peers)]),
     "b200q_peer_barrier": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, C.c_uint32]),
     "b200q_moe_route": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),

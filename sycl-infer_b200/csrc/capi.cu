@@ -3,6 +3,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "launch.h"
 
@@ -20,6 +23,28 @@ void set_error(const char * fmt, ...) {
 int cuda_fail(cudaError_t e, const char * what) {
     set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
     return B200Q_ECUDA;
+}
+
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of a kernel on ONE
+// device; a process that drives several GPUs must set it on each.  Remembered per (kernel, device).
+cudaError_t ensure_dynamic_smem(const void * func, int bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, int> done;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    int & have = done[std::make_pair(func, dev)];
+    if (have < bytes) {
+        e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        have = bytes;
+    }
+    return cudaSuccess;
 }
 
 static bool type_ok(uint32_t t) {
@@ -108,8 +133,10 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
     return B200Q_OK;
 }
 
-// Kernel choice: up to four tokens stream the weights once through shared memory and dp4a; more
-// tokens (or activation packs that do not fit) take the tcgen05 kernel.  B200Q_KERNEL=rows forces the general warp-per-row kernel (A/B).
+// Kernel choice.  One token: the pinned-activation streaming kernel (gemv_pinned.cu).  Two to
+// four tokens: the streaming kernel with one shared-memory activation pack per token.  More
+// tokens (or packs that do not fit): the tcgen05 kernel.  The warp-per-row kernel takes what is left.
+#ifdef B200Q_TUNING
 static bool force_rows() {
     static const bool v = [] {
         const char * e = getenv("B200Q_KERNEL");
@@ -117,24 +144,35 @@ static bool force_rows() {
     }();
     return v;
 }
-// Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
-// (one shared-memory activation pack per token, weights unpacked once per unit) needs 14.6 / 23.0 /
-// 27.7 us for two / three / four tokens of Q4_K against a flat 28 us of the tensor-core kernel up to
-// eight tokens; Q6_K 21.8 / 33.0 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.  Calls of up to
-// four tokens whose packs fit therefore stream; B200Q_MMA_FROM overrides.
-static int mma_from(const CallDev & c) {
+static int mma_from_env() {
     static const int env = [] {
         const char * e = getenv("B200Q_MMA_FROM");
         return e && *e ? atoi(e) : 0;
     }();
-    (void)c;
+    return env;
+}
+#else
+static bool force_rows() { return false; }
+static int mma_from_env() { return 0; }
+#endif
+// Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
+// needs 14.6 / 23.0 / 27.7 us for two / three / four tokens of Q4_K against a flat 28 us of the
+// tensor-core kernel up to eight tokens; Q6_K 21.8 / 33.0 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.
+static int mma_from() {
+    const int env = mma_from_env();
     return env > 0 ? env : 5;
 }
+bool gemv_takes_pinned(const CallDev & c) {
+    return !force_rows() && c.TB == 1 && pinned_supported(c);
+}
 bool gemv_takes_stream(const CallDev & c) {
-    return !force_rows() && c.TB < mma_from(c) && stream_supported(c);
+    return !force_rows() && c.TB < mma_from() && stream_supported(c);
 }
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
-    if (!force_rows() && c.TB >= mma_from(c)) {
+    if (gemv_takes_pinned(c)) {
+        return launch_gemv_pinned(s, c, nullptr, nullptr);
+    }
+    if (!force_rows() && c.TB >= mma_from()) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
     if (gemv_takes_stream(c)) {
@@ -145,6 +183,80 @@ cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
         return launch_gemm_mma(s, c, pdl_secondary);
     }
     return launch_gemv_rows(s, c, pdl_secondary);
+}
+
+// Shared body of the fused quantize + GEMV entry points.
+int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8,
+                    float * xmeta, int32_t * xsumq, const b200q_call_opts * opts) {
+    if (!x8 || !xmeta || !xsumq) {
+        set_error("%s: scratch x8/xmeta/xsumq must be non-null", who);
+        return B200Q_EINVAL;
+    }
+    CallDev c;
+    const int rc = build_call(segs, n_segs, TB, x8, xmeta, xsumq, c);
+    if (rc != B200Q_OK) {
+        return rc;
+    }
+    const bool prequant = opts && (opts->flags & B200Q_OPT_PREQUANTIZED);
+    const b200q_seg & s0 = segs[0];
+    if (!prequant) {
+        if (!s0.x || s0.x_stride < s0.K) {
+            set_error("%s: segs[0].x must be non-null with x_stride >= K", who);
+            return B200Q_EINVAL;
+        }
+        for (int i = 1; i < n_segs; i++) {
+            if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
+                set_error("%s: segment %d does not share the call's activation", who, i);
+                return B200Q_EINVAL;
+            }
+        }
+    }
+    if (opts && opts->peers) {
+        const b200q_peers * peers = opts->peers;
+        if (peers->n_peers < 0 || peers->n_peers > B200Q_MAX_PEERS) {
+            set_error("%s: n_peers must be 0..%d (got %d)", who, B200Q_MAX_PEERS, peers->n_peers);
+            return B200Q_EINVAL;
+        }
+        c.n_peers = peers->n_peers;
+        for (int i = 0; i < peers->n_peers; i++) {
+            if (peers->out_delta[i] & 3) {
+                set_error("%s: out_delta[%d] is not a multiple of 4 bytes", who, i);
+                return B200Q_EINVAL;
+            }
+            c.peer_delta[i] = peers->out_delta[i];
+        }
+    }
+    NextAct next{nullptr, nullptr, nullptr, nullptr};
+    if (opts && opts->next) {
+        const b200q_next_act & n = *opts->next;
+        if (!n.x8 || !n.xmeta || !n.xsumq || !n.group_counters || !aligned(n.xmeta, 8) || !aligned(n.xsumq, 8)) {
+            set_error("%s: next-activation views must be non-null (xmeta, xsumq 8-byte aligned)", who);
+            return B200Q_EINVAL;
+        }
+        if (TB != 1 || n_segs != 2 || segs[0].n_rows != segs[1].n_rows || (segs[0].n_rows & 31) || c.n_peers > 0) {
+            set_error("%s: the next-activation form needs one token, two segments (gate, up) of equal n_rows, a "
+                      "multiple of 32, and no peers", who);
+            return B200Q_EINVAL;
+        }
+        if (!gemv_takes_pinned(c) || !pinned_pairs_supported(c)) {
+            set_error("%s: the next-activation form needs gate and up of one type and a supported K (K=%d)", who, c.K);
+            return B200Q_EUNSUPPORTED;
+        }
+        next = NextAct{n.group_counters, n.x8, n.xmeta, n.xsumq};
+    }
+    if (gemv_takes_pinned(c)) {
+        const bool inside = !prequant && pinned_quantizes(c, s0.x, s0.act_up);
+        if (!prequant && !inside) {
+            B200Q_CUDA_OK(launch_xq(stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB, s0.K, true));
+        }
+        B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.cnt ? &next : nullptr));
+        return B200Q_OK;
+    }
+    if (!prequant) {
+        B200Q_CUDA_OK(launch_xq(stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB, s0.K, true));
+    }
+    B200Q_CUDA_OK(launch_gemv(stream, c, true));
+    return B200Q_OK;
 }
 
 } // namespace b200q
@@ -199,78 +311,23 @@ int b200q_i8_gemv(void * stream, const b200q_seg * segs, int n_segs) {
 
 int b200q_quant_gemv(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
                      int32_t * xsumq) {
-    if (!x8 || !xmeta || !xsumq) {
-        set_error("b200q_quant_gemv: scratch x8/xmeta/xsumq must be non-null");
-        return B200Q_EINVAL;
-    }
-    CallDev c;
-    const int rc = build_call(segs, n_segs, TB, x8, xmeta, xsumq, c);
-    if (rc != B200Q_OK) {
-        return rc;
-    }
-    const b200q_seg & s0 = segs[0];
-    if (!s0.x || s0.x_stride < s0.K) {
-        set_error("b200q_quant_gemv: segs[0].x must be non-null with x_stride >= K");
-        return B200Q_EINVAL;
-    }
-    for (int i = 1; i < n_segs; i++) {
-        if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
-            set_error("b200q_quant_gemv: segment %d does not share the call's activation", i);
-            return B200Q_EINVAL;
-        }
-    }
-    if (gemv_takes_stream(c) && stream_quantizes(c, s0.act_up)) { // one launch: the GEMV quantizes in its prologue
-        B200Q_CUDA_OK(launch_gemv_stream((cudaStream_t)stream, c, true, s0.x));
-        return B200Q_OK;
-    }
-    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
-                            s0.K, true));
-    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));
-    return B200Q_OK;
+    return quant_gemv_call("b200q_quant_gemv", (cudaStream_t)stream, segs, n_segs, TB, x8, xmeta, xsumq, nullptr);
+}
+
+int b200q_quant_gemv_ex(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
+                        int32_t * xsumq, const b200q_call_opts * opts) {
+    return quant_gemv_call("b200q_quant_gemv_ex", (cudaStream_t)stream, segs, n_segs, TB, x8, xmeta, xsumq, opts);
 }
 
 int b200q_quant_gemv_scatter(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
                              int32_t * xsumq, const b200q_peers * peers) {
-    if (!x8 || !xmeta || !xsumq || !peers) {
-        set_error("b200q_quant_gemv_scatter: scratch and peers must be non-null");
+    if (!peers) {
+        set_error("b200q_quant_gemv_scatter: peers must be non-null");
         return B200Q_EINVAL;
     }
-    if (peers->n_peers < 0 || peers->n_peers > B200Q_MAX_PEERS) {
-        set_error("b200q_quant_gemv_scatter: n_peers must be 0..%d (got %d)", B200Q_MAX_PEERS, peers->n_peers);
-        return B200Q_EINVAL;
-    }
-    CallDev c;
-    const int rc = build_call(segs, n_segs, TB, x8, xmeta, xsumq, c);
-    if (rc != B200Q_OK) {
-        return rc;
-    }
-    const b200q_seg & s0 = segs[0];
-    if (!s0.x || s0.x_stride < s0.K) {
-        set_error("b200q_quant_gemv_scatter: segs[0].x must be non-null with x_stride >= K");
-        return B200Q_EINVAL;
-    }
-    for (int i = 1; i < n_segs; i++) {
-        if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
-            set_error("b200q_quant_gemv_scatter: segment %d does not share the call's activation", i);
-            return B200Q_EINVAL;
-        }
-    }
-    c.n_peers = peers->n_peers;
-    for (int i = 0; i < peers->n_peers; i++) {
-        if (peers->out_delta[i] & 3) {
-            set_error("b200q_quant_gemv_scatter: out_delta[%d] is not a multiple of 4 bytes", i);
-            return B200Q_EINVAL;
-        }
-        c.peer_delta[i] = peers->out_delta[i];
-    }
-    if (gemv_takes_stream(c) && stream_quantizes(c, s0.act_up)) { // one launch: the GEMV quantizes in its prologue
-        B200Q_CUDA_OK(launch_gemv_stream((cudaStream_t)stream, c, true, s0.x));
-        return B200Q_OK;
-    }
-    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB,
-                            s0.K, true));
-    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));
-    return B200Q_OK;
+    b200q_call_opts opts = {};
+    opts.peers = peers;
+    return quant_gemv_call("b200q_quant_gemv_scatter", (cudaStream_t)stream, segs, n_segs, TB, x8, xmeta, xsumq, &opts);
 }
 
 int b200q_peer_barrier(void * stream, uint32_t * const * flags, int world, int rank, uint32_t seq) {
@@ -298,14 +355,35 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
         set_error("b200q_i8_block_dots: bad shape or alignment (K=%d n_rows=%d TB=%d t=%d)", K, n_rows, TB, t);
         return B200Q_EINVAL;
     }
-    // same rule as the GEMV dispatch: up to 8 tokens run the streaming kernel's decode path,
-    // more tokens the rows kernel's
-    if (TB <= 8) {
-        B200Q_CUDA_OK(launch_unit_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows, x8,
-                                       TB, t, wd));
+    // Same rule as the GEMV dispatch, so the sums come out of the code that serves such a call:
+    // one token: the half-superblock decoders of the pinned kernel; two to four: the streaming
+    // kernel's quarter units; five and more: the tcgen05 kernel, whose epilogue then stores the
+    // accumulators it read from tensor memory instead of folding them.
+    const uint8_t * wb = static_cast<const uint8_t *>(w);
+    if (TB >= mma_from()) {
+        CallDev c;
+        memset(&c, 0, sizeof(c));
+        c.K = K;
+        c.TB = TB;
+        c.n_segs = 1;
+        c.total_rows = n_rows;
+        c.x8 = x8;
+        // the instrument has no scales or sums: the producers' loads of them land inside x8 (8 of
+        // every group's 32 bytes) and what they read is never used
+        c.xmeta = reinterpret_cast<const float *>(x8);
+        c.xsumq = reinterpret_cast<const int32_t *>(x8);
+        c.seg[0].w = wb;
+        c.seg[0].out = reinterpret_cast<float *>(wd); // never written in this mode
+        c.seg[0].alpha = 1.0f;
+        c.seg[0].type = (int32_t)type;
+        c.seg[0].n_rows = n_rows;
+        c.seg[0].out_stride = n_rows;
+        c.seg[0].row_end = n_rows;
+        B200Q_CUDA_OK(launch_gemm_mma((cudaStream_t)stream, c, false, wd, t));
+    } else if (TB == 1 && K > 65536) { // beyond the streaming kernels: the warp-per-row kernel's decoders
+        B200Q_CUDA_OK(launch_block_dots((cudaStream_t)stream, wb, (int)type, K, n_rows, x8, TB, t, wd));
     } else {
-        B200Q_CUDA_OK(launch_block_dots((cudaStream_t)stream, static_cast<const uint8_t *>(w), (int)type, K, n_rows,
-                                        x8, TB, t, wd));
+        B200Q_CUDA_OK(launch_unit_dots((cudaStream_t)stream, wb, (int)type, K, n_rows, x8, TB, t, wd));
     }
     return B200Q_OK;
 }
@@ -382,6 +460,10 @@ int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uin
     if (rc != B200Q_OK) {
         return rc;
     }
+    if (!aligned(x8, 16) || !aligned(xmeta, 8) || !aligned(xsumq, 8)) {
+        set_error("b200q_moe_gate_up: x8 must be 16-byte aligned, xmeta and xsumq 8-byte aligned");
+        return B200Q_EINVAL;
+    }
     if (n_act_max < 1 || n_tok < 1 || top_k < 1 || h_stride < n_ff_exp || (slot_gb & 15) || (slot_ub & 15)) {
         set_error("b200q_moe_gate_up: bad n_act_max/n_tok/top_k/h_stride or plane bytes not a multiple of 16");
         return B200Q_EINVAL;
@@ -402,6 +484,10 @@ int b200q_moe_down(void * stream, const void * dbank, uint32_t dtype, size_t slo
     }
     if (rc != B200Q_OK) {
         return rc;
+    }
+    if (!aligned(h8, 16) || !aligned(hmeta, 8) || !aligned(hsumq, 8)) {
+        set_error("b200q_moe_down: h8 must be 16-byte aligned, hmeta and hsumq 8-byte aligned");
+        return B200Q_EINVAL;
     }
     if (n_act_max < 1 || n_pairs < 1 || acc_stride < n_embd || (slot_db & 15)) {
         set_error("b200q_moe_down: bad n_act_max/n_pairs/acc_stride or plane bytes not a multiple of 16");
@@ -438,6 +524,9 @@ int b200q_device_status(int * status, int clear) {
     int moe = 0;
     B200Q_CUDA_OK(read_moe_status(&moe, clear != 0));
     *status = *status ? *status : moe;
+    int pin = 0;
+    B200Q_CUDA_OK(read_pin_status(&pin, clear != 0));
+    *status = *status ? *status : pin;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

@@ -126,6 +126,14 @@ struct CallDev {
     int64_t peer_delta[B200Q_MAX_PEERS];
 };
 
+// gate|up calls: where the quantized silu(gate)*up of the following call goes (b200q_next_act)
+struct NextAct {
+    int32_t * cnt; // per 32-row group: output values stored so far (nullptr: feature off)
+    int8_t * x8;
+    float * xmeta;
+    int32_t * xsumq;
+};
+
 #ifdef __CUDACC__
 __device__ __forceinline__ void store_out(const CallDev & c, float * p, float v) {
     *p = v;

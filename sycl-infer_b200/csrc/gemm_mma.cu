@@ -58,6 +58,10 @@ struct MmaArgs {
     int32_t raw_bytes; // per-thread staging bytes for one raw superblock (16-byte units)
     int32_t depth;     // operand slots in the shared-memory ring
     int32_t lbo, sbo; // operand descriptor strides (bytes): K-adjacent core matrices, 8-row groups
+    // parity instrument: when set, the epilogue stores the raw int32 accumulators of token dump_t
+    // (dump[row * D + step], D steps per row) exactly as tcgen05.ld returned them, and folds nothing
+    int32_t * dump;
+    int32_t dump_t;
 };
 
 template <int TYPE> struct StepFmt { // steps (MMAs) per superblock, operand signedness
@@ -509,6 +513,22 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(bars.acc_empty + 8 * grp); // the batch's accumulators may be overwritten
+            if (a.dump) { // parity instrument: the tensor core's int32 sums as they are
+                const int tcol = a.dump_t - t0 - c0;
+                if (tcol >= 0 && tcol < NC && row0 + rl < sg.n_rows) {
+                    const size_t D = (size_t)slots * kSlotSteps;
+#pragma unroll
+                    for (int b = 0; b < BATCH; b++) {
+#pragma unroll
+                        for (int j = 0; j < NC; j++) {
+                            if (j == tcol) {
+                                a.dump[(size_t)(row0 + rl) * D + (size_t)(kSlotSteps * i + st0 + b)] = (int32_t)v[b][j];
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (int b = 0; b < BATCH; b++) {
                 const int st = st0 + b;
@@ -556,7 +576,7 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
             mbar_arrive(bars.done + 8 * slot); // the operand slot and its factors may be refilled
         }
     }
-    if (ok) {
+    if (ok && !a.dump) {
         const int row = row0 + rl;
         if (row < sg.n_rows) {
 #pragma unroll
@@ -662,20 +682,13 @@ template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, M
     }
     int depth = (int)((budget - kHdr - raw) / Slot<NT>::BYTES);
     depth = depth > kMaxDepth ? kMaxDepth : depth;
-    if (const char * e = getenv("B200Q_MMA_DEPTH")) {
-        const int d = atoi(e);
-        depth = d >= 2 && d <= depth ? d : depth;
-    }
     a.depth = depth;
     const size_t smem = kHdr + (size_t)depth * Slot<NT>::BYTES + raw;
-    static size_t configured = 0;
-    if (configured < smem) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_mma_kernel<NT, EW, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+    {
+        cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_mma_kernel<NT, EW, PG>), (int)smem);
         if (e != cudaSuccess) {
             return e;
         }
-        configured = smem;
     }
     a.n_tiles_t = (a.c.TB + NT - 1) / NT;
     const int tiles = a.n_tiles_m * a.n_tiles_t;
@@ -692,9 +705,11 @@ template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, M
     return cudaLaunchKernelEx(&cfg, gemm_mma_kernel<NT, EW, PG>, a);
 }
 
-cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
+cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondary, int32_t * dump, int dump_t) {
     MmaArgs a;
     a.c = c;
+    a.dump = dump;
+    a.dump_t = dump_t;
     int tiles = 0, need = 0;
     for (int i = 0; i < c.n_segs; i++) {
         tiles += (c.seg[i].n_rows + kTileM - 1) / kTileM;

@@ -1,0 +1,711 @@
+// Single-token decode GEMV: the HBM-bound kernel of the library.
+//
+// Every consumer thread is pinned to ONE 128-value unit of the input vector (four activation
+// groups) for the whole launch and keeps that unit's quantized activation - 128 int8 codes,
+// four scales, the sums the min / offset terms need - in registers.  A step of the CTA is R
+// whole weight rows; the 32*W consumer threads cover R row slots x U units (U = K / 128), so
+// a thread's work per step is exactly one unit of one row: load 72..136 bytes of raw GGUF
+// blocks from shared memory, unpack, dp4a against registers, apply the fp32 scales.  No
+// activation is re-read from shared memory, lanes are fully used whatever K is (W is chosen
+// per call so that R*U fills 32*W), and a call with few rows per SM loses nothing to ragged
+// tiles.
+//
+// Data movement.  One CTA per SM.  A producer thread brings the R contiguous rows of a step
+// into a ring of shared-memory stages with ONE bulk asynchronous copy (cp.async.bulk, the 1-D
+// TMA path, no multicast) that completes on an mbarrier; the ring holds up to ~200 KB per SM.
+// A copy starts on a 16-byte boundary: rows that start at address A are fetched from A & ~15
+// and decoded from offset A & 15 (Q6_K / Q8_0 rows are only 2-byte aligned).
+//
+// Reduction.  Lanes are summed in aligned segments of `seg` lanes (the largest power of two
+// that divides U, so a segment never straddles two rows) with butterfly shuffles; one lane per
+// segment stores the partial into a small shared-memory array [slot][part]; a dedicated
+// epilogue warp (lane = row slot) adds the U/seg partials of its row in a fixed order, applies
+// alpha and the residual and stores the outputs (also into the peers' copies for row-sharded
+// calls).  For a gate|up call it can also form silu(gate)*up and quantize
+// it per 32 rows as soon as both halves of a group are complete, so the following down call
+// needs no quantizer launch.
+//
+// Chaining.  The kernel is launched with programmatic stream serialization: its producer
+// prefetches weights while the previous kernel of the stream is still draining; consumers and
+// the epilogue execute griddepcontrol.wait before they touch the activation or any output.
+// Early starts only happen behind kernels that trigger them (this library's own), and none of
+// those writes weights.
+//
+// Every mbarrier wait is bounded by a clock budget; a wait that runs out records
+// B200Q_ETIMEOUT in a status word the host reads (b200q_device_status) and the role returns.
+#include <mutex>
+
+#include "launch.h"
+#include "stream_core.cuh"
+
+namespace b200q {
+
+constexpr int kPinMaxW = 18;                      // consumer warps
+constexpr int kPinThreads = 32 * (kPinMaxW + 2);  // + producer warp + epilogue warp
+constexpr int kPinSmem = 227 * 1024;
+constexpr int kRedBufs = 4;   // partial-sum buffers in flight between consumers and the epilogue warp
+constexpr int kPinHdr = 256;  // mbarriers and flags at the start of shared memory
+
+__device__ int g_pin_status = 0;
+
+struct PinArgs {
+    CallDev c;
+    CostSplit cost;
+    const float * xq_x; // when set, every CTA quantizes this fp32 activation itself
+    NextAct next;       // gate|up calls: quantized silu(gate)*up for the following call (cnt == nullptr: off)
+    int32_t W, R, U, seg, P, Ppad; // P = U / seg partials per row, rows Ppad words apart
+    // paired mode (next.cnt != nullptr): a step is H gate rows and the H up rows of the same
+    // indices; the up rows sit half_off bytes into the stage
+    int32_t H, half_off;
+    int32_t stages, stage_bytes, red_bytes;
+    int32_t off_pack, off_tiles;
+};
+
+struct PinRing {
+    int stage;
+    uint32_t phase;
+    int rb;
+    uint32_t rphase;
+    __device__ __forceinline__ void advance(int S) {
+        if (++stage == S) {
+            stage = 0;
+            phase ^= 1;
+        }
+        if (++rb == kRedBufs) {
+            rb = 0;
+            rphase ^= 1;
+        }
+    }
+};
+
+// Paired mode: the CTA's range of (gate row, up row) pairs.  Both segments have the same type
+// and row count, so a pair costs 2 x bytes-per-superblock.
+__device__ __forceinline__ RowRange pair_rows(const CallDev & c, uint32_t lo, uint32_t hi) {
+    const uint32_t w = 2u * (uint32_t)sb_bytes(c.seg[0].type);
+    RowRange r;
+    r.lo = (int)((lo + w - 1) / w);
+    r.hi = (int)((hi + w - 1) / w);
+    r.hi = r.hi < c.seg[0].n_rows ? r.hi : c.seg[0].n_rows;
+    return r;
+}
+
+// A wait whose clock budget only runs while `gate` (a shared-memory word) is non-zero: the
+// producer must not time out while the consumers are still parked behind the previous kernel.
+__device__ __forceinline__ bool mbar_wait_gated(uint32_t bar, uint32_t parity, int * status, uint32_t gate) {
+    long long t0 = 0;
+    for (uint32_t n = 0;; n++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) {
+            return true;
+        }
+        if (n == 64) {
+            t0 = clock64();
+        } else if (n > 64 && clock64() - t0 > kSpinCycles) {
+            uint32_t g;
+            asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(g) : "r"(gate) : "memory");
+            if (g) {
+                break;
+            }
+            t0 = clock64();
+        }
+    }
+    atomicExch(status, B200Q_ETIMEOUT);
+    return false;
+}
+
+// ---- activation: quantize (8 threads per 32-value group) or fetch, then pin --------------------
+// The arithmetic is the standalone quantizer's (xq.cuh), bit for bit: max and integer sums are
+// exact in any order, every fp32 operation is a single correctly rounded one.
+__device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, const float * x, int G, int warp,
+                                             int lane, int W, bool write_views) {
+    constexpr int kBatch = 4; // loads of several passes in flight before the first is used
+    const int stride = 32 * W, n_tasks = 8 * G;
+    for (int base0 = warp * 32; base0 < n_tasks; base0 += kBatch * stride) {
+        float4 fb[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+            const int task = base0 + i * stride + lane;
+            fb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (task < n_tasks) { // through L2 when peers store x
+                const float4 * src = reinterpret_cast<const float4 *>(x) + task;
+                fb[i] = c.n_peers > 0 ? __ldcg(src) : *src;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+            if (base0 + i * stride >= n_tasks) { // uniform per warp
+                break;
+            }
+            const int task = base0 + i * stride + lane;
+            const bool valid = task < n_tasks;
+            const int g = task >> 3, j = task & 7;
+            const float4 f = fb[i];
+            float mx = fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w)));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 4));
+            const float inv = mx > 0.0f ? __fdiv_rn(127.0f, mx) : 0.0f;
+            const float v[4] = {f.x, f.y, f.z, f.w};
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const float r = fminf(127.0f, fmaxf(-127.0f, roundf(__fmul_rn(v[b], inv))));
+                word |= ((uint32_t)(int)r & 0xFFu) << (8 * b);
+            }
+            int s = __dp4a((int)word, 0x01010101, 0);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+            const int other = __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+            const int s0 = (j & 4) ? other : s, s1 = (j & 4) ? s : other;
+            const float sx = h2f(f2h_trunc(mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 0.0f));
+            if (valid) {
+                const uint32_t p = pack_addr(pack, g);
+                sts32(p + 4 * j, word);
+                if (j == 0) {
+                    sts128(p + 32, __float_as_uint(sx), (uint32_t)s0, (uint32_t)s1,
+                           __float_as_uint(sx * (float)(s0 + s1)));
+                }
+                if (write_views) {
+                    reinterpret_cast<uint32_t *>(const_cast<int8_t *>(c.x8))[task] = word;
+                    if (j == 0) {
+                        reinterpret_cast<float2 *>(const_cast<float *>(c.xmeta))[g] = make_float2(sx, 0.0f);
+                        reinterpret_cast<int2 *>(const_cast<int32_t *>(c.xsumq))[g] = make_int2(s0, s1);
+                    }
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & a) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t p = pack_addr(pack, 4 * unit + i);
+        const uint4 x0 = lds128(p), x1 = lds128(p + 16), m = lds128(p + 32);
+        a.x[i][0] = x0.x, a.x[i][1] = x0.y, a.x[i][2] = x0.z, a.x[i][3] = x0.w;
+        a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
+        a.sx[i] = __uint_as_float(m.x);
+        a.xs[i][0] = (int)m.y;
+        a.xs[i][1] = (int)m.z;
+        a.c[i] = __uint_as_float(m.w);
+    }
+}
+
+// The pack from the caller's quantized views (one token): each group is fetched ONCE per CTA.
+// (Every thread fetching its own unit straight from global memory makes all row slots of all
+// CTAs hit the same few lines of xmeta / xsumq, which serialises in one L2 slice.)
+__device__ __forceinline__ void pin_stage_views(uint32_t pack, const CallDev & c, int G, int tid, int nthr) {
+    for (int g = tid; g < G; g += nthr) { // one token: group index == array index
+        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + (size_t)g * 32);
+        const uint4 x0 = __ldcg(gx), x1 = __ldcg(gx + 1);
+        const float sx = __ldcg(c.xmeta + 2 * (size_t)g);
+        const int2 xs = __ldcg(reinterpret_cast<const int2 *>(c.xsumq) + g);
+        const uint32_t p = pack_addr(pack, g);
+        sts128(p, x0.x, x0.y, x0.z, x0.w);
+        sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
+        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
+    }
+}
+
+// One thread, one unit (half h of the superblock at shared address sb) of one row.
+template <int TYPE> __device__ __forceinline__ float pinned_term(uint32_t sb, int h, const ActPin & p) {
+    if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+        return HalfK45<TYPE>::term(sb, h, p);
+    } else if constexpr (TYPE == kQ6_K) {
+        return HalfQ6::term(sb, h, p);
+    } else { // two quarter units of two groups each
+        float r = 0.f;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            WUnit<TYPE> w;
+            w.load(sb, 2 * h + e);
+            ActG2 g;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                g.xa[k] = p.x[2 * e][k];
+                g.xb[k] = p.x[2 * e + 1][k];
+            }
+            g.ma.sx = p.sx[2 * e];
+            g.mb.sx = p.sx[2 * e + 1];
+            r += w.term(g);
+        }
+        return r;
+    }
+}
+
+struct PinBars {
+    uint32_t full, empty, red_full, red_empty;
+};
+
+// Rows [lo, hi) of weight w0 - and, in paired mode, the same rows of w1 in the slots from H on.
+template <int TYPE>
+__device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_t * w0, const uint8_t * w1, int lo,
+                                                 int hi, uint32_t tiles, uint32_t red, const PinBars & bars,
+                                                 const ActPin & pin, int slot, int unit, PinRing & pos) {
+    constexpr uint32_t SB = Fmt<TYPE>::SB;
+    const int lane = threadIdx.x & 31;
+    const int H = a.H, S = a.stages;
+    const uint32_t row_bytes = (uint32_t)(a.c.K >> 8) * SB;
+    const int part = slot >= H ? 1 : 0, sl = slot - part * H; // normal mode: H == R, part 0 only
+    const bool mine = slot < a.R;
+    const uint32_t wbase = (uint32_t)(reinterpret_cast<uintptr_t>(part ? w1 : w0) & 15);
+    const uint32_t my_off = (uint32_t)(part * a.half_off) + (uint32_t)sl * row_bytes + (uint32_t)(unit >> 1) * SB;
+    const int seg = a.seg;
+    const uint32_t red_off = (uint32_t)(slot * a.Ppad + unit / seg) * 4u;
+    const bool writer = (lane & (seg - 1)) == 0;
+    const int h = unit & 1;
+    for (int row0 = lo; row0 < hi; row0 += H) {
+        if (!mbar_wait(bars.full + 8 * pos.stage, pos.phase, &g_pin_status)) {
+            return false;
+        }
+        const bool active = mine && sl < hi - row0;
+        float v = 0.f;
+        if (active) {
+            const uint32_t mis = (wbase + (uint32_t)row0 * row_bytes) & 15u; // only the low four bits matter
+            v = pinned_term<TYPE>(tiles + (uint32_t)(pos.stage * a.stage_bytes) + mis + my_off, h, pin);
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { // all lanes of a segment belong to the same row slot
+            if (o < seg) {
+                v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+            }
+        }
+        if (!mbar_wait(bars.red_empty + 8 * pos.rb, pos.rphase ^ 1, &g_pin_status)) {
+            return false;
+        }
+        if (writer && active) {
+            sts32(red + (uint32_t)(pos.rb * a.red_bytes) + red_off, __float_as_uint(v));
+        }
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(bars.red_full + 8 * pos.rb);
+            mbar_arrive(bars.empty + 8 * pos.stage);
+        }
+        pos.advance(S);
+    }
+    return true;
+}
+
+template <int TYPE>
+__device__ __forceinline__ bool pin_consume_call(const PinArgs & a, int si, uint32_t cost_lo, uint32_t cost_hi,
+                                                 uint32_t tiles, uint32_t red, const PinBars & bars, const ActPin & pin,
+                                                 int slot, int unit, PinRing & pos) {
+    if (a.next.cnt) { // gate rows and up rows together
+        const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
+        return pin_consume_rows<TYPE>(a, a.c.seg[0].w, a.c.seg[1].w, pr.lo, pr.hi, tiles, red, bars, pin, slot, unit, pos);
+    }
+    const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+    return pin_consume_rows<TYPE>(a, a.c.seg[si].w, a.c.seg[si].w, rr.lo, rr.hi, tiles, red, bars, pin, slot, unit, pos);
+}
+
+// silu(gate)*up of rows [32g, 32g+32) quantized as b200q_xq would (one token); lane i holds
+// gate and up of row 32g + i.
+__device__ __forceinline__ void next_act_group(const PinArgs & a, int g, int lane, float gv, float uv) {
+    const float v = __fmul_rn(silu_exact(gv), uv);
+    float scale;
+    int s0, s1;
+    const int q = xq_group(v, lane, scale, s0, s1);
+    a.next.x8[32 * g + lane] = (int8_t)q;
+    if (lane == 0) {
+        a.next.xmeta[2 * g] = scale;
+        a.next.xmeta[2 * g + 1] = 0.0f;
+        a.next.xsumq[2 * g] = s0;
+        a.next.xsumq[2 * g + 1] = s1;
+    }
+}
+
+// A group this CTA owns only part of (`mine` of its 32 pairs, already stored): publish the
+// stores, count them, and quantize the group if this CTA's rows were the last to arrive.
+__device__ __forceinline__ void next_act_shared_group(const PinArgs & a, int g, int mine, int lane) {
+    __threadfence();
+    __syncwarp();
+    int old = 0;
+    if (lane == 0) {
+        old = atomicAdd(a.next.cnt + g, mine);
+    }
+    old = __shfl_sync(0xFFFFFFFFu, old, 0);
+    if (old + mine == 32) {
+        __threadfence();
+        const float gv = __ldcg(a.c.seg[0].out + 32 * g + lane), uv = __ldcg(a.c.seg[1].out + 32 * g + lane);
+        next_act_group(a, g, lane, gv, uv);
+        if (lane == 0) {
+            a.next.cnt[g] = 0; // ready for the next call
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __grid_constant__ PinArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const PinBars bars{base, base + 64, base + 128, base + 160};
+    const uint32_t started = base + 192;
+    const uint32_t red = base + kPinHdr, pack = base + (uint32_t)a.off_pack, tiles = base + (uint32_t)a.off_tiles;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int W = a.W, R = a.R, S = a.stages, nb = a.c.K >> 8;
+    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+
+    // let the next kernel of the stream be scheduled as soon as this grid is resident
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(bars.full + 8 * s, 1);
+            mbar_init(bars.empty + 8 * s, (uint32_t)W);
+        }
+        for (int b = 0; b < kRedBufs; b++) {
+            mbar_init(bars.red_full + 8 * b, (uint32_t)W);
+            mbar_init(bars.red_empty + 8 * b, 1);
+        }
+        sts32(started, 0);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == W) {
+        // ---------------------------------------------------------------- producer (one thread)
+        if (lane != 0) {
+            return;
+        }
+        int stage = 0, issued = 0;
+        uint32_t par = 1; // parity of the empty barrier: a fresh slot is free
+        bool alive = true;
+        if (a.next.cnt) { // paired: H gate rows and the H up rows of the same indices per stage
+            const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
+            const size_t row_bytes = (size_t)nb * sb_bytes(a.c.seg[0].type);
+            for (int p0 = pr.lo; p0 < pr.hi; p0 += a.H) {
+                const int rows = min(a.H, pr.hi - p0);
+                uintptr_t A0[2];
+                uint32_t len[2];
+                for (int e = 0; e < 2; e++) {
+                    const uintptr_t A = reinterpret_cast<uintptr_t>(a.c.seg[e].w + (size_t)p0 * row_bytes);
+                    A0[e] = A & ~uintptr_t(15);
+                    len[e] = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0[e]);
+                }
+                alive = mbar_wait_gated(bars.empty + 8 * stage, par, &g_pin_status, started);
+                if (!alive) {
+                    break;
+                }
+                mbar_expect_tx(bars.full + 8 * stage, len[0] + len[1]);
+                const uint32_t dst = tiles + (uint32_t)(stage * a.stage_bytes);
+                bulk_g2s(dst, reinterpret_cast<const void *>(A0[0]), len[0], bars.full + 8 * stage);
+                bulk_g2s(dst + (uint32_t)a.half_off, reinterpret_cast<const void *>(A0[1]), len[1], bars.full + 8 * stage);
+                issued++;
+                if (++stage == S) {
+                    stage = 0;
+                    par ^= 1;
+                }
+            }
+        }
+        for (int si = 0; si < a.c.n_segs && alive && !a.next.cnt; si++) {
+            const SegDev & sg = a.c.seg[si];
+            const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+            const size_t row_bytes = (size_t)nb * sb_bytes(sg.type);
+            for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
+                const int rows = min(R, rr.hi - row0);
+                const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
+                const uintptr_t A0 = A & ~uintptr_t(15);
+                const uint32_t len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
+                alive = mbar_wait_gated(bars.empty + 8 * stage, par, &g_pin_status, started);
+                if (!alive) {
+                    break;
+                }
+                mbar_expect_tx(bars.full + 8 * stage, len);
+                bulk_g2s(tiles + (uint32_t)(stage * a.stage_bytes), reinterpret_cast<const void *>(A0), len,
+                         bars.full + 8 * stage);
+                issued++;
+                if (++stage == S) {
+                    stage = 0;
+                    par ^= 1;
+                }
+            }
+        }
+        if (!alive) { // leaving early: wait (bounded) until the copies still in flight have landed
+            for (int s = 0; s < S && s < issued; s++) {
+                const int last = ((issued - 1 - s) / S) * S + s; // last step that filled stage s
+                mbar_wait(bars.full + 8 * s, (uint32_t)(last / S) & 1u, &g_pin_status);
+            }
+        }
+        return;
+    }
+
+    // everything below reads the activation or writes outputs: wait for the previous kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp == W + 1) {
+        // ---------------------------------------------------------------- epilogue warp
+        int rb = 0;
+        uint32_t rphase = 0;
+        const int P = a.P, Ppad = a.Ppad;
+        if (a.next.cnt) {
+            // Paired mode.  Lanes 0..15 take gate slots, lanes 16..31 the up slots of the same pairs,
+            // sixteen pairs at a time.  Every stored value is also kept in a 64-pair ring in shared
+            // memory; when a 32-pair group completes, lane i forms silu(gate)*up of its row from
+            // the ring and the warp quantizes the group.  Groups shared with a neighbouring CTA
+            // (at most the first and the last of the range) are completed through a counter.
+            const uint32_t ring = red + (uint32_t)(kRedBufs * a.red_bytes); // 2 x 64 floats behind the partials
+            const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
+            const SegDev & sg0 = a.c.seg[0];
+            const SegDev & sg1 = a.c.seg[1];
+            const int H = a.H;
+            for (int p0 = pr.lo; p0 < pr.hi; p0 += H) {
+                const int rows = min(H, pr.hi - p0);
+                if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
+                    return;
+                }
+                const uint32_t rbuf = red + (uint32_t)(rb * a.red_bytes);
+                const int e = lane >> 4, li = lane & 15;
+                const SegDev & sg = e ? sg1 : sg0;
+                for (int c0 = 0; c0 < rows; c0 += 16) {
+                    if (c0 + li < rows) {
+                        const uint32_t p = rbuf + (uint32_t)((e * H + c0 + li) * Ppad) * 4u;
+                        float sum = 0.f;
+                        for (int j = 0; j < P; j++) {
+                            sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
+                        }
+                        const int row = p0 + c0 + li;
+                        float v = sg.alpha * sum;
+                        if (sg.residual) {
+                            v += sg.residual[row];
+                        }
+                        sg.out[row] = v;
+                        sts32(ring + (uint32_t)(e * 64 + (row & 63)) * 4u, __float_as_uint(v));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bars.red_empty + 8 * rb);
+                }
+                if (++rb == kRedBufs) {
+                    rb = 0;
+                    rphase ^= 1;
+                }
+                // groups whose last pair was stored in this step (H <= 32: at most two)
+                for (int g = p0 >> 5; 32 * g + 32 <= p0 + rows; g++) {
+                    if (32 * g + 32 <= p0) {
+                        continue;
+                    }
+                    if (32 * g >= pr.lo) { // all 32 pairs are this CTA's
+                        const float gv = __uint_as_float(lds32(ring + (uint32_t)((32 * g + lane) & 63) * 4u));
+                        const float uv = __uint_as_float(lds32(ring + (uint32_t)(64 + ((32 * g + lane) & 63)) * 4u));
+                        next_act_group(a, g, lane, gv, uv);
+                    } else {
+                        next_act_shared_group(a, g, 32 * g + 32 - pr.lo, lane);
+                    }
+                    __syncwarp();
+                }
+            }
+            if (pr.hi > pr.lo && (pr.hi & 31)) { // the range ends inside a group
+                const int g = pr.hi >> 5;
+                next_act_shared_group(a, g, pr.hi - max(pr.lo, 32 * g), lane);
+            }
+            return;
+        }
+        for (int si = 0; si < a.c.n_segs; si++) {
+            const SegDev & sg = a.c.seg[si];
+            const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+            for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
+                const int rows = min(R, rr.hi - row0);
+                if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
+                    return;
+                }
+                const uint32_t rbuf = red + (uint32_t)(rb * a.red_bytes);
+                for (int c0 = 0; c0 < rows; c0 += 32) { // lane = row slot; partials added in a fixed order
+                    if (c0 + lane < rows) {
+                        const uint32_t p = rbuf + (uint32_t)((c0 + lane) * Ppad) * 4u;
+                        float sum = 0.f;
+                        for (int j = 0; j < P; j++) {
+                            sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
+                        }
+                        const size_t o = (size_t)(row0 + c0 + lane); // one token
+                        float v = sg.alpha * sum;
+                        if (sg.residual) {
+                            v += sg.residual[o];
+                        }
+                        store_out(a.c, &sg.out[o], v);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bars.red_empty + 8 * rb);
+                }
+                if (++rb == kRedBufs) {
+                    rb = 0;
+                    rphase ^= 1;
+                }
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    const int U = a.U;
+    const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
+    ActPin pin;
+    if (a.xq_x) {
+        pin_quantize(pack, a.c, a.xq_x, 8 * nb, warp, lane, W, blockIdx.x == 0);
+    } else {
+        pin_stage_views(pack, a.c, 8 * nb, (int)threadIdx.x, 32 * W);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
+    pin_from_pack(pack, unit, pin);
+    if (threadIdx.x == 0) {
+        asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(started), "r"(1u) : "memory");
+    }
+
+    PinRing pos{0, 0, 0, 0};
+    const int n_calls = a.next.cnt ? 1 : a.c.n_segs; // paired mode walks both segments at once
+    for (int si = 0; si < n_calls; si++) {
+        bool ok;
+        switch (a.c.seg[si].type) {
+        case kQ4_K: ok = pin_consume_call<kQ4_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kQ5_K: ok = pin_consume_call<kQ5_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kQ6_K: ok = pin_consume_call<kQ6_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kIQ4_XS: ok = pin_consume_call<kIQ4_XS>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        default: ok = pin_consume_call<kQ8_0>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        }
+        if (!ok) {
+            return;
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+// Consumer warps W and row slots R for U units per row: the most warps whose lane use
+// R*U / (32*W) is within 4 % of the best (more warps hide more latency).
+static void pick_shape(int U, bool even_rows, int & W, int & R) {
+    W = 0;
+    R = 0;
+    double best = -1.0;
+    for (int pass = 0; pass < 2; pass++) {
+        for (int w = kPinMaxW; w >= 8; w--) {
+            int r = 32 * w / U;
+            r = even_rows ? r & ~1 : r;
+            if (r < 1) {
+                continue;
+            }
+            const double use = (double)r * U / (32.0 * w);
+            if (pass == 0) {
+                best = use > best ? use : best;
+            } else if (use >= best - 0.04) {
+                W = w;
+                R = r;
+                return;
+            }
+        }
+    }
+}
+
+static uint32_t pin_grid(const CallDev & c, const PinArgs & a) {
+    const int steps = (c.total_rows + a.R - 1) / a.R;
+    return (uint32_t)(steps < kSMs ? steps : kSMs);
+}
+
+static bool pin_plan(const CallDev & c, bool paired, PinArgs & a) {
+    if (c.TB != 1 || (c.K & 255)) {
+        return false;
+    }
+    const int nb = c.K >> 8, U = c.K >> 7;
+    int W, R;
+    pick_shape(U, paired, W, R);
+    if (W == 0) {
+        return false;
+    }
+    if (paired) { // at most 32 pairs per step (the epilogue's ring holds 64), same type and rows
+        R = R > 64 ? 64 : R;
+        if (c.n_segs != 2 || c.seg[0].type != c.seg[1].type || c.seg[0].n_rows != c.seg[1].n_rows) {
+            return false;
+        }
+    }
+    int max_sbb = 0;
+    for (int i = 0; i < c.n_segs; i++) {
+        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+    }
+    const size_t row_max = (size_t)nb * max_sbb;
+    int seg = 1; // lanes summed by shuffles: the largest power of two dividing U, at most a warp
+    while (seg < 32 && U % (2 * seg) == 0) {
+        seg *= 2;
+    }
+    const int P = U / seg, Ppad = P | 1; // odd row pitch: the epilogue's lanes hit distinct banks
+    const size_t pack_bytes = (size_t)nb * kPackSB;
+    for (;; R -= paired ? 2 : 1) { // fewer row slots when two stages of R rows do not fit
+        if (R < 1) {
+            return false;
+        }
+        const size_t red_bytes = ((size_t)R * Ppad * 4 + 15) / 16 * 16;
+        const size_t off_pack = kPinHdr + kRedBufs * red_bytes + (paired ? 512 : 0); // + the epilogue's value ring
+        const size_t off_tiles = (off_pack + pack_bytes + 127) / 128 * 128;
+        const size_t half = ((size_t)(R / 2) * row_max + 32 + 15) / 16 * 16;
+        const size_t stage = paired ? (2 * half + 127) / 128 * 128 : ((size_t)R * row_max + 32 + 127) / 128 * 128;
+        a.H = paired ? R / 2 : R;
+        a.half_off = paired ? (int32_t)half : 0;
+        if (off_tiles + 2 * stage > (size_t)kPinSmem || stage >= (1u << 20)) {
+            continue;
+        }
+        int stages = (int)(((size_t)kPinSmem - off_tiles) / stage);
+        a.W = W, a.R = R, a.U = U, a.seg = seg, a.P = P, a.Ppad = Ppad;
+        a.stages = stages > 8 ? 8 : stages;
+        a.stage_bytes = (int32_t)stage;
+        a.red_bytes = (int32_t)red_bytes;
+        a.off_pack = (int32_t)off_pack;
+        a.off_tiles = (int32_t)off_tiles;
+        break;
+    }
+    return cost_split(c, pin_grid(c, a), a.cost);
+}
+
+bool pinned_supported(const CallDev & c) {
+    PinArgs a;
+    return pin_plan(c, false, a);
+}
+
+bool pinned_pairs_supported(const CallDev & c) {
+    PinArgs a;
+    return pin_plan(c, true, a);
+}
+
+bool pinned_quantizes(const CallDev & c, const float * x, const float * act_up) {
+    // the fused silu(x)*up form evaluates a double-precision exp per value: every CTA repeating
+    // that costs more than a launch; the vector loads of the in-kernel quantizer need 16-byte alignment
+    return c.TB == 1 && !act_up && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && pinned_supported(c);
+}
+
+cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next) {
+    PinArgs a;
+    a.c = c;
+    a.xq_x = xq_x;
+    a.next = next ? *next : NextAct{nullptr, nullptr, nullptr, nullptr};
+    if (!pin_plan(c, a.next.cnt != nullptr, a)) {
+        return cudaErrorInvalidConfiguration;
+    }
+    const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_pinned_kernel), kPinSmem);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pin_grid(c, a));
+    cfg.blockDim = dim3((unsigned)(32 * (a.W + 2)));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_pinned_kernel, a);
+}
+
+cudaError_t read_pin_status(int * status, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_pin_status, sizeof(int));
+    if (e == cudaSuccess && clear && *status != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_pin_status, &zero, sizeof(int));
+    }
+    return e;
+}
+
+} // namespace b200q

@@ -1,4 +1,4 @@
-// Streaming decode GEMV for 1..8 tokens: the HBM-bound kernel of the library.
+// Streaming GEMV for two to four tokens (one token runs in gemv_pinned.cu).
 //
 // Data movement.  A tile is the raw GGUF block stream of `rows_per_tile` consecutive weight
 // rows x kb superblocks.  It is brought into shared memory by bulk asynchronous copies
@@ -13,14 +13,12 @@
 // Roles.  Warp 8 is the producer: lane r issues the copy of row r of the tile.  Warps 0..7
 // are consumers: warp w owns rows RW*w .. RW*w+RW-1 of the tile for the whole K loop, so a
 // row's partial sums stay in registers and no cross-warp reduction exists.  Four lanes
-// cover a superblock (64 weights each, see units.cuh); the activation of a unit is loaded
-// once and used for all RW rows.  A single-token call stages its quantized activation once
-// per CTA in shared memory; for 2..8 tokens it is read through L1.
+// cover a superblock (64 weights each, see units.cuh); the unpacked weights of a unit stay in
+// registers for all tokens.  Every token's quantized activation is staged once per CTA in
+// shared memory as a pack (units.cuh).
 //
 // Every wait on an mbarrier is bounded by a clock budget; a wait that runs out records an
 // error status the host can read (b200q_device_status) and the CTA leaves its loop.
-#include <cstdlib>
-#include <type_traits>
 
 #include "launch.h"
 #include "stream_core.cuh"
@@ -44,8 +42,6 @@ struct StreamArgs {
     int32_t stages;
     int32_t tile_bytes; // shared bytes reserved per tile (the largest segment's)
     CostSplit cost; // the call's cost over the grid, for the row split
-    const float * xq_x; // single token: when set, every CTA quantizes this fp32 activation itself
-    int32_t dry; // experiment: stream the weights but skip the decode (results are wrong)
 };
 
 // Position in the shared-memory ring: slot and the parity of its full barrier.
@@ -89,7 +85,7 @@ __device__ __forceinline__ bool consume_segment(const StreamArgs & a, int si, co
             if (!mbar_wait(bar_full + 8 * pos.stage, pos.phase, &g_device_status)) {
                 return false;
             }
-            if (row0 < rr.hi && !a.dry) { // rows past the range hold stale bytes: their results are dropped
+            if (row0 < rr.hi) { // rows past the range hold stale bytes: their results are dropped
                 const int kb = min((int)st.kb_max, nb - sb0);
                 const uint32_t slot0 = tiles + (uint32_t)(pos.stage * a.tile_bytes) + warp_off;
                 uint32_t mis[RW];
@@ -224,19 +220,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
     // ---------------------------------------------------------------------- consumers
     // The weight copies above do not depend on the activation quantizer; all below does.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if constexpr (TT == 1) {
-        if (a.xq_x) {
-            stage_pack_quant(pack, a.c, a.xq_x, 8 * nb, threadIdx.x, 32 * kConsumerWarps, blockIdx.x == 0);
-        } else {
-            stage_pack(pack, a.c, 0, nb, threadIdx.x, 32 * kConsumerWarps);
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory");
-    }
-    using AS = typename std::conditional<TT == 1, PackA, PackT>::type;
-    AS as;
-    if constexpr (TT == 1) {
-        as.pack = pack;
-    } else { // a pack per token: the activations are read from shared memory, as for one token
+    PackT as; // a pack per token in shared memory
+    {
         const uint32_t stride = (uint32_t)(nb * kPackSB);
         for (int t = 0; t < a.c.TB; t++) {
             stage_pack_token(pack + (uint32_t)t * stride, a.c, t, nb, threadIdx.x, 32 * kConsumerWarps);
@@ -265,24 +250,12 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_stream_kernel(const __
 }
 
 // ---- host side ----------------------------------------------------------------------------
-static int env_int(const char * name, int dflt) {
-    const char * e = getenv(name);
-    return e && *e ? atoi(e) : dflt;
-}
-
 template <int TT, int RW>
 static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_secondary) {
-    static bool configured = false; // per instantiation; setting the attribute twice is harmless
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<TT, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kSmemBudget);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        configured = true;
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_stream_kernel<TT, RW>), kSmemBudget);
+    if (e != cudaSuccess) {
+        return e;
     }
-    static const int kb_env = env_int("B200Q_KB", 0), st_env = env_int("B200Q_STAGES", 0);
-    static const int grid_env = env_int("B200Q_GRID", 0);
     const CallDev & c = a.c;
     constexpr int kRows = kConsumerWarps * RW;
     const int nb = c.K >> 8;
@@ -293,31 +266,25 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     // Superblocks per tile along K, per segment.  Copies are efficient when large (the copy
     // engine spends about as long on a copy's fixed cost as on 750 bytes), so take whole rows
     // - one copy per tile - when two tiles of whole rows fit, else per row the largest run of
-    // superblocks that leaves room for two tiles, in multiples of what one pass of a warp covers.
+    // superblocks that leaves room for two tiles, in multiples of eight.
     const size_t pack_probe = (size_t)TT * nb * kPackSB;
     const size_t room = (kSmemBudget - 128 - pack_probe) / 2; // bytes per tile with two stages
-    static const int contig_env = env_int("B200Q_CONTIG", 1);
     a.tile_bytes = 0;
     for (int i = 0; i < c.n_segs; i++) {
         const int type = c.seg[i].type, sbb = sb_bytes((uint32_t)type);
         SegTile & st = a.seg_tile[i];
         int kb;
-        if (kb_env > 0) {
-            kb = kb_env;
-        } else if ((size_t)kRows * nb * sbb + 48 <= room) {
+        if ((size_t)kRows * nb * sbb + 48 <= room) {
             kb = nb;
         } else {
-            // a single-token pass of a warp covers 16 superblocks of Q4_K/Q5_K/Q6_K (two units each)
             const int fit = (int)((room / kRows - 48) / sbb);
-            const bool half_units = type == kQ4_K || type == kQ5_K || type == kQ6_K;
-            const int gran = TT == 1 && half_units && fit >= 16 ? 16 : 8;
-            kb = fit / gran * gran;
+            kb = fit / 8 * 8;
             kb = kb < 8 ? 8 : kb;
-            const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of gran
-            kb = (((nb + n_chunks - 1) / n_chunks + gran - 1) / gran) * gran;
+            const int n_chunks = (nb + kb - 1) / kb; // equal chunks, rounded up to a multiple of eight
+            kb = (((nb + n_chunks - 1) / n_chunks + 7) / 8) * 8;
         }
         st.kb_max = (int16_t)(kb < nb ? kb : nb);
-        st.contig = (contig_env && st.kb_max == nb) ? 1 : 0;
+        st.contig = st.kb_max == nb ? 1 : 0;
         st.slot_bytes = ((st.kb_max * sbb + 32 + 15) / 16) * 16;
         const int tile = st.contig ? ((kRows * nb * sbb + 32 + 15) / 16) * 16 : kRows * st.slot_bytes;
         a.tile_bytes = a.tile_bytes > tile ? a.tile_bytes : tile;
@@ -328,15 +295,9 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
         return cudaErrorInvalidConfiguration;
     }
     int stages = (int)((kSmemBudget - fixed) / (size_t)a.tile_bytes);
-    stages = stages > 8 ? 8 : stages;
-    if (st_env > 0 && st_env < stages) {
-        stages = st_env;
-    }
-    a.stages = stages;
-    static const int dry_env = env_int("B200Q_DRY", 0);
-    a.dry = dry_env;
-    const size_t smem = 128 + (size_t)stages * a.tile_bytes + pack_bytes;
-    int grid = grid_env > 0 ? grid_env : 2 * kSMs;
+    a.stages = stages > 8 ? 8 : stages;
+    const size_t smem = 128 + (size_t)a.stages * a.tile_bytes + pack_bytes;
+    int grid = 2 * kSMs;
     grid = groups < grid ? groups : grid;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -347,8 +308,8 @@ static cudaError_t launch_stream_tt(cudaStream_t s, StreamArgs & a, bool pdl_sec
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const int pdl_env = env_int("B200Q_PDL", 1);
-    cfg.numAttrs = (pdl_secondary || pdl_env) && pdl_env >= 0 ? 1 : 0;
+    cfg.numAttrs = 1; // see the note on launch chaining in b200q.h
+    (void)pdl_secondary;
     if (!cost_split(c, (uint32_t)grid, a.cost)) {
         return cudaErrorInvalidConfiguration;
     }
@@ -366,38 +327,13 @@ bool stream_supported(const CallDev & c) {
     const size_t rows = c.TB == 2 ? 2 * kConsumerWarps : kConsumerWarps; // the two-token kernel takes two rows per warp
     const size_t min_tile = rows * (size_t)(((8 * max_sbb + 32 + 15) / 16) * 16);
     CostSplit cs; // ... and the byte-balanced row split works in 32-bit arithmetic
-    return c.TB >= 1 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 &&
+    return c.TB >= 2 && c.TB <= 4 && c.K <= 24576 && (size_t)tt * nb * kPackSB <= 56 * 1024 &&
            128 + (size_t)tt * nb * kPackSB + 2 * min_tile <= (size_t)kSmemBudget && cost_split(c, 2 * kSMs, cs);
 }
 
-bool stream_quantizes(const CallDev & c, const float * act_up) {
-    // every CTA repeats the quantizer: worth it for short plain activations only (the fused
-    // silu(x)*up form evaluates a double-precision exp per value)
-    static const int lim = env_int("B200Q_FUSE_XQ_MAX_K", 8192);
-    return c.TB == 1 && !act_up && c.K <= lim && stream_supported(c);
-}
-
-cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary, const float * xq_x) {
+cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     StreamArgs a;
     a.c = c;
-    a.xq_x = xq_x;
-    static const int rw_env = env_int("B200Q_RW", 0);
-    if (c.TB == 1) {
-        // two rows per warp share every activation load; one row per warp gives twice the
-        // tiles, which matters when a call is too small to give every CTA a 16-row tile
-        // ... and when rows are too long for two 16-row tiles of at least 3 KB per row copy
-        // (small bulk copies waste the copy engine), 8-row tiles with longer segments win
-        int max_sbb = 0;
-        for (int i = 0; i < c.n_segs; i++) {
-            max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
-        }
-        const int nb = c.K >> 8;
-        const size_t room = (kSmemBudget - 128 - (size_t)nb * kPackSB) / 2;
-        const bool whole_rows = (size_t)16 * nb * max_sbb + 48 <= room;
-        const bool long_copies = room / 16 >= 3072 + 48;
-        const bool rw2 = rw_env ? rw_env == 2 : (c.total_rows >= 16 * 2 * kSMs && (whole_rows || long_copies));
-        return rw2 ? launch_stream_tt<1, 2>(s, a, pdl_secondary) : launch_stream_tt<1, 1>(s, a, pdl_secondary);
-    }
     if (c.TB == 2) {
         return launch_stream_tt<2, 2>(s, a, pdl_secondary);
     }

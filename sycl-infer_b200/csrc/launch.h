@@ -8,11 +8,19 @@ cudaError_t launch_xq(cudaStream_t s, const float * x, const float * up, int x_s
                       float * xmeta, int32_t * xsumq, int TB, int K, bool pdl_primary);
 cudaError_t launch_gemv_rows(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 bool stream_supported(const CallDev & call);
-// xq_x != nullptr (single token, see stream_quantizes): the kernel quantizes that fp32 activation itself
-cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary, const float * xq_x = nullptr);
-bool stream_quantizes(const CallDev & call, const float * act_up);
+cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 cudaError_t read_device_status(int * status, bool clear);
-cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & call, bool pdl_secondary);
+// single-token kernel with the activation pinned in registers (gemv_pinned.cu)
+bool pinned_supported(const CallDev & call);
+bool pinned_pairs_supported(const CallDev & call); // gate|up with the next call's activation
+bool pinned_quantizes(const CallDev & call, const float * x, const float * act_up);
+cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next);
+cudaError_t read_pin_status(int * status, bool clear);
+// cudaFuncAttributeMaxDynamicSharedMemorySize is per device: set once per (kernel, device)
+cudaError_t ensure_dynamic_smem(const void * func, int bytes);
+// dump != nullptr: parity instrument, the raw int32 accumulators of token dump_t instead of outputs
+cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & call, bool pdl_secondary, int32_t * dump = nullptr,
+                            int dump_t = 0);
 cudaError_t read_mma_status(int * status, bool clear);
 cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8, int TB,
                              int t, int32_t * wd);
@@ -49,5 +57,8 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
                const int32_t * xsumq, CallDev & c);
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary);
 bool gemv_takes_stream(const CallDev & c);
+bool gemv_takes_pinned(const CallDev & c);
+int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8,
+                    float * xmeta, int32_t * xsumq, const b200q_call_opts * opts);
 
 } // namespace b200q

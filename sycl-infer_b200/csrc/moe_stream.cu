@@ -332,10 +332,14 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_stream_kernel(const __grid
 
 // ---- host side ----------------------------------------------------------------------------
 bool moe_stream_supported(int type_a, int type_b, int K, int n_rows, int fuse_silu) {
+#ifdef B200Q_TUNING
     static const bool off = [] {
         const char * e = getenv("B200Q_MOE_KERNEL");
         return e && strcmp(e, "rows") == 0;
     }();
+#else
+    const bool off = false;
+#endif
     const int nb = K >> 8;
     const int ra = nb * sb_bytes((uint32_t)type_a), rb = nb * sb_bytes((uint32_t)type_b);
     if (off || (ra & 15) || (fuse_silu && (rb & 15)) || n_rows < 1) {
@@ -409,14 +413,13 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
     }
     a.stages = stages > 8 ? 8 : stages;
     const size_t smem = kMoeHdr + (size_t)a.stages * a.tile_bytes + packs;
-    static bool configured[2] = {false, false};
-    if (!configured[fuse_silu ? 1 : 0]) {
-        cudaError_t e = fuse_silu ? cudaFuncSetAttribute(moe_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoeSmem)
-                                  : cudaFuncSetAttribute(moe_stream_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoeSmem);
+    {
+        const void * fn = fuse_silu ? reinterpret_cast<const void *>(moe_stream_kernel<1>)
+                                    : reinterpret_cast<const void *>(moe_stream_kernel<0>);
+        cudaError_t e = ensure_dynamic_smem(fn, kMoeSmem);
         if (e != cudaSuccess) {
             return e;
         }
-        configured[fuse_silu ? 1 : 0] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * kSMs));

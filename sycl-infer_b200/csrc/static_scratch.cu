@@ -13,7 +13,7 @@
 namespace b200q {
 
 // One token of at most B200Q_STATIC_MAX_K values: codes, (scale, 0) pairs, two sums per
-// 32-value group.  56 KB of every GPU that loads the library, held until the process exits.
+// 32-value group.  48 KB of every GPU that loads the library, held until the process exits.
 constexpr size_t kStaticX8 = B200Q_STATIC_MAX_K;
 constexpr size_t kStaticMeta = (B200Q_STATIC_MAX_K / 32) * 2 * sizeof(float);
 constexpr size_t kStaticSum = (B200Q_STATIC_MAX_K / 32) * 2 * sizeof(int32_t);
@@ -66,27 +66,8 @@ extern "C" int b200q_quant_gemv_static(void * stream, const b200q_seg * segs, in
     int8_t * x8 = reinterpret_cast<int8_t *>(base);
     float * xmeta = reinterpret_cast<float *>(base + kStaticX8);
     int32_t * xsumq = reinterpret_cast<int32_t *>(base + kStaticX8 + kStaticMeta);
-    CallDev c;
-    rc = build_call(segs, n_segs, 1, x8, xmeta, xsumq, c);
-    if (rc != B200Q_OK) {
-        return rc;
-    }
-    const b200q_seg & s0 = segs[0];
-    if (!s0.x || s0.x_stride < s0.K) {
-        set_error("b200q_quant_gemv_static: segs[0].x must be non-null with x_stride >= K");
-        return B200Q_EINVAL;
-    }
-    for (int i = 1; i < n_segs; i++) {
-        if (segs[i].x != s0.x || segs[i].act_up != s0.act_up || segs[i].x_stride != s0.x_stride) {
-            set_error("b200q_quant_gemv_static: segment %d does not share the call's activation", i);
-            return B200Q_EINVAL;
-        }
-    }
-    // The quantizer rewrites every byte of the scratch the GEMV reads (K codes, K/32 scale
-    // pairs and sum pairs), so nothing left over from an earlier call is ever consumed and
-    // nothing needs clearing.
-    B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, 1, s0.K,
-                            true));
-    B200Q_CUDA_OK(launch_gemv((cudaStream_t)stream, c, true));
-    return B200Q_OK;
+    // The quantizer (a kernel of its own, or the GEMV's prologue) rewrites every byte of the
+    // scratch the GEMV reads (K codes, K/32 scale pairs and sum pairs), so nothing left over from
+    // an earlier call is ever consumed and nothing needs clearing.
+    return quant_gemv_call("b200q_quant_gemv_static", (cudaStream_t)stream, segs, n_segs, 1, x8, xmeta, xsumq, nullptr);
 }

@@ -9,21 +9,6 @@ namespace b200q {
 
 constexpr int kConsumerWarps = 8; // consumer warps of one ring: a tile is kConsumerWarps x RW rows
 
-// Build the activation pack of superblocks [sb0, sb0+n) of token 0 (see units.cuh).
-__device__ __forceinline__ void stage_pack(uint32_t pack, const CallDev & c, int sb0, int n, int tid, int nthr) {
-    for (int i = tid; i < 8 * n; i += nthr) {
-        const int g = 8 * sb0 + i; // TB == 1: group index == array index
-        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + (size_t)g * 32);
-        const uint4 x0 = __ldg(gx), x1 = __ldg(gx + 1);
-        const float sx = __ldg(c.xmeta + 2 * (size_t)g);
-        const int2 xs = __ldg(reinterpret_cast<const int2 *>(c.xsumq) + g);
-        const uint32_t p = pack_addr(pack, i);
-        sts128(p, x0.x, x0.y, x0.z, x0.w);
-        sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
-        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
-    }
-}
-
 // Pack of token `tok` of a TB-token activation (group-major views).
 __device__ __forceinline__ void stage_pack_token(uint32_t pack, const CallDev & c, int tok, int n_sb, int tid, int nthr) {
     for (int g = tid; g < 8 * n_sb; g += nthr) {
@@ -36,38 +21,6 @@ __device__ __forceinline__ void stage_pack_token(uint32_t pack, const CallDev & 
         sts128(p, x0.x, x0.y, x0.z, x0.w);
         sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
         sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
-    }
-}
-
-// The same pack straight from the fp32 activation: every CTA quantizes the whole vector
-// itself (one thread per 32-value group, the standalone quantizer's arithmetic), which removes
-// a kernel and a global round trip from the critical path between two GEMV calls.  CTA 0 also
-// writes the caller's scratch views, so they hold the quantized activation as after b200q_xq.
-__device__ __forceinline__ void stage_pack_quant(uint32_t pack, const CallDev & c, const float * x, int n_groups,
-                                                 int tid, int nthr, bool write_views) {
-    for (int g = tid; g < n_groups; g += nthr) {
-        float v[32];
-        const float4 * src = reinterpret_cast<const float4 *>(x + (size_t)g * 32);
-#pragma unroll
-        for (int i = 0; i < 8; i++) { // a thread's eight loads share one 128-byte line; through L2 when peers store x
-            const float4 f = c.n_peers > 0 ? __ldcg(src + i) : src[i];
-            v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
-        }
-        uint32_t q[8];
-        float sx;
-        int s0, s1;
-        xq_group_thread(v, q, sx, s0, s1);
-        const uint32_t p = pack_addr(pack, g);
-        sts128(p, q[0], q[1], q[2], q[3]);
-        sts128(p + 16, q[4], q[5], q[6], q[7]);
-        sts128(p + 32, __float_as_uint(sx), (uint32_t)s0, (uint32_t)s1, __float_as_uint(sx * (float)(s0 + s1)));
-        if (write_views) {
-            uint4 * d8 = reinterpret_cast<uint4 *>(const_cast<int8_t *>(c.x8) + (size_t)g * 32);
-            d8[0] = make_uint4(q[0], q[1], q[2], q[3]);
-            d8[1] = make_uint4(q[4], q[5], q[6], q[7]);
-            reinterpret_cast<float2 *>(const_cast<float *>(c.xmeta))[g] = make_float2(sx, 0.0f);
-            reinterpret_cast<int2 *>(const_cast<int32_t *>(c.xsumq))[g] = make_int2(s0, s1);
-        }
     }
 }
 
@@ -149,13 +102,6 @@ __device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_strid
         }
     }
 }
-template <int TYPE, int RW, int TT>
-__device__ __forceinline__ void consume_tile(uint32_t slot0, uint32_t slot_stride, const uint32_t (&mis)[RW], int kb,
-                                             int sb0, const PackA & as, float (&acc)[RW][TT]) {
-    static_assert(TT == 1, "the activation pack holds one token");
-    consume_tile1<TYPE, RW>(slot0, slot_stride, mis, kb, sb0, as, acc);
-}
-
 // The rows of a call are split among the G parts (CTAs, or consumer groups) in proportion to
 // their bytes: part p owns the flattened cost range [total*p/G, total*(p+1)/G), cost = rows x
 // bytes per superblock.  All in 32-bit arithmetic (64-bit division is a long software routine

@@ -53,6 +53,15 @@ struct ActG4 {
     float sx[4], c[4];
 };
 
+// The same four groups with everything any weight type needs (scales, min-term factors and
+// both 16-value sums): the activation of one 128-value unit as a thread keeps it in
+// registers for a whole launch (gemv_pinned.cu)
+struct ActPin {
+    uint32_t x[4][8];
+    float sx[4], c[4];
+    int xs[4][2];
+};
+
 // two consecutive groups, all 32 codes each
 struct ActG2 {
     uint32_t xa[8], xb[8];
@@ -232,7 +241,7 @@ template <int TYPE> struct HalfK45 {
     static constexpr float kHiScale = TYPE == kQ4_K ? 0.0625f : 0.125f;
 
     // exact sums of the four groups; odd groups come scaled by 1 << kHiShift
-    static __device__ __forceinline__ void dots(uint32_t sb, int h, const ActG4 & a, int (&w)[4]) {
+    template <class A> static __device__ __forceinline__ void dots(uint32_t sb, int h, const A & a, int (&w)[4]) {
         const uint32_t qs = sb + (TYPE == kQ4_K ? 16u : 48u) + 64u * h;
         uint32_t hq[8];
         if (TYPE == kQ5_K) {
@@ -267,7 +276,7 @@ template <int TYPE> struct HalfK45 {
             w[2 * pr + 1] = sb0 + sb1;
         }
     }
-    static __device__ __forceinline__ float term(uint32_t sb, int h, const ActG4 & a) {
+    template <class A> static __device__ __forceinline__ float term(uint32_t sb, int h, const A & a) {
         const uint4 hdr = lds128(sb);
         int w[4];
         dots(sb, h, a, w);
@@ -293,7 +302,7 @@ template <int TYPE> struct HalfK45 {
         const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
         return d * fmaf(vo, kHiScale, ve) - dmin * ms;
     }
-    static __device__ __forceinline__ void exact(uint32_t sb, int h, const ActG4 & a, int G, int32_t * wd) {
+    template <class A> static __device__ __forceinline__ void exact(uint32_t sb, int h, const A & a, int G, int32_t * wd) {
         int w[4];
         dots(sb, h, a, w);
         wd[G] = w[0];
@@ -371,7 +380,7 @@ template <> struct WUnit<kQ6_K> {
 // fp32 is exact), leaving one conversion and one FMA per group and a single multiply by d.
 struct HalfQ6 {
     // raw-code sums per 16-value scale group: w[plane][half]
-    static __device__ __forceinline__ void dots(uint32_t sb, int h, const ActG6H & a, int (&w)[4][2]) {
+    template <class A> static __device__ __forceinline__ void dots(uint32_t sb, int h, const A & a, int (&w)[4][2]) {
         const uint32_t sh = (sb & 2u) * 8, q = (sb & ~3u) + 64u * h, qhp = (sb & ~3u) + 128u + 32u * h;
 #pragma unroll
         for (int hs = 0; hs < 2; hs++) {
@@ -395,7 +404,7 @@ struct HalfQ6 {
             w[0][hs] = s0, w[1][hs] = s1, w[2][hs] = s2, w[3][hs] = s3;
         }
     }
-    static __device__ __forceinline__ float term(uint32_t sb, int h, const ActG6H & a) {
+    template <class A> static __device__ __forceinline__ float term(uint32_t sb, int h, const A & a) {
         int w[4][2];
         dots(sb, h, a, w);
         // the half's eight int8 scales: scales[8h + 2*plane + half]
@@ -411,7 +420,7 @@ struct HalfQ6 {
         }
         return h2f((uint16_t)lds16(sb + 208)) * r;
     }
-    static __device__ __forceinline__ void exact(uint32_t sb, int h, const ActG6H & a, int G, int32_t * wd) {
+    template <class A> static __device__ __forceinline__ void exact(uint32_t sb, int h, const A & a, int G, int32_t * wd) {
         int w[4][2];
         dots(sb, h, a, w);
 #pragma unroll

@@ -62,11 +62,7 @@ cudaError_t launch_xq(cudaStream_t s, const float * x, const float * up, int x_s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const bool pdl = [] {
-        const char * e = getenv("B200Q_PDL");
-        return !(e && atoi(e) < 0);
-    }();
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, xq_kernel, x, up, x_stride, up_stride, x8, xmeta, xsumq, TB, G);
 }
 

@@ -47,6 +47,9 @@ class DenseLayer:
         self.act_h = alloc_act(TB, hidden, dev)
         self.act_q = alloc_act(TB, self.q_dim, dev)
         self.act_f = alloc_act(TB, n_ff, dev)
+        # one token on one GPU: the gate|up GEMV leaves the quantized silu(gate)*up for the down call
+        self.fused_h = TB == 1 and world == 1
+        self.h_counters = torch.zeros(n_ff // 32, dtype=torch.int32, device=dev) if self.fused_h else None
         self._staging = {}
 
     def weight_bytes(self):
@@ -79,7 +82,13 @@ class DenseLayer:
         return [([s for s, _ in call], [g for _, g in call]) for call in plan]
 
     def forward(self, x, out, calls=None):
-        for segs, gathers in (calls or self.calls(x, out)):
+        for i, (segs, gathers) in enumerate(calls or self.calls(x, out)):
+            if self.fused_h and i >= 2:
+                if i == 2:
+                    self.be.quant_gemv_ex(segs, 1, next_act=self.act_f, counters=self.h_counters)
+                else:
+                    self.be.quant_gemv_ex(segs, 1, prequantized=True)
+                continue
             if self.arena:
                 self.be.quant_gemv_scatter(segs, self.TB, self._peers)
                 self.be.peer_barrier(self._flags, self.world, self.rank, 0)  # device-numbered: graph-safe
@@ -95,8 +104,10 @@ class DenseLayer:
         return out
 
     def launches_per_step(self):
-        # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue (one launch
-        # each), down keeps the separate silu(gate)*up quantizer; otherwise a quantizer + GEMV per call
+        # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue and gate|up
+        # also emits down's quantized activation: one launch per call; otherwise a quantizer + GEMV per call
         if self.arena is not None:  # GEMV with peer stores (+ quantizer where it is a kernel of its own) + flag barrier
             return 9 if self.TB == 1 else 12
+        if self.fused_h:
+            return 4
         return 5 if self.TB == 1 else 8

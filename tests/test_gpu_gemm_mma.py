@@ -1,7 +1,8 @@
-"""Tensor-core GEMM path (more than 8 tokens: tcgen05 int8 MMA per 32-value group) against the
-oracle's tiled-GEMM order.  fp32 outputs within 1e-5 of the sum of |terms|; the int32 group
-dots come out of the tensor core exact, which the fp32 agreement at this tolerance on
-cancelling sums already demands."""
+"""Tensor-core GEMM path (five tokens and more: one tcgen05 int8 MMA per 32-value group) against
+the oracle.  The int32 group dots are compared bit for bit: b200q_i8_block_dots with five or
+more tokens runs the tensor-core kernel itself and stores the accumulators its epilogue read
+from tensor memory.  fp32 outputs are within 1e-5 of the sum of |terms| of the oracle's
+tiled-GEMM order."""
 import numpy as np
 import pytest
 
@@ -56,3 +57,106 @@ def test_prefill_config2_slice(be, orc, pkg):
     ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
     got = _gemm(be, t, w, K, N, a, TB)
     assert float(np.max(np.abs(got - ref) / ab)) <= TOL
+
+
+def _dots(be, t, w, K, N, act, TB, tok):
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()  # noqa: E731
+    D = K // 16 if t == 14 else K // 32
+    wd = torch.full((N, D), -77, dtype=torch.int32, device="cuda")
+    be.i8_block_dots(dev(w), t, K, N, dev(act.x8), TB, tok, wd)
+    be.synchronize()
+    assert be.device_status() == 0
+    return wd.cpu().numpy()
+
+
+@pytest.mark.parametrize("t", (12, 13, 14, 8, 23))
+@pytest.mark.parametrize("TB,N,K", [(5, 64, 256), (8, 130, 512), (16, 128, 1280), (32, 200, 512), (33, 129, 768),
+                                    (64, 37, 512), (100, 260, 256)])
+def test_mma_int32_dots_bit_exact(be, orc, pkg, t, TB, N, K):
+    """Token tiles of 8 / 16 / 32 / 64 columns, ragged last row tile and last token tile: the
+    accumulators the tensor core produced are the reference's int32 sums
+    (src/backend/cpu/kernels/i8.cpp:57,117,149 of the reference), bit for bit, for the first, a
+    middle and the last token."""
+    w = pkg.synth.make_weight(t, N, K, 1500 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 1501), None, TB)
+    for tok in sorted({0, TB // 2, TB - 1}):
+        want = orc.block_dots(t, w, K, N, a, tok)
+        got = _dots(be, t, w, K, N, a, TB, tok)
+        assert np.array_equal(got, want), f"token {tok}"
+
+
+def _saturated(pkg, t, N, K):
+    """Weights whose every quant code is the largest in magnitude the format holds (scales stay
+    random): 15 / 31 / 63 for Q4_K / Q5_K / Q6_K, +127 and -128 on alternating rows for Q8_0,
+    codebook entry 0 (-127) for IQ4_XS."""
+    sbb = pkg.synth.SUPERBLOCK_BYTES[t]
+    w = pkg.synth.make_weight(t, N, K, 1600 + t).reshape(N, K // 256, sbb).copy()
+    if t == 12:
+        w[:, :, 16:] = 0xFF
+    elif t == 13:
+        w[:, :, 16:] = 0xFF
+    elif t == 14:
+        w[:, :, :192] = 0xFF
+    elif t == 23:
+        w[:, :, 8:] = 0x00
+    else:
+        b = w.reshape(N, K // 32, 34)
+        b[0::2, :, 2:] = 0x7F
+        b[1::2, :, 2:] = 0x80
+    return w.reshape(-1)
+
+
+@pytest.mark.parametrize("t", (12, 13, 14, 8, 23))
+@pytest.mark.parametrize("TB", (8, 48))
+def test_mma_saturated_operands(be, orc, pkg, t, TB):
+    """Every activation code +-127 against the largest weight codes: the int32 sums reach their
+    extreme (32*127*128 = 520192 for Q8_0), far inside the 2^22 range the epilogue's
+    integer-to-float conversion relies on; both the raw sums and the fp32 outputs must hold."""
+    N, K = 130, 512
+    w = _saturated(pkg, t, N, K)
+    x = np.ones((TB, K), np.float32)
+    x[1::2] = -1.0
+    x[:, 5::7] *= -1.0  # mixed signs inside a group as well
+    a = orc.xq(x, None, TB)
+    assert np.all(np.abs(a.x8) == 127)
+    for tok in (0, TB - 1):
+        want = orc.block_dots(t, w, K, N, a, tok)
+        assert np.array_equal(_dots(be, t, w, K, N, a, TB, tok), want)
+    all_pos = orc.xq(np.ones((TB, K), np.float32), None, TB)
+    assert np.max(np.abs(orc.block_dots(t, w, K, N, all_pos, 0))) >= {12: 60960, 13: 125984, 14: 128016, 8: 516128,
+                                                                       23: 516128}[t]
+    assert np.array_equal(_dots(be, t, w, K, N, all_pos, TB, 0), orc.block_dots(t, w, K, N, all_pos, 0))
+    for act in (a, all_pos):
+        ref, ab = orc.gemm(t, w, K, N, act), orc.gemm_abs(t, w, K, N, act)
+        got = _gemm(be, t, w, K, N, act, TB)
+        assert float(np.max(np.abs(got - ref) / ab)) <= TOL
+
+
+def test_prefill_config2_m2048_sampled_rows(be, orc, pkg):
+    """Prefill GEMM of configuration 2 at M = 2048 tokens, K = 5120: the GPU computes a 256-row
+    slice of the gate weight for all 2048 tokens (two full row tiles, 32 token tiles of 64); the
+    oracle checks 64 sampled rows x all tokens."""
+    t, N, K, TB = 12, 256, 5120, 2048
+    w = pkg.synth.make_weight(t, N, K, 1700)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 1701), None, TB)
+    got = _gemm(be, t, w, K, N, a, TB)
+    rb = pkg.synth.row_bytes(t, K)
+    rows = np.random.default_rng(5).choice(N, 64, replace=False)
+    sub = np.concatenate([w[r * rb:(r + 1) * rb] for r in rows])
+    ref, ab = orc.gemm(t, sub, K, 64, a), orc.gemm_abs(t, sub, K, 64, a)
+    assert float(np.max(np.abs(got[:, rows] - ref) / ab)) <= TOL
+
+
+@pytest.mark.parametrize("t,N,K", [(23, 17408, 5120), (13, 17408, 5120), (23, 5120, 17408), (13, 5120, 17408)])
+def test_batch32_layer_shapes_iq4xs_q5k(be, orc, pkg, t, N, K):
+    """Configuration 4's batch 32 on the real layer shapes in IQ4_XS and Q5_K (one gate-shaped and
+    one down-shaped matrix each): the GPU computes the full matrix, the oracle 96 sampled rows."""
+    TB = 32
+    w = pkg.synth.make_weight(t, N, K, 1800 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 1801), None, TB)
+    got = _gemm(be, t, w, K, N, a, TB)
+    rb = pkg.synth.row_bytes(t, K)
+    rows = np.sort(np.random.default_rng(6).choice(N, 96, replace=False))
+    sub = np.concatenate([w[r * rb:(r + 1) * rb] for r in rows])
+    ref, ab = orc.gemm(t, sub, K, 96, a), orc.gemm_abs(t, sub, K, 96, a)
+    assert float(np.max(np.abs(got[:, rows] - ref) / ab)) <= TOL

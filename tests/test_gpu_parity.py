@@ -283,3 +283,142 @@ def test_quant_gemv_single_token_quantizes_in_kernel(be, orc, pkg, t, K, N):
     ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=0.5)
     ab = orc.gemm_abs(t, w, K, N, a, alpha=0.5) + np.abs(res)
     assert rel_err(o.cpu().numpy().reshape(1, N), ref, ab) <= TOL
+
+
+def test_quant_gemv_misaligned_activation_pointer(be, orc, pkg):
+    """An fp32 activation that starts 4 bytes off a 16-byte boundary is legal (the reference's
+    gemv_seg.x is any float pointer): the call must take the separate quantizer (scalar loads)
+    instead of the in-kernel one (128-bit loads) and give the same results."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    t, K, N = 12, 2048, 70
+    x = pkg.synth.make_activation(1, K, 930)
+    w = pkg.synth.make_weight(t, N, K, 931)
+    a = orc.xq(x)
+    buf = torch.zeros(K + 4, dtype=torch.float32, device="cuda")
+    dx = buf[1:K + 1]
+    dx.copy_(torch.from_numpy(x[0]))
+    assert dx.data_ptr() % 16 == 4
+    x8, xm, xs = alloc_act(1, K)
+    o = torch.zeros(N, dtype=torch.float32, device="cuda")
+    be.quant_gemv([gemv_seg(w=dev(w), type=t, K=K, n_rows=N, x=dx, x_stride=K, out=o, out_stride=N, x8=x8, xmeta=xm,
+                            xsumq=xs)], 1)
+    be.synchronize()
+    assert be.device_status() == 0
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
+    assert rel_err(o.cpu().numpy().reshape(1, N), ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("K,N", [(256, 700), (2560, 333), (4096, 4096), (8704, 50), (32768, 9)])
+def test_gemv_parity_row_slot_shapes(be, orc, pkg, t, K, N):
+    """Single-token shapes that exercise the pinned kernel's geometry: many row slots per step
+    (short K), a partly filled last step, unit counts that do not divide the lanes, long rows."""
+    w = pkg.synth.make_weight(t, N, K, 940 + t)
+    a = orc.xq(pkg.synth.make_activation(1, K, 941))
+    res = pkg.synth.make_activation(1, N, 942)
+    ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=0.5)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=0.5) + np.abs(res)
+    got = gpu_gemm(be, t, w, K, N, a, 1, residual=res, alpha=0.5)
+    assert be.device_status() == 0
+    assert rel_err(got, ref, ab) <= TOL
+
+
+@pytest.mark.parametrize("K,n_ff", [(1024, 1280), (5120, 17408)])
+def test_gate_up_emits_next_activation(be, orc, pkg, K, n_ff):
+    """gate|up with the next-activation option: besides gate and up, the launch leaves
+    quantize(silu(gate)*up) for the down call.  Codes, scales and sums must be exactly what the
+    standalone quantizer makes of the SAME gate and up values (same device arithmetic), and agree
+    with the host quantizer up to rounding ties of expf; the counters must be back at zero, so a
+    second call works; the down call on that activation (no quantizer) matches the oracle."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    t = 12
+    x = pkg.synth.make_activation(1, K, 950)
+    wg, wu = pkg.synth.make_weight(t, n_ff, K, 951), pkg.synth.make_weight(t, n_ff, K, 952)
+    a = orc.xq(x)
+    alpha = 1.0 / (3.0 * K ** 0.5)
+    gu = torch.zeros(1, 2 * n_ff, dtype=torch.float32, device="cuda")
+    x8, xm, xs = alloc_act(1, K)
+    h8, hm, hs = alloc_act(1, n_ff)
+    cnt = torch.zeros(n_ff // 32, dtype=torch.int32, device="cuda")
+    dx, dwg, dwu = dev(x), dev(wg), dev(wu)
+    segs = [gemv_seg(w=dwg, type=t, K=K, n_rows=n_ff, x=dx, x_stride=K, out=gu.view(-1), out_stride=2 * n_ff,
+                     alpha=alpha, x8=x8, xmeta=xm, xsumq=xs),
+            gemv_seg(w=dwu, type=t, K=K, n_rows=n_ff, x=dx, x_stride=K, out=gu.view(-1)[n_ff:], out_stride=2 * n_ff,
+                     alpha=alpha, x8=x8, xmeta=xm, xsumq=xs)]
+    for _ in range(2):
+        h8.zero_()
+        be.quant_gemv_ex(segs, 1, next_act=(h8, hm, hs), counters=cnt)
+        be.synchronize()
+        assert be.device_status() == 0
+        assert int(cnt.abs().sum()) == 0
+        g = gu.cpu().numpy()
+        for wq, lo in ((wg, 0), (wu, n_ff)):
+            rows = slice(0, n_ff) if n_ff <= 2048 else slice(n_ff - 300, n_ff)
+            rb = pkg.synth.row_bytes(t, K)
+            sub = wq[rows.start * rb:rows.stop * rb]
+            ref = orc.gemm(t, sub, K, rows.stop - rows.start, a, alpha=alpha)
+            ab = orc.gemm_abs(t, sub, K, rows.stop - rows.start, a, alpha=alpha)
+            assert rel_err(g[:, lo + rows.start:lo + rows.stop], ref, ab) <= TOL
+        q8, qm, qs = gpu_xq(be, g[:, :n_ff], g[:, n_ff:], 1)  # the standalone quantizer on the same values
+        assert np.array_equal(h8.cpu().numpy(), q8.cpu().numpy())
+        assert np.array_equal(hm.cpu().numpy().view(np.uint32), qm.cpu().numpy().view(np.uint32))
+        assert np.array_equal(hs.cpu().numpy(), qs.cpu().numpy())
+        host = orc.xq(g[:, :n_ff], g[:, n_ff:], 1)
+        d = np.abs(h8.cpu().numpy().astype(np.int32) - host.x8.astype(np.int32))
+        assert d.max() <= 1 and np.count_nonzero(d) <= 1e-4 * d.size + 1
+    # down on the emitted activation, quantizer skipped
+    N = 64
+    wd_ = pkg.synth.make_weight(14, N, n_ff, 953)
+    o = torch.zeros(N, dtype=torch.float32, device="cuda")
+    be.quant_gemv_ex([gemv_seg(w=dev(wd_), type=14, K=n_ff, n_rows=N, out=o, out_stride=N, x8=h8, xmeta=hm, xsumq=hs)],
+                     1, prequantized=True)
+    be.synchronize()
+    act = orc.xq(g[:, :n_ff], g[:, n_ff:], 1)
+    act.x8, act.xmeta, act.xsumq = h8.cpu().numpy(), hm.cpu().numpy(), hs.cpu().numpy()
+    ref, ab = orc.gemm(14, wd_, n_ff, N, act), orc.gemm_abs(14, wd_, n_ff, N, act)
+    assert rel_err(o.cpu().numpy().reshape(1, N), ref, ab) <= TOL
+
+
+def test_moe_rejects_misaligned_activation(be):
+    """The expert kernels read the quantized activation with 128-bit loads: a misaligned view is
+    refused with EINVAL before any launch."""
+    from sycl_infer_b200.capi import B200QError
+    import ctypes as C
+    z = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = z.data_ptr()
+    i32 = torch.zeros(64, dtype=torch.int32, device="cuda")
+    f32 = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    lib = be.lib
+    rc = lib.moe_gate_up(None, p, p, 12, 12, 144 * 8 * 8, 144 * 8 * 8, i32.data_ptr(), i32.data_ptr(), i32.data_ptr(),
+                         i32.data_ptr(), 1, p + 4, f32.data_ptr(), i32.data_ptr(), 1, f32.data_ptr(), 8, 2048, 8, 1)
+    assert rc == 1 and "16-byte aligned" in lib.last_error()
+    rc = lib.moe_down(None, p, 12, 144 * 2 * 8, i32.data_ptr(), i32.data_ptr(), i32.data_ptr(), i32.data_ptr(), 1,
+                      p + 8, f32.data_ptr(), i32.data_ptr(), 1, f32.data_ptr(), 2048, 2048, 512)
+    assert rc == 1 and "16-byte aligned" in lib.last_error()
+    del B200QError, C
+
+
+def test_second_device_in_one_process(pkg, orc):
+    """One process, two GPUs (the reference's layer split runs this way): kernels that opt in to
+    large dynamic shared memory must be configured on the second device too."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    for d in (0, 1):
+        with torch.cuda.device(d):
+            be_d = pkg.make_cuda_backend(d)
+            for TB, t, K, N in ((1, 12, 5120, 300), (3, 14, 2048, 70), (16, 12, 1024, 200)):
+                w = pkg.synth.make_weight(t, N, K, 960)
+                x = pkg.synth.make_activation(TB, K, 961)
+                a = orc.xq(x, None, TB)
+                x8, xm, xs = alloc_act(TB, K, device=f"cuda:{d}")
+                o = torch.zeros(TB * N, dtype=torch.float32, device=f"cuda:{d}")
+                seg = gemv_seg(w=torch.from_numpy(w).to(f"cuda:{d}"), type=t, K=K, n_rows=N,
+                               x=torch.from_numpy(x).to(f"cuda:{d}"), x_stride=K, out=o, out_stride=N, x8=x8,
+                               xmeta=xm, xsumq=xs)
+                be_d.quant_gemv([seg], TB)
+                be_d.synchronize()
+                ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
+                assert rel_err(o.cpu().numpy().reshape(TB, N), ref, ab) <= TOL
+            assert be_d.device_status() == 0
