@@ -1,18 +1,20 @@
-"""Benchmark of the quantized-GEMV hot path: one dense layer's GEMV calls, batch 1.
+"""Benchmark of the quantized-GEMV hot path.
 
-Workload = benchmark configuration 1: hidden 5120, 40 query / 8 KV heads of dim 128, FFN
-17408, Q/K/O/gate/up in Q4_K, V/down in Q6_K (the "Q4_K_M" mix), seeded synthetic blocks.
-One step = one layer pass = four calls (q|k|v, o, gate|up, down), each an activation
-quantize + one GEMV launch.  Steps rotate over `--layers` distinct weight sets of 210 MB
-each, so every step streams weights that are not in the 126 MB L2.
+Headline workload = benchmark configuration 1, batch 1: hidden 5120, 40 query / 8 KV heads of
+dim 128, FFN 17408, Q/K/O/gate/up in Q4_K, V/down in Q6_K (the "Q4_K_M" mix), seeded synthetic
+blocks.  One step = one layer pass = four calls (q|k|v, o, gate|up, down), each ONE launch that
+quantizes its activation and streams its weights.  Steps rotate over `--layers` distinct weight
+sets of 210 MB each, so every step streams weights that are not in the 126 MB L2.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-cells]
 
-Prints ONE JSON line (rank 0).  `value` is weight-stream GB/s with all inputs resident in
-HBM; `e2e` is the same through the host-buffer call sequence (pinned H2D of the step's
-activations, D2H of its output, every step); `roofline` is the GEMV kernel alone against
-the measured HBM copy bandwidth; `cpu_baseline` is the reference's own CPU path on this
-machine's cores.  `--impl reference` times that CPU path as the headline instead.
+Prints ONE JSON line (rank 0).  `value` is weight-stream GB/s with all inputs resident in HBM;
+`e2e` is the same through the host-buffer call sequence (pinned H2D of the step's activations,
+D2H of its output, every step); `roofline` is the GEMV kernel alone against the measured HBM copy
+bandwidth; `cpu_baseline` is the reference's own CPU path on this machine's cores; `cells` holds
+the other configurations (config 0, config 1 batch 16, config 2, config 3 on one GPU; batch 1 and
+32 x three type mixes x {peer-store, NCCL all-gather, layer split} on several).  `--impl
+reference` times the CPU path as the headline instead.
 """
 import argparse
 import json
@@ -28,12 +30,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as graft  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMV launches of one layer step, from an
-# ncu capture of this workload on one B200 (215.6 MB per layer against 210.1 MB of weights): per launch
-NCU_DRAM_BYTES_PER_LAUNCH = 53.9e6
 METRIC = "quant_gemv_effective_hbm_gbs"
 WORKLOAD = "dense layer GEMV set, Q4_K_M mix (hidden 5120, 40q/8kv x128, ffn 17408), batch 1"
 LAYERS_PER_TOKEN = 64
+DTYPE = "int8xu4/u6->int32, fp32 scales"
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMV launch of one layer step: from the ncu capture
+# summarised in profiles/gemv_pinned_layer_q4km_batch1.md (not re-measured by this program)
+TRAFFIC_NOTE = "profiles/gemv_pinned_layer_q4km_batch1.md"
 
 
 def measured_peaks():
@@ -41,6 +44,18 @@ def measured_peaks():
     if os.path.exists(p):
         return json.load(open(p)), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def ncu_traffic_per_launch():
+    """The figure the profile summary records, if it is there: 'traffic_bytes_per_launch: N'."""
+    p = os.path.join(ROOT, TRAFFIC_NOTE)
+    try:
+        for line in open(p):
+            if line.startswith("traffic_bytes_per_launch:"):
+                return float(line.split(":", 1)[1])
+    except OSError:
+        pass
+    return None
 
 
 class ClockSampler(threading.Thread):
@@ -60,7 +75,7 @@ class ClockSampler(threading.Thread):
                 self.rows.append([c.strip() for c in out.strip().split(",")])
             except Exception:
                 pass
-            self.stop_flag.wait(0.1)
+            self.stop_flag.wait(0.05)
 
     def summary(self):
         self.stop_flag.set()
@@ -74,7 +89,7 @@ class ClockSampler(threading.Thread):
 
 
 # ------------------------------------------------------------------ CPU reference arm
-def cpu_layer_pass(ref, po, pkg, weights, x, attn):
+def cpu_layer_pass(ref, pkg, weights, x, attn):
     """One layer pass on the reference's CPU integer path (cpu_xq + cpu_i8_gemv)."""
     sh = {n: (t, r, k) for n, t, r, k in pkg.synth.dense_layer_shapes("Q4_K_M")}
     a = ref.xq(x)
@@ -94,7 +109,7 @@ def cpu_arm(steps, warmup, budget_s=25.0):
         cores = ref.threads()
     else:  # the C restatement stands in where the reference's sources were never compiled
         orc = po.Oracle()
-        kind, cores = "port", os.cpu_count() or 1
+        kind, cores = "port", 1
 
         class _R:
             xq = staticmethod(lambda x, up=None: orc.xq(x, up))
@@ -109,11 +124,11 @@ def cpu_arm(steps, warmup, budget_s=25.0):
     x, attn = pkg.synth.make_activation(1, 5120, 1), pkg.synth.make_activation(1, 5120, 2)
     t_begin = time.perf_counter()
     for _ in range(warmup):
-        cpu_layer_pass(ref, po, pkg, weights, x, attn)
+        cpu_layer_pass(ref, pkg, weights, x, attn)
     times = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        cpu_layer_pass(ref, po, pkg, weights, x, attn)
+        cpu_layer_pass(ref, pkg, weights, x, attn)
         times.append(time.perf_counter() - t0)
         if time.perf_counter() - t_begin > budget_s:
             break
@@ -123,181 +138,365 @@ def cpu_arm(steps, warmup, budget_s=25.0):
             "ms_per_step": ms, "steps": len(times)}
 
 
+# ------------------------------------------------------------------------ GPU helpers
+class Ctx:
+    """What every cell needs: package, backend, ranks, peaks, a side stream for graph capture."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank, self.world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+        self.local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        self.pkg = graft.load_package()
+        self.be = self.pkg.make_cuda_backend(self.local)
+        self.side = torch.cuda.Stream()
+        self.peaks, self.peak_source = measured_peaks()
+        self.args = args
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, vals):
+        if self.world == 1:
+            return [float(v) for v in vals]
+        t = self.torch.tensor(list(vals), device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.cpu()]
+
+    def capture(self, fn):
+        """Record fn() into a CUDA graph (the backend launches on the side stream meanwhile)."""
+        torch = self.torch
+        self.be._stream = self.side
+        try:
+            with torch.cuda.stream(self.side):
+                fn()
+                self.side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.side):
+                    fn()
+        finally:
+            self.be._stream = None
+        torch.cuda.synchronize()
+        return g
+
+    def time_ms(self, run, n, warm=3):
+        """Device time of n calls of run(i): warm-up, barrier, CUDA events, barrier; max over ranks."""
+        torch = self.torch
+        for i in range(warm):
+            run(i)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            run(i)
+        e1.record()
+        self.barrier()
+        return self.max_over_ranks([e0.elapsed_time(e1)])[0]
+
+    def frac(self, gbs):
+        return gbs / self.peaks["hbm_gbs"]
+
+
+def clocked(ctx, fn):
+    """Run fn() with a clock sampler around it; returns (result, clocks summary)."""
+    s = ClockSampler(ctx.local)
+    s.start()
+    r = fn()
+    return r, s.summary()
+
+
+def make_layers(ctx, mix, TB, L, rank, world, arena=None, seed0=100):
+    from sycl_infer_b200.layer import DenseLayer
+    torch, pkg = ctx.torch, ctx.pkg
+    layers = [DenseLayer(ctx.be, mix, seed=seed0 + i, TB=TB, rank=rank, world=world, arena=arena,
+                         group=None) for i in range(L)]
+    for i, ly in enumerate(layers):
+        ly.next_layer = layers[(i + 1) % L]  # the step that follows replays the next weight set
+    hidden, q_dim = layers[0].hidden, layers[0].q_dim
+    # a step's two inputs (hidden state and attention output) share one device buffer per weight
+    # set, so the end-to-end loop moves them with ONE host-to-device copy
+    xin = [torch.zeros(TB * (hidden + q_dim), dtype=torch.float32, device="cuda") for _ in range(L)]
+    xs = [b[:TB * hidden].view(TB, hidden) for b in xin]
+    for i, ly in enumerate(layers):
+        xs[i].copy_(torch.from_numpy(pkg.synth.make_activation(TB, hidden, 10 + i)))
+        ly.attn = xin[i][TB * hidden:].view(TB, q_dim)
+        ly.attn.copy_(torch.from_numpy(pkg.synth.make_activation(TB, q_dim, 3)))
+    return layers, xin, xs
+
+
+def layer_bytes(pkg, mix, TB, ly):
+    """Algorithmic bytes of one layer pass: raw weight blocks once + fp32 activations in and out."""
+    vec = 2 * ly.hidden + ly.q_dim + 2 * ly.n_ff + (ly.q_dim + 2 * ly.kv_dim) + 2 * ly.hidden + 2 * ly.n_ff
+    return pkg.synth.layer_weight_bytes(mix) + 4 * TB * vec
+
+
+# ------------------------------------------------------------------------ cells, one GPU
+def cell_single_matrix(ctx, name, qtype, rows, K, copies=16, iters=64):
+    """One quantize + GEMV call per iteration over rotating copies of one matrix (config 0)."""
+    torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    w0 = pkg.synth.make_weight(qtype, rows, K, 0xB200)
+    ws = [torch.from_numpy(w0).cuda() for _ in range(copies)]
+    x = torch.from_numpy(pkg.synth.make_activation(1, K, 0xB201)).cuda()
+    x8, xm, xs = alloc_act(1, K)
+    out = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    segs = [gemv_seg(w=w, type=qtype, K=K, n_rows=rows, x=x, x_stride=K, out=out, out_stride=rows, x8=x8, xmeta=xm,
+                     xsumq=xs) for w in ws]
+    g = ctx.capture(lambda: [be.quant_gemv([segs[i % copies]], 1) for i in range(iters)])
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: g.replay(), 20))
+    us = 1e3 * ms / (20 * iters)
+    nbytes = w0.size + 8 * K
+    gbs = nbytes / us / 1e3
+    return {"cell": name, "us": us, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": ctx.frac(gbs),
+            "l2": f"{copies} rotating copies ({copies * w0.size / 1e6:.0f} MB)", "launches_per_iter": 1, "clocks": clocks}
+
+
+def cell_layer(ctx, name, mix, TB, L=4, steps=40):
+    """One dense layer per step on ONE GPU (config 1 at another batch or mix)."""
+    layers, xin, xs = make_layers(ctx, mix, TB, L, 0, 1)
+    torch, be = ctx.torch, ctx.be
+    out = torch.zeros(TB, layers[0].hidden, dtype=torch.float32, device="cuda")
+    graphs = [ctx.capture(lambda i=i: layers[i].forward(xs[i], out)) for i in range(L)]
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: graphs[i % L].replay(), steps))
+    us = 1e3 * ms / steps
+    nbytes = layer_bytes(ctx.pkg, mix, TB, layers[0])
+    gbs = nbytes / us / 1e3
+    return {"cell": name, "us": us, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": ctx.frac(gbs),
+            "tok_s_64_layers": TB * 1e6 / (us * LAYERS_PER_TOKEN), "launches_per_iter": layers[0].launches_per_step(),
+            "l2": f"{L} rotating weight sets", "clocks": clocks}
+
+
+def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
+    """Config 2: M tokens x (Q4_K weight of `rows` x K); quantizer + tensor-core GEMM per iteration."""
+    torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    w = torch.from_numpy(pkg.synth.make_weight(12, rows, K, 0xB202)).cuda()
+    x = torch.from_numpy(pkg.synth.make_activation(M, K, 0xB203)).cuda()
+    x8, xm, xs = alloc_act(M, K)
+    out = torch.zeros(M * rows, dtype=torch.float32, device="cuda")
+    seg = gemv_seg(w=w, type=12, K=K, n_rows=rows, x=x, x_stride=K, out=out, out_stride=rows, x8=x8, xmeta=xm, xsumq=xs)
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: be.quant_gemv([seg], M), iters, warm=1))
+    us = 1e3 * ms / iters
+    ops = 2.0 * M * K * rows
+    nbytes = w.numel() + 4 * M * K + 4 * M * rows
+    return {"cell": name, "us": us, "int8_ops": ops, "Tops": ops / us / 1e6, "bytes": nbytes, "GB/s": nbytes / us / 1e3,
+            "frac_of_measured_hbm": ctx.frac(nbytes / us / 1e3),
+            "frac_of_dense_peak": None, "note": "no measured int8 tcgen05 peak on record; bf16 cuBLAS peak x2 would be "
+            f"{2 * ctx.peaks.get('bf16_tflops', 0):.0f} T int8-op/s", "clocks": clocks}
+
+
+def cell_moe(ctx, name, tokens=16, experts=256, topk=8, embd=2048, ff=512, copies=2, iters=20):
+    """Config 3: router -> CSR -> quantize -> grouped gate|up -> quantize -> grouped down -> reduce."""
+    torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
+    from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_call
+    banks = [make_synthetic_moe(experts, topk, embd, ff, (12, 12, 12), seed=i, with_router=True)[1]
+             for i in range(copies)]
+    S = MoeScratch(banks[0], tokens)
+    x = torch.from_numpy(pkg.synth.make_activation(tokens, embd, 5)).cuda()
+    out = torch.zeros(tokens, embd, device="cuda")
+    g = ctx.capture(lambda: [moe_call(be, banks[i % copies], S, x, tokens, out) for i in range(iters)])
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: g.replay(), 10))
+    us = 1e3 * ms / (10 * iters)
+    n_active = int(S.n_active.cpu()[0])
+    per_expert = sum(int(pkg.synth.row_bytes(12, K)) * r for r, K in ((ff, embd), (ff, embd), (embd, ff)))
+    nbytes = n_active * per_expert
+    gbs = nbytes / us / 1e3
+    return {"cell": name, "us": us, "bytes": nbytes, "active_experts": n_active, "GB/s": gbs,
+            "frac_of_measured_hbm": ctx.frac(gbs), "l2": f"{copies} rotating expert banks", "clocks": clocks}
+
+
+# ------------------------------------------------------------------------ cells, several GPUs
+def cell_sharded(ctx, mix, TB, arm, L=2, steps=30):
+    """Row-sharded layer: `peer` = GEMV epilogue stores rows on every GPU (flag barrier folded into
+    the kernels), `nccl` = NCCL all-gather after each call (host launches)."""
+    torch, be, rank, world = ctx.torch, ctx.be, ctx.rank, ctx.world
+    arena = None
+    if arm == "peer":
+        from sycl_infer_b200.sharding import PeerArena
+        arena = PeerArena(L * TB * 65536 + 8192, rank, world)
+    layers, xin, xs = make_layers(ctx, mix, TB, L, rank, world, arena=arena, seed0=300)
+    out = arena.alloc(TB, layers[0].hidden) if arena is not None else torch.zeros(TB, layers[0].hidden, device="cuda")
+    graphs = None
+    if arm == "peer":
+        graphs = [ctx.capture(lambda i=i: layers[i].forward(xs[i], out)) for i in range(L)]
+    run = (lambda i: graphs[i % L].replay()) if graphs else (lambda i: layers[i % L].forward(xs[i % L], out))
+    ms = ctx.time_ms(run, steps)
+    # the same step with the exchange left out (wrong results, timing only): its share is the difference
+    for ly in layers:
+        ly.exchange = False
+    if arm == "peer":
+        graphs = [ctx.capture(lambda i=i: layers[i].forward(xs[i], out)) for i in range(L)]
+        run = lambda i: graphs[i % L].replay()  # noqa: E731
+    ms_noex = ctx.time_ms(run, steps)
+    us, us_noex = 1e3 * ms / steps, 1e3 * ms_noex / steps
+    nbytes = layer_bytes(ctx.pkg, mix, TB, layers[0])
+    gbs = nbytes / us / 1e3
+    return {"cell": f"{mix} batch {TB} row-sharded x{world} ({arm})", "us": us, "bytes": nbytes, "GB/s": gbs,
+            "frac_of_P_x_measured_hbm": gbs / (world * ctx.peaks["hbm_gbs"]),
+            "tok_s_64_layers": TB * 1e6 / (us * LAYERS_PER_TOKEN),
+            "exchange_share": max(0.0, 1.0 - us_noex / us), "launch": "cuda graph" if arm == "peer" else "host launches"}
+
+
+def cell_layer_split(ctx, mix, TB, n_layers=8, steps=10):
+    """The reference's contiguous layer split (--layer-map): n_layers layers over the ranks, the
+    hidden state handed on at each boundary (NCCL send/recv).  One step = one token batch through
+    all n_layers; a rank idles while the others compute (no pipelining across steps here)."""
+    from sycl_infer_b200.layer import DenseLayer
+    from sycl_infer_b200.sharding import even_layer_map, parse_layer_map, run_layer_split
+    torch, be, rank, world = ctx.torch, ctx.be, ctx.rank, ctx.world
+    ranges = parse_layer_map(even_layer_map(n_layers, world), n_layers)
+    mine = ranges[rank] if rank < len(ranges) else None
+    layers = {}
+    if mine is not None:
+        for l in range(mine.l0, mine.l1):
+            layers[l] = DenseLayer(be, mix, seed=500 + l, TB=TB)
+            layers[l].attn.copy_(torch.from_numpy(ctx.pkg.synth.make_activation(TB, layers[l].q_dim, 3)))
+    hidden = 5120
+    x = torch.from_numpy(ctx.pkg.synth.make_activation(TB, hidden, 11)).cuda()
+
+    def run_layer(l, xx):
+        layers[l].forward(xx, xx)  # residual add in place: the layer's output is the next layer's input
+
+    ms = ctx.time_ms(lambda i: run_layer_split(ranges, rank, x, run_layer), steps)
+    us = 1e3 * ms / steps
+    proto = next(iter(layers.values())) if layers else DenseLayer(be, mix, seed=1, TB=TB, hidden=256, n_head=2,
+                                                                  n_kv=2, head_dim=128, n_ff=256)
+    nbytes = n_layers * (ctx.pkg.synth.layer_weight_bytes(mix) + 4 * TB * 4 * hidden)
+    del proto
+    gbs = nbytes / us / 1e3
+    return {"cell": f"{mix} batch {TB} layer split x{world} ({n_layers} layers, {even_layer_map(n_layers, world)})",
+            "us": us, "us_per_layer": us / n_layers, "bytes": nbytes, "GB/s": gbs,
+            "frac_of_P_x_measured_hbm": gbs / (world * ctx.peaks["hbm_gbs"]),
+            "tok_s_64_layers": TB * 1e6 / (us / n_layers * LAYERS_PER_TOKEN), "launch": "host launches",
+            "note": "one batch in flight: per-token latency form; throughput with P batches pipelined is up to P x"}
+
+
+def safe(cells, fn, *a, **kw):
+    try:
+        cells.append(fn(*a, **kw))
+    except Exception as e:  # a cell that cannot run is reported, not hidden
+        cells.append({"cell": getattr(fn, "__name__", "cell") + str(a[1:]), "error": f"{type(e).__name__}: {e}"[:300]})
+
+
 # ------------------------------------------------------------------------ GPU arm
 def gpu_arm(args):
-    import torch
-    import torch.distributed as dist
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    pkg = graft.load_package()
-    from sycl_infer_b200.layer import DenseLayer
-    be = pkg.make_cuda_backend(local)
+    ctx = Ctx(args)
+    torch, pkg, be, rank, world = ctx.torch, ctx.pkg, ctx.be, ctx.rank, ctx.world
     L = args.layers
     arena = None
     if world > 1 and args.gather == "peer":
         from sycl_infer_b200.sharding import PeerArena
         arena = PeerArena(L * 65536 + 8192, rank, world)
-    layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1, rank=rank, world=world, arena=arena) for i in range(L)]
-    hidden = layers[0].hidden
-    # a step's two inputs (hidden state and attention output) share one device buffer per weight
-    # set, so the end-to-end loop moves them with ONE host-to-device copy
-    q_dim = layers[0].q_dim
-    xin = [torch.zeros(hidden + q_dim, dtype=torch.float32, device="cuda") for _ in range(L)]
-    xs = [b[:hidden].view(1, hidden) for b in xin]
-    attn = torch.from_numpy(pkg.synth.make_activation(1, q_dim, 3)).cuda()
-    for i, ly in enumerate(layers):
-        xs[i].copy_(torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)))
-        ly.attn = xin[i][hidden:].view(1, q_dim)
-        ly.attn.copy_(attn)
+    layers, xin, xs = make_layers(ctx, "Q4_K_M", 1, L, rank, world, arena=arena)
+    hidden, q_dim = layers[0].hidden, layers[0].q_dim
     out = arena.alloc(1, hidden) if arena is not None else torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
-    full_bytes = pkg.synth.layer_weight_bytes("Q4_K_M") + 4 * (
-        2 * hidden + layers[0].q_dim + 2 * layers[0].n_ff + (layers[0].q_dim + 2 * layers[0].kv_dim)
-        + 2 * hidden + 2 * layers[0].n_ff)
-    step_bytes = full_bytes  # whole-job bytes per step regardless of how rows are sharded
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    step_bytes = layer_bytes(pkg, "Q4_K_M", 1, layers[0])  # whole-job bytes per step however rows are sharded
 
     # One CUDA graph per weight set: the engine this path plugs into replays a recorded graph
-    # per decode step too, so a step is one graph launch (8 kernels), not 8 host launches.
+    # per decode step too, so a step is one graph launch, not four host launches.
     graphs = []
     if (world == 1 or arena is not None) and not args.no_graph:
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            for i in range(L):
-                layers[i].forward(xs[i], out)
-            side.synchronize()
-            for i in range(L):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    layers[i].forward(xs[i], out)
-                graphs.append(g)
-        torch.cuda.synchronize()
+        graphs = [ctx.capture(lambda i=i: layers[i].forward(xs[i], out)) for i in range(L)]
 
-    def run_steps(n, first=0):
-        for i in range(n):
-            if graphs:
-                graphs[(first + i) % L].replay()
-            else:
-                j = (first + i) % L
-                layers[j].forward(xs[j], out, cached[j])
-
-    cached = [ly.calls(xs[i], out) for i, ly in enumerate(layers)]
-    run_steps(max(args.warmup, 3))
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    run_steps(args.steps)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    # the device-resident loop is short; keep sampling clocks through the e2e loop as well
-    # ---- e2e: host buffers, pinned H2D of the step's activations, D2H of its output
-    hx = [torch.cat([torch.from_numpy(pkg.synth.make_activation(1, hidden, 10 + i)).view(-1), attn.cpu().view(-1)]).pin_memory()
-          for i in range(L)]
-    hout = torch.zeros(1, hidden, dtype=torch.float32).pin_memory()
-    dx = torch.zeros(1, hidden, dtype=torch.float32, device="cuda")
-
-    def e2e_step(i):
-        ly = layers[i % L]
-        xin[i % L].copy_(hx[i % L], non_blocking=True)
+    def step(i):
         if graphs:
             graphs[i % L].replay()
         else:
-            ly.forward(xs[i % L], out)
+            layers[i % L].forward(xs[i % L], out)
+
+    sampler = ClockSampler(ctx.local)
+    sampler.start()
+    ms = ctx.time_ms(step, args.steps, warm=max(args.warmup, 3))
+
+    # ---- e2e: host buffers, pinned H2D of the step's activations, D2H of its output, every step
+    hx = [xin[i].cpu().pin_memory() for i in range(L)]
+    hout = torch.zeros(1, hidden, dtype=torch.float32).pin_memory()
+
+    def e2e_step(i):
+        xin[i % L].copy_(hx[i % L], non_blocking=True)
+        step(i)
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g0.record()
-    for i in range(args.steps):
-        e2e_step(i)
-    g1.record()
-    barrier()
-    ms_e2e = g0.elapsed_time(g1)
-    # ---- roofline of the dominant kernel: GEMV launches alone (activations pre-quantized)
-    from sycl_infer_b200.backend import gemv_seg  # noqa: F401
+    ms_e2e = ctx.time_ms(e2e_step, args.steps)
+
+    # ---- roofline of the dominant kernel: the four GEMV launches of a layer alone, activations
+    # pre-quantized, in one CUDA graph over all weight sets
     calls = [ly.calls(xs[i], out) for i, ly in enumerate(layers)]
     for i, ly in enumerate(layers):  # make sure the quantized views are valid
         ly.forward(xs[i], out)
     torch.cuda.synchronize()
-    n_launch = 4 * args.steps
-    if world == 1 and not args.no_graph:
-        side = torch.cuda.Stream()
-        gg = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(gg, stream=side):
-                for i in range(L):
-                    for segs, _ in calls[i]:
-                        be.i8_gemv(segs)
-        torch.cuda.synchronize()
-        reps = max(1, args.steps // L)
-        n_launch = 4 * L * reps
-        gg.replay()
-        torch.cuda.synchronize()
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        r0.record()
-        for _ in range(reps):
-            gg.replay()
-        r1.record()
+    reps = max(1, args.steps // L)
+    n_launch = 4 * L * reps
+    gemv_only = lambda: [be.i8_gemv(segs) for i in range(L) for segs, _ in calls[i]]  # noqa: E731
+    if world == 1 or arena is not None:
+        gg = ctx.capture(gemv_only)
+        ms_gemv = ctx.time_ms(lambda i: gg.replay(), reps)
     else:
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        r0.record()
-        for i in range(args.steps):
-            for segs, _ in calls[i % L]:
-                be.i8_gemv(segs)
-        r1.record()
-    barrier()
-    ms_gemv = r0.elapsed_time(r1)
+        ms_gemv = ctx.time_ms(lambda i: gemv_only(), reps)
     clocks = sampler.summary()
-    if world > 1:
-        t = torch.tensor([ms, ms_e2e, ms_gemv], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e, ms_gemv = (float(v) for v in t.cpu())
-    peaks, how = measured_peaks()
+
+    cells = []
+    if not args.no_cells:
+        if world == 1:
+            safe(cells, cell_single_matrix, ctx, "config 0: Q4_K 4096x4096 GEMV, batch 1", 12, 4096, 4096)
+            safe(cells, cell_layer, ctx, "config 1: dense layer Q4_K_M, batch 16", "Q4_K_M", 16)
+            safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=512 x 5120 x 17408 Q4_K", 512)
+            safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=2048 x 5120 x 17408 Q4_K", 2048)
+            safe(cells, cell_moe, ctx, "config 3: routed MoE, 256 experts top-8, 16 tokens, Q4_K")
+            safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer IQ4_XS, batch 1", "IQ4_XS", 1)
+            safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer Q5_K, batch 1", "Q5_K", 1)
+            safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer Q4_K_M, batch 32", "Q4_K_M", 32)
+        else:
+            for mix in ("Q4_K_M", "IQ4_XS", "Q5_K"):
+                for TB in (1, 32):
+                    for arm in ("peer", "nccl"):
+                        safe(cells, cell_sharded, ctx, mix, TB, arm)
+                    safe(cells, cell_layer_split, ctx, mix, TB)
+
     if rank == 0:
         per_step = ms / args.steps
         gbs = step_bytes * args.steps / (ms * 1e-3) / 1e9
-        wbytes_launch = pkg.synth.layer_weight_bytes("Q4_K_M") / 4.0 / world
         alg_launch = step_bytes / 4.0 / world
         achieved = alg_launch * n_launch / (ms_gemv * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": per_step, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xu4/u6->int32, fp32 scales",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD, "launch": "cuda graph per step" if graphs else "host launches", "l2": f"inputs larger than L2: {L} rotating weight sets of 210 MB",
-                       "bytes_per_step": step_bytes, "parallelism": (f"row-sharded x{world}, " + ("peer-store epilogue + flag barrier" if arena is not None
-                                                                 else "NCCL all-gather")) if world > 1 else "1 GPU",
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": WORKLOAD, "launch": "cuda graph per step" if graphs else "host launches",
+                       "l2": f"inputs larger than L2: {L} rotating weight sets of 210 MB", "bytes_per_step": step_bytes,
+                       "parallelism": (f"row-sharded x{world}, " + ("peer-store epilogue, flag exchange inside the GEMV kernels"
+                                                                   if arena is not None else "NCCL all-gather"))
+                       if world > 1 else "1 GPU",
                        "decode_tok_s_64_layers": 1e3 / (per_step * LAYERS_PER_TOKEN),
-                       "pct_of_measured_hbm": 100.0 * gbs / peaks["hbm_gbs"], "pct_of_8TBs": 100.0 * gbs / 8000.0},
+                       "pct_of_measured_hbm": 100.0 * gbs / ctx.peaks["hbm_gbs"], "pct_of_8TBs": 100.0 * gbs / 8000.0},
             "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": 4 * (hidden + layers[0].q_dim), "d2h_bytes_per_step": 4 * hidden,
+                    "h2d_bytes_per_step": 4 * (hidden + q_dim), "d2h_bytes_per_step": 4 * hidden,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": args.steps * layers[0].launches_per_step(),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
-                         "peak_source": how,
-                         "kernel": "gemv (one launch per call, 4 per layer)", "bytes_per_launch": alg_launch,
-                         "weight_bytes_per_launch": wbytes_launch, "us_per_launch": 1e3 * ms_gemv / n_launch},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": ctx.peaks["hbm_gbs"] , "unit": "GB/s",
+                         "frac": achieved / ctx.peaks["hbm_gbs"],
+                         "traffic": ncu_traffic_per_launch() if world == 1 else None, "traffic_source": TRAFFIC_NOTE,
+                         "peak_source": ctx.peak_source,
+                         "kernel": "gemv_pinned_kernel (one launch per call, 4 per layer), CUDA graph, pre-quantized activations",
+                         "bytes_per_launch": alg_launch,
+                         "weight_bytes_per_launch": pkg.synth.layer_weight_bytes("Q4_K_M") / 4.0 / world,
+                         "us_per_launch": 1e3 * ms_gemv / n_launch},
+            "cells": cells,
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = {k: v for k, v in cpu_arm(6, 1, budget_s=20.0).items()
                                     if k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        ctx.dist.destroy_process_group()
 
 
 def main():
@@ -308,8 +507,9 @@ def main():
     ap.add_argument("--layers", type=int, default=8, help="distinct weight sets rotated through (L2 defeat)")
     ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-cells", action="store_true", help="headline only: skip the other configurations")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: GEMV epilogue stores rows on every GPU + flag barrier (peer), or NCCL all-gather")
+                    help="N > 1: GEMV epilogue stores rows on every GPU (peer), or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels from the host instead of CUDA graphs")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -319,7 +519,7 @@ def main():
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "GB/s", "n_gpus": args.gpus,
             "steps": r["steps"], "warmup": max(args.warmup, 1), "ms_per_step": r["ms_per_step"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xu4/u6->int32, fp32 scales",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
             "data": "synthetic", "config": {"workload": WORKLOAD, "device": "host CPU"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))

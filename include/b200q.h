@@ -102,27 +102,60 @@ int b200q_quant_gemv(void * stream, const b200q_seg * segs /*host*/, int n_segs,
 
 /* Options of b200q_quant_gemv_ex. */
 #define B200Q_OPT_PREQUANTIZED 1u /* the scratch already holds the call's quantized activation: no quantizer runs */
+#define B200Q_OPT_WAIT_PEERS 2u   /* before reading the activation, wait until every peer has signalled as often as this rank */
+#define B200Q_OPT_SIGNAL_PEERS 4u /* after the last output is stored on every peer, signal all peers */
 
-/* Where a gate|up call leaves the NEXT call's activation.  The reference quantizes
- * silu(gate)*up in front of the down projection (act_up, src/engine/graph.cpp:355-357;
- * quantizer src/backend/cpu/kernels/xq.cpp:21-26); with this set, the GEMV that computes gate
- * and up emits that quantized activation itself (one token), so the down call can run with
- * B200Q_OPT_PREQUANTIZED and no quantizer launch lies between the two.  The call must be
- * exactly two segments (gate, up) of equal n_rows, a multiple of 32.  group_counters:
- * n_rows/32 words, zero before the first call; every call leaves them zero again.  Calls
- * that share group_counters must not overlap on the GPU. */
+/* Flag words of the cross-GPU exchange, one array per rank, every array mapped on every rank
+ * (the same arrays b200q_peer_barrier uses): flags[p] is rank p's array as mapped on this GPU,
+ * at least 64 words, zero before the first call.  Word r of an array counts rank r's signals;
+ * words 32 and 33 are the owner's own counters.  With B200Q_OPT_SIGNAL_PEERS the last CTA of
+ * the launch tells every peer "my outputs of this call are in your memory"; with
+ * B200Q_OPT_WAIT_PEERS the launch's first action after the previous kernel has finished is a
+ * bounded wait (about a second, then B200Q_ETIMEOUT in the status word) for all peers' signals
+ * of the previous call.  Together they replace the separate b200q_peer_barrier launch between
+ * two row-sharded calls.  One token only; other calls use b200q_peer_barrier. */
+typedef struct b200q_peer_sync {
+    uint32_t * const * flags; /* host array of `world` device pointers */
+    int32_t world, rank;
+} b200q_peer_sync;
+
+/* Where a call leaves the NEXT call's activation.  The reference quantizes every GEMV input
+ * right in front of the GEMV (cpu_xq, src/backend/cpu/kernels/xq.cpp:10-50), for the down
+ * projection as silu(gate)*up (act_up, src/engine/graph.cpp:355-357; xq.cpp:21-26).  With this
+ * set, the GEMV that produces those values emits the quantized activation itself (one token),
+ * so the next call runs with B200Q_OPT_PREQUANTIZED: no quantizer launch, and every CTA of
+ * the next call fetches K*1.5 bytes instead of quantizing K floats.  Two forms:
+ *   one segment           the call's output vector (alpha, residual applied) is quantized;
+ *   two segments (gate|up) silu(gate)*up is quantized; equal n_rows, one weight type.
+ * n_rows must be a multiple of 32: such a call splits its rows over the SMs in whole 32-row
+ * groups, so that the CTA finishing a group holds all of its values. */
 typedef struct b200q_next_act {
     int8_t * x8;      /* [n_rows] codes of silu(gate)*up */
     float * xmeta;    /* [n_rows/32][2] */
     int32_t * xsumq;  /* [n_rows/32][2] */
-    int32_t * group_counters;
 } b200q_next_act;
+
+/* Weights of the call that will run NEXT in the stream (a hint; results never depend on it).
+ * A decode step is a chain of dependent launches; while one launch drains its last tiles and
+ * the next one waits for its activation, HBM would idle.  With this hint every CTA, once it
+ * has requested its last own weights, asks the memory system to bring the first part of the
+ * next call's weights into L2 (cp.async.bulk.prefetch.L2), so the next launch starts on warm
+ * L2 lines.  The reference has no counterpart (its GPU kernels rely on the hardware prefetcher
+ * of in-order queues); the plan that lists the calls of a layer (seg_plan,
+ * src/engine/engine_types.h:11-133) is where an engine takes the pointers from. */
+typedef struct b200q_weights_hint {
+    const void * w[B200Q_MAX_SEGS]; /* 16-byte aligned */
+    size_t bytes[B200Q_MAX_SEGS];
+    int32_t n;
+} b200q_weights_hint;
 
 struct b200q_peers;
 typedef struct b200q_call_opts {
     uint32_t flags;                  /* B200Q_OPT_* */
     const struct b200q_peers * peers; /* host; NULL = outputs stay on this GPU (see b200q_quant_gemv_scatter) */
     const b200q_next_act * next;     /* host; NULL = off */
+    const b200q_peer_sync * sync;    /* host; needed by B200Q_OPT_WAIT_PEERS / B200Q_OPT_SIGNAL_PEERS */
+    const b200q_weights_hint * prefetch; /* host; NULL = none */
 } b200q_call_opts;
 
 /* b200q_quant_gemv with options: the general form of the fused decode launch

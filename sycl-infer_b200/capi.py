@@ -27,15 +27,26 @@ class Peers(C.Structure):
 
 class NextAct(C.Structure):
     """struct b200q_next_act."""
-    _fields_ = [("x8", _vp), ("xmeta", _vp), ("xsumq", _vp), ("group_counters", _vp)]
+    _fields_ = [("x8", _vp), ("xmeta", _vp), ("xsumq", _vp)]
+
+
+class PeerSync(C.Structure):
+    """struct b200q_peer_sync."""
+    _fields_ = [("flags", C.POINTER(_vp)), ("world", C.c_int32), ("rank", C.c_int32)]
+
+
+class WeightsHint(C.Structure):
+    """struct b200q_weights_hint."""
+    _fields_ = [("w", _vp * 8), ("bytes", C.c_size_t * 8), ("n", C.c_int32)]
 
 
 class CallOpts(C.Structure):
     """struct b200q_call_opts."""
-    _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct))]
+    _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct)),
+                ("sync", C.POINTER(PeerSync)), ("prefetch", C.POINTER(WeightsHint))]
 
 
-OPT_PREQUANTIZED = 1
+OPT_PREQUANTIZED, OPT_WAIT_PEERS, OPT_SIGNAL_PEERS = 1, 2, 4
 
 
 class Seg(C.Structure):

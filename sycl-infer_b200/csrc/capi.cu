@@ -226,30 +226,76 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             c.peer_delta[i] = peers->out_delta[i];
         }
     }
-    NextAct next{nullptr, nullptr, nullptr, nullptr};
+    NextAct next{nullptr, nullptr, nullptr};
     if (opts && opts->next) {
         const b200q_next_act & n = *opts->next;
-        if (!n.x8 || !n.xmeta || !n.xsumq || !n.group_counters || !aligned(n.xmeta, 8) || !aligned(n.xsumq, 8)) {
+        if (!n.x8 || !n.xmeta || !n.xsumq || !aligned(n.xmeta, 8) || !aligned(n.xsumq, 8)) {
             set_error("%s: next-activation views must be non-null (xmeta, xsumq 8-byte aligned)", who);
             return B200Q_EINVAL;
         }
-        if (TB != 1 || n_segs != 2 || segs[0].n_rows != segs[1].n_rows || (segs[0].n_rows & 31) || c.n_peers > 0) {
-            set_error("%s: the next-activation form needs one token, two segments (gate, up) of equal n_rows, a "
-                      "multiple of 32, and no peers", who);
+        if (TB != 1 || n_segs > 2 || (n_segs == 2 && segs[0].n_rows != segs[1].n_rows) || (segs[0].n_rows & 31) ||
+            c.n_peers > 0) {
+            set_error("%s: the next-activation form needs one token, one segment or two (gate, up) of equal n_rows, "
+                      "n_rows a multiple of 32, and no peers", who);
             return B200Q_EINVAL;
         }
-        if (!gemv_takes_pinned(c) || !pinned_pairs_supported(c)) {
-            set_error("%s: the next-activation form needs gate and up of one type and a supported K (K=%d)", who, c.K);
+        if (!gemv_takes_pinned(c) || !pinned_next_supported(c)) {
+            set_error("%s: the next-activation form needs segments of one type and a supported K (K=%d)", who, c.K);
             return B200Q_EUNSUPPORTED;
         }
-        next = NextAct{n.group_counters, n.x8, n.xmeta, n.xsumq};
+        next = NextAct{n.x8, n.xmeta, n.xsumq};
+    }
+    PeerSync sync;
+    memset(&sync, 0, sizeof(sync));
+    if (opts && (opts->flags & (B200Q_OPT_WAIT_PEERS | B200Q_OPT_SIGNAL_PEERS))) {
+        const b200q_peer_sync * ps = opts->sync;
+        if (!ps || !ps->flags || ps->world < 1 || ps->world > B200Q_MAX_PEERS + 1 || ps->rank < 0 || ps->rank >= ps->world) {
+            set_error("%s: waiting for / signalling peers needs a valid b200q_peer_sync", who);
+            return B200Q_EINVAL;
+        }
+        for (int i = 0; i < ps->world; i++) {
+            if (!ps->flags[i]) {
+                set_error("%s: sync flags[%d] is null", who, i);
+                return B200Q_EINVAL;
+            }
+            sync.flag[i] = ps->flags[i];
+        }
+        sync.world = ps->world;
+        sync.rank = ps->rank;
+        sync.wait = (opts->flags & B200Q_OPT_WAIT_PEERS) ? 1 : 0;
+        sync.signal = (opts->flags & B200Q_OPT_SIGNAL_PEERS) ? 1 : 0;
+        if (!gemv_takes_pinned(c) || next.x8) {
+            set_error("%s: the in-kernel peer exchange serves one-token calls; use b200q_peer_barrier otherwise", who);
+            return B200Q_EUNSUPPORTED;
+        }
+    }
+    WeightsHint hint;
+    memset(&hint, 0, sizeof(hint));
+    if (opts && opts->prefetch) {
+        const b200q_weights_hint & h = *opts->prefetch;
+        if (h.n < 0 || h.n > B200Q_MAX_SEGS) {
+            set_error("%s: prefetch hint holds 0..%d weight ranges (got %d)", who, B200Q_MAX_SEGS, h.n);
+            return B200Q_EINVAL;
+        }
+        for (int i = 0; i < h.n; i++) {
+            if (!h.w[i] || !aligned(h.w[i], 16)) {
+                set_error("%s: prefetch hint range %d is null or not 16-byte aligned", who, i);
+                return B200Q_EINVAL;
+            }
+            hint.w[i] = static_cast<const uint8_t *>(h.w[i]);
+            hint.bytes[i] = h.bytes[i];
+        }
+        hint.n = h.n; // only the single-token kernel acts on it
     }
     if (gemv_takes_pinned(c)) {
         const bool inside = !prequant && pinned_quantizes(c, s0.x, s0.act_up);
-        if (!prequant && !inside) {
-            B200Q_CUDA_OK(launch_xq(stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB, s0.K, true));
+        if (!prequant && !inside) { // a quantizer launch of its own: it is the one that waits for the peers
+            B200Q_CUDA_OK(launch_xq(stream, s0.x, s0.act_up, s0.x_stride, s0.x_stride, x8, xmeta, xsumq, TB, s0.K, true,
+                                    sync.wait ? &sync : nullptr));
+            sync.wait = 0;
         }
-        B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.cnt ? &next : nullptr));
+        B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.x8 ? &next : nullptr,
+                                         (sync.wait || sync.signal) ? &sync : nullptr, hint.n ? &hint : nullptr));
         return B200Q_OK;
     }
     if (!prequant) {
@@ -527,6 +573,9 @@ int b200q_device_status(int * status, int clear) {
     int pin = 0;
     B200Q_CUDA_OK(read_pin_status(&pin, clear != 0));
     *status = *status ? *status : pin;
+    int xq = 0;
+    B200Q_CUDA_OK(read_xq_status(&xq, clear != 0));
+    *status = *status ? *status : xq;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

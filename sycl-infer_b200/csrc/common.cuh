@@ -128,10 +128,24 @@ struct CallDev {
 
 // gate|up calls: where the quantized silu(gate)*up of the following call goes (b200q_next_act)
 struct NextAct {
-    int32_t * cnt; // per 32-row group: output values stored so far (nullptr: feature off)
-    int8_t * x8;
+    int8_t * x8; // nullptr: feature off
     float * xmeta;
     int32_t * xsumq;
+};
+
+// weights of the call that follows, to be pulled into L2 (b200q_weights_hint)
+struct WeightsHint {
+    const uint8_t * w[B200Q_MAX_SEGS];
+    unsigned long long bytes[B200Q_MAX_SEGS];
+    int32_t n;
+    uint32_t per_cta; // bytes each CTA asks for
+};
+
+// cross-GPU flag exchange folded into a GEMV launch (b200q_peer_sync)
+struct PeerSync {
+    uint32_t * flag[B200Q_MAX_PEERS + 1]; // rank p's flag array as mapped on this GPU
+    int32_t world, rank;
+    int32_t wait, signal;
 };
 
 #ifdef __CUDACC__

@@ -16,6 +16,12 @@
 // A copy starts on a 16-byte boundary: rows that start at address A are fetched from A & ~15
 // and decoded from offset A & 15 (Q6_K / Q8_0 rows are only 2-byte aligned).
 //
+// Activation.  After the previous kernel has finished, ONE thread fetches the activation (the
+// fp32 vector, or the already quantized views) into shared memory with bulk copies: 148 CTAs
+// asking for the same 20 KB through per-thread loads serialise in the L2 slices that own those
+// lines (measured 3.7 us), a copy engine's full-line requests do not.  The consumer warps then
+// quantize it (8 threads per 32-value group) into a pack from which every thread takes its unit.
+//
 // Reduction.  Lanes are summed in aligned segments of `seg` lanes (the largest power of two
 // that divides U, so a segment never straddles two rows) with butterfly shuffles; one lane per
 // segment stores the partial into a small shared-memory array [slot][part]; a dedicated
@@ -33,7 +39,8 @@
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // B200Q_ETIMEOUT in a status word the host reads (b200q_device_status) and the role returns.
-#include <mutex>
+#include <cstdlib>
+#include <cstring>
 
 #include "launch.h"
 #include "stream_core.cuh"
@@ -52,14 +59,34 @@ struct PinArgs {
     CallDev c;
     CostSplit cost;
     const float * xq_x; // when set, every CTA quantizes this fp32 activation itself
-    NextAct next;       // gate|up calls: quantized silu(gate)*up for the following call (cnt == nullptr: off)
+    NextAct next;       // the call's output, quantized, as the following call's activation (x8 == nullptr: off)
+    PeerSync sync;      // row-sharded calls: wait for / signal the peers inside this launch
+    WeightsHint hint;   // the next call's weights, for the L2 prefetch at the end of the producer's work
     int32_t W, R, U, seg, P, Ppad; // P = U / seg partials per row, rows Ppad words apart
     // paired mode (next.cnt != nullptr): a step is H gate rows and the H up rows of the same
     // indices; the up rows sit half_off bytes into the stage
-    int32_t H, half_off;
+    int32_t H, half_off, paired, next_mode;
     int32_t stages, stage_bytes, red_bytes;
     int32_t off_pack, off_tiles;
+    int32_t off_xraw; // shared-memory landing zone of the raw activation (fp32 vector, or the three quantized views)
+#ifdef B200Q_TUNING
+    unsigned long long * trace; // [launch % 64][CTA][8] globaltimer stamps of the roles' milestones
+    int32_t launch_idx;
+#endif
 };
+
+#ifdef B200Q_TUNING
+__device__ __forceinline__ void pin_stamp(const PinArgs & a, int ev) {
+    if (a.trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.trace[((size_t)(a.launch_idx & 63) * 160 + blockIdx.x) * 8 + ev] = t;
+    }
+}
+#define PIN_STAMP(ev) pin_stamp(a, ev)
+#else
+#define PIN_STAMP(ev)
+#endif
 
 struct PinRing {
     int stage;
@@ -78,14 +105,14 @@ struct PinRing {
     }
 };
 
-// Paired mode: the CTA's range of (gate row, up row) pairs.  Both segments have the same type
-// and row count, so a pair costs 2 x bytes-per-superblock.
-__device__ __forceinline__ RowRange pair_rows(const CallDev & c, uint32_t lo, uint32_t hi) {
-    const uint32_t w = 2u * (uint32_t)sb_bytes(c.seg[0].type);
+// Calls that also emit the next call's activation split their rows (or gate|up pairs) in whole
+// 32-row groups: the CTA that finishes a group holds all 32 values and quantizes it on the
+// spot, with no exchange between CTAs.  Part p of G owns groups [n*p/G, n*(p+1)/G).
+__device__ __forceinline__ RowRange group_rows(const CallDev & c, uint32_t p, uint32_t G) {
+    const uint32_t n = (uint32_t)c.seg[0].n_rows >> 5;
     RowRange r;
-    r.lo = (int)((lo + w - 1) / w);
-    r.hi = (int)((hi + w - 1) / w);
-    r.hi = r.hi < c.seg[0].n_rows ? r.hi : c.seg[0].n_rows;
+    r.lo = (int)(32u * (n * p / G));
+    r.hi = (int)(32u * (n * (p + 1) / G));
     return r;
 }
 
@@ -119,9 +146,18 @@ __device__ __forceinline__ bool mbar_wait_gated(uint32_t bar, uint32_t parity, i
 }
 
 // ---- activation: quantize (8 threads per 32-value group) or fetch, then pin --------------------
+// Pack layout of this kernel: 48 bytes per group (codes | sx | xs0 | xs1 | sx*(xs0+xs1)), the
+// four groups of a unit back to back, units 208 bytes apart: an odd number of 16-byte chunks, so
+// the eight lanes of a quarter-warp that fetch their units with 128-bit loads hit distinct banks
+// (units 192 bytes apart would put them on two).
+constexpr uint32_t kPinUnitBytes = 4 * kPackGroup + 16;
+__device__ __forceinline__ uint32_t pin_pack_addr(uint32_t pack, int g) {
+    return pack + (uint32_t)(g >> 2) * kPinUnitBytes + (uint32_t)(g & 3) * kPackGroup;
+}
+
 // The arithmetic is the standalone quantizer's (xq.cuh), bit for bit: max and integer sums are
 // exact in any order, every fp32 operation is a single correctly rounded one.
-__device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, const float * x, int G, int warp,
+__device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, uint32_t xraw, int G, int warp,
                                              int lane, int W, bool write_views) {
     constexpr int kBatch = 4; // loads of several passes in flight before the first is used
     const int stride = 32 * W, n_tasks = 8 * G;
@@ -131,9 +167,9 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, c
         for (int i = 0; i < kBatch; i++) {
             const int task = base0 + i * stride + lane;
             fb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (task < n_tasks) { // through L2 when peers store x
-                const float4 * src = reinterpret_cast<const float4 *>(x) + task;
-                fb[i] = c.n_peers > 0 ? __ldcg(src) : *src;
+            if (task < n_tasks) {
+                const uint4 u = lds128(xraw + 16u * (uint32_t)task);
+                fb[i] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
             }
         }
 #pragma unroll
@@ -164,7 +200,7 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, c
             const int s0 = (j & 4) ? other : s, s1 = (j & 4) ? s : other;
             const float sx = h2f(f2h_trunc(mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 0.0f));
             if (valid) {
-                const uint32_t p = pack_addr(pack, g);
+                const uint32_t p = pin_pack_addr(pack, g);
                 sts32(p + 4 * j, word);
                 if (j == 0) {
                     sts128(p + 32, __float_as_uint(sx), (uint32_t)s0, (uint32_t)s1,
@@ -185,7 +221,7 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, c
 __device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & a) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const uint32_t p = pack_addr(pack, 4 * unit + i);
+        const uint32_t p = pin_pack_addr(pack, 4 * unit + i);
         const uint4 x0 = lds128(p), x1 = lds128(p + 16), m = lds128(p + 32);
         a.x[i][0] = x0.x, a.x[i][1] = x0.y, a.x[i][2] = x0.z, a.x[i][3] = x0.w;
         a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
@@ -196,19 +232,18 @@ __device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & 
     }
 }
 
-// The pack from the caller's quantized views (one token): each group is fetched ONCE per CTA.
-// (Every thread fetching its own unit straight from global memory makes all row slots of all
-// CTAs hit the same few lines of xmeta / xsumq, which serialises in one L2 slice.)
-__device__ __forceinline__ void pin_stage_views(uint32_t pack, const CallDev & c, int G, int tid, int nthr) {
+// The pack from the caller's quantized views (one token), which lie in shared memory as
+// [K codes][K/32 (scale, 0) pairs][K/32 sum pairs].
+__device__ __forceinline__ void pin_stage_views(uint32_t pack, uint32_t xraw, int G, int tid, int nthr) {
+    const uint32_t meta = xraw + 32u * (uint32_t)G, sums = meta + 8u * (uint32_t)G;
     for (int g = tid; g < G; g += nthr) { // one token: group index == array index
-        const uint4 * gx = reinterpret_cast<const uint4 *>(c.x8 + (size_t)g * 32);
-        const uint4 x0 = __ldcg(gx), x1 = __ldcg(gx + 1);
-        const float sx = __ldcg(c.xmeta + 2 * (size_t)g);
-        const int2 xs = __ldcg(reinterpret_cast<const int2 *>(c.xsumq) + g);
-        const uint32_t p = pack_addr(pack, g);
+        const uint4 x0 = lds128(xraw + 32u * (uint32_t)g), x1 = lds128(xraw + 32u * (uint32_t)g + 16u);
+        const float sx = __uint_as_float(lds32(meta + 8u * (uint32_t)g));
+        const uint2 xs = lds64(sums + 8u * (uint32_t)g);
+        const uint32_t p = pin_pack_addr(pack, g);
         sts128(p, x0.x, x0.y, x0.z, x0.w);
         sts128(p + 16, x1.x, x1.y, x1.z, x1.w);
-        sts128(p + 32, __float_as_uint(sx), (uint32_t)xs.x, (uint32_t)xs.y, __float_as_uint(sx * (float)(xs.x + xs.y)));
+        sts128(p + 32, __float_as_uint(sx), xs.x, xs.y, __float_as_uint(sx * (float)((int)xs.x + (int)xs.y)));
     }
 }
 
@@ -260,10 +295,20 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_
     const bool writer = (lane & (seg - 1)) == 0;
     const int h = unit & 1;
     for (int row0 = lo; row0 < hi; row0 += H) {
+#ifdef B200Q_TUNING
+        if (threadIdx.x == 0 && row0 == lo) {
+            PIN_STAMP(6);
+        }
+#endif
         if (!mbar_wait(bars.full + 8 * pos.stage, pos.phase, &g_pin_status)) {
             return false;
         }
         const bool active = mine && sl < hi - row0;
+#ifdef B200Q_TUNING
+        if (threadIdx.x == 0 && row0 == lo) {
+            PIN_STAMP(3);
+        }
+#endif
         float v = 0.f;
         if (active) {
             const uint32_t mis = (wbase + (uint32_t)row0 * row_bytes) & 15u; // only the low four bits matter
@@ -295,18 +340,19 @@ template <int TYPE>
 __device__ __forceinline__ bool pin_consume_call(const PinArgs & a, int si, uint32_t cost_lo, uint32_t cost_hi,
                                                  uint32_t tiles, uint32_t red, const PinBars & bars, const ActPin & pin,
                                                  int slot, int unit, PinRing & pos) {
-    if (a.next.cnt) { // gate rows and up rows together
-        const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
+    if (a.paired) { // gate rows and up rows together
+        const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
         return pin_consume_rows<TYPE>(a, a.c.seg[0].w, a.c.seg[1].w, pr.lo, pr.hi, tiles, red, bars, pin, slot, unit, pos);
     }
-    const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+    const RowRange rr = a.next.x8 ? group_rows(a.c, blockIdx.x, gridDim.x) : cta_rows(a.c, si, cost_lo, cost_hi);
     return pin_consume_rows<TYPE>(a, a.c.seg[si].w, a.c.seg[si].w, rr.lo, rr.hi, tiles, red, bars, pin, slot, unit, pos);
 }
 
-// silu(gate)*up of rows [32g, 32g+32) quantized as b200q_xq would (one token); lane i holds
-// gate and up of row 32g + i.
+// Rows [32g, 32g+32) of the call's output as the next call's activation, quantized as b200q_xq
+// would (one token): the output itself (one segment; lane i holds row 32g + i in gv), or
+// silu(gate)*up (two segments; lane i holds gate and up of row 32g + i).
 __device__ __forceinline__ void next_act_group(const PinArgs & a, int g, int lane, float gv, float uv) {
-    const float v = __fmul_rn(silu_exact(gv), uv);
+    const float v = a.paired ? __fmul_rn(silu_exact(gv), uv) : gv;
     float scale;
     int s0, s1;
     const int q = xq_group(v, lane, scale, s0, s1);
@@ -316,26 +362,6 @@ __device__ __forceinline__ void next_act_group(const PinArgs & a, int g, int lan
         a.next.xmeta[2 * g + 1] = 0.0f;
         a.next.xsumq[2 * g] = s0;
         a.next.xsumq[2 * g + 1] = s1;
-    }
-}
-
-// A group this CTA owns only part of (`mine` of its 32 pairs, already stored): publish the
-// stores, count them, and quantize the group if this CTA's rows were the last to arrive.
-__device__ __forceinline__ void next_act_shared_group(const PinArgs & a, int g, int mine, int lane) {
-    __threadfence();
-    __syncwarp();
-    int old = 0;
-    if (lane == 0) {
-        old = atomicAdd(a.next.cnt + g, mine);
-    }
-    old = __shfl_sync(0xFFFFFFFFu, old, 0);
-    if (old + mine == 32) {
-        __threadfence();
-        const float gv = __ldcg(a.c.seg[0].out + 32 * g + lane), uv = __ldcg(a.c.seg[1].out + 32 * g + lane);
-        next_act_group(a, g, lane, gv, uv);
-        if (lane == 0) {
-            a.next.cnt[g] = 0; // ready for the next call
-        }
     }
 }
 
@@ -352,6 +378,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
     // let the next kernel of the stream be scheduled as soon as this grid is resident
     asm volatile("griddepcontrol.launch_dependents;");
     if (threadIdx.x == 0) {
+        PIN_STAMP(0);
         for (int s = 0; s < S; s++) {
             mbar_init(bars.full + 8 * s, 1);
             mbar_init(bars.empty + 8 * s, (uint32_t)W);
@@ -360,6 +387,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
             mbar_init(bars.red_full + 8 * b, (uint32_t)W);
             mbar_init(bars.red_empty + 8 * b, 1);
         }
+        mbar_init(base + 200, 1); // the activation's bulk copies
         sts32(started, 0);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -373,8 +401,8 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         int stage = 0, issued = 0;
         uint32_t par = 1; // parity of the empty barrier: a fresh slot is free
         bool alive = true;
-        if (a.next.cnt) { // paired: H gate rows and the H up rows of the same indices per stage
-            const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
+        if (a.paired) { // H gate rows and the H up rows of the same indices per stage
+            const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
             const size_t row_bytes = (size_t)nb * sb_bytes(a.c.seg[0].type);
             for (int p0 = pr.lo; p0 < pr.hi; p0 += a.H) {
                 const int rows = min(a.H, pr.hi - p0);
@@ -400,9 +428,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
                 }
             }
         }
-        for (int si = 0; si < a.c.n_segs && alive && !a.next.cnt; si++) {
+        for (int si = 0; si < a.c.n_segs && alive && !a.paired; si++) {
             const SegDev & sg = a.c.seg[si];
-            const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+            const RowRange rr = a.next.x8 ? group_rows(a.c, blockIdx.x, gridDim.x) : cta_rows(a.c, si, cost_lo, cost_hi);
             const size_t row_bytes = (size_t)nb * sb_bytes(sg.type);
             for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
                 const int rows = min(R, rr.hi - row0);
@@ -423,6 +451,32 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
                 }
             }
         }
+        if (alive && a.hint.n > 0) {
+            // This CTA's own weights are all requested: warm L2 with the part of the next call's
+            // weight stream that the same-numbered CTA of the next launch will ask for first.
+            unsigned long long total = 0;
+            for (int i = 0; i < a.hint.n; i++) {
+                total += a.hint.bytes[i];
+            }
+            unsigned long long off = (total / gridDim.x * blockIdx.x) & ~15ull, left = a.hint.per_cta;
+            for (int i = 0; i < a.hint.n && left > 0; i++) {
+                if (off >= a.hint.bytes[i]) {
+                    off -= a.hint.bytes[i];
+                    continue;
+                }
+                unsigned long long n = a.hint.bytes[i] - off;
+                n = n < left ? n : left;
+                const uint8_t * p = a.hint.w[i] + off;
+                for (unsigned long long done = 0; done < n; done += 32768) {
+                    const uint32_t sz = (uint32_t)((n - done < 32768 ? n - done : 32768) & ~15ull);
+                    if (sz) {
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + done), "r"(sz) : "memory");
+                    }
+                }
+                left -= n;
+                off = 0;
+            }
+        }
         if (!alive) { // leaving early: wait (bounded) until the copies still in flight have landed
             for (int s = 0; s < S && s < issued; s++) {
                 const int last = ((issued - 1 - s) / S) * S + s; // last step that filled stage s
@@ -434,32 +488,34 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
 
     // everything below reads the activation or writes outputs: wait for the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        PIN_STAMP(1);
+    }
 
     if (warp == W + 1) {
         // ---------------------------------------------------------------- epilogue warp
         int rb = 0;
         uint32_t rphase = 0;
         const int P = a.P, Ppad = a.Ppad;
-        if (a.next.cnt) {
-            // Paired mode.  Lanes 0..15 take gate slots, lanes 16..31 the up slots of the same pairs,
-            // sixteen pairs at a time.  Every stored value is also kept in a 64-pair ring in shared
-            // memory; when a 32-pair group completes, lane i forms silu(gate)*up of its row from
-            // the ring and the warp quantizes the group.  Groups shared with a neighbouring CTA
-            // (at most the first and the last of the range) are completed through a counter.
+        if (a.next.x8) {
+            // The call's output doubles as the next call's activation.  One segment: lane = row
+            // slot.  Two segments (gate|up, paired mode): lanes 0..15 take gate slots, lanes 16..31
+            // the up slots of the same pairs, sixteen pairs at a time.  Every stored value is also
+            // kept in a 64-row ring in shared memory; when a 32-row group completes, lane i takes
+            // its row's value(s) from the ring and the warp quantizes the group (a CTA's range
+            // is made of whole groups).
             const uint32_t ring = red + (uint32_t)(kRedBufs * a.red_bytes); // 2 x 64 floats behind the partials
-            const RowRange pr = pair_rows(a.c, cost_lo, cost_hi);
-            const SegDev & sg0 = a.c.seg[0];
-            const SegDev & sg1 = a.c.seg[1];
-            const int H = a.H;
+            const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
+            const int H = a.H, per = a.paired ? 16 : 32;
+            const int e = a.paired ? lane >> 4 : 0, li = lane & (per - 1);
+            const SegDev & sg = a.c.seg[e];
             for (int p0 = pr.lo; p0 < pr.hi; p0 += H) {
                 const int rows = min(H, pr.hi - p0);
                 if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
                     return;
                 }
                 const uint32_t rbuf = red + (uint32_t)(rb * a.red_bytes);
-                const int e = lane >> 4, li = lane & 15;
-                const SegDev & sg = e ? sg1 : sg0;
-                for (int c0 = 0; c0 < rows; c0 += 16) {
+                for (int c0 = 0; c0 < rows; c0 += per) {
                     if (c0 + li < rows) {
                         const uint32_t p = rbuf + (uint32_t)((e * H + c0 + li) * Ppad) * 4u;
                         float sum = 0.f;
@@ -483,24 +539,13 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
                     rb = 0;
                     rphase ^= 1;
                 }
-                // groups whose last pair was stored in this step (H <= 32: at most two)
+                // groups whose last row was stored in this step (H <= 32: at most two)
                 for (int g = p0 >> 5; 32 * g + 32 <= p0 + rows; g++) {
-                    if (32 * g + 32 <= p0) {
-                        continue;
-                    }
-                    if (32 * g >= pr.lo) { // all 32 pairs are this CTA's
-                        const float gv = __uint_as_float(lds32(ring + (uint32_t)((32 * g + lane) & 63) * 4u));
-                        const float uv = __uint_as_float(lds32(ring + (uint32_t)(64 + ((32 * g + lane) & 63)) * 4u));
-                        next_act_group(a, g, lane, gv, uv);
-                    } else {
-                        next_act_shared_group(a, g, 32 * g + 32 - pr.lo, lane);
-                    }
+                    const float gv = __uint_as_float(lds32(ring + (uint32_t)((32 * g + lane) & 63) * 4u));
+                    const float uv = __uint_as_float(lds32(ring + (uint32_t)(64 + ((32 * g + lane) & 63)) * 4u));
+                    next_act_group(a, g, lane, gv, uv);
                     __syncwarp();
                 }
-            }
-            if (pr.hi > pr.lo && (pr.hi & 31)) { // the range ends inside a group
-                const int g = pr.hi >> 5;
-                next_act_shared_group(a, g, pr.hi - max(pr.lo, 32 * g), lane);
             }
             return;
         }
@@ -538,26 +583,97 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
                 }
             }
         }
+        if (a.sync.signal) {
+            // every CTA: publish its peer stores system-wide, then count itself; the last one
+            // advances this rank's call count and writes it into every peer's flag array
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t * own = a.sync.flag[a.sync.rank];
+                const uint32_t old = atomicAdd(own + 33, 1u);
+                if (old == gridDim.x - 1) {
+                    own[33] = 0;
+                    uint32_t seq;
+                    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(seq) : "l"(own + 32) : "memory");
+                    seq += 1;
+                    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(own + 32), "r"(seq) : "memory");
+                    __threadfence_system();
+                    for (int p = 0; p < a.sync.world; p++) {
+                        if (p != a.sync.rank) {
+                            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.sync.flag[p] + a.sync.rank), "r"(seq)
+                                         : "memory");
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+            PIN_STAMP(5);
+        }
         return;
     }
 
     // -------------------------------------------------------------------- consumers
+    if (a.sync.wait) {
+        // every peer must have finished storing the previous call's rows into this GPU's memory:
+        // its signal count has to reach this rank's own (all ranks run the same call sequence)
+        if (warp == 0 && lane < a.sync.world && lane != a.sync.rank) {
+            const uint32_t * own = a.sync.flag[a.sync.rank];
+            uint32_t expected;
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(expected) : "l"(own + 32) : "memory");
+            const long long t0 = clock64();
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(own + lane) : "memory");
+                if ((int32_t)(v - expected) >= 0) {
+                    break;
+                }
+                if (clock64() - t0 > kSpinCycles) {
+                    atomicExch(&g_pin_status, B200Q_ETIMEOUT);
+                    break;
+                }
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
+    }
     const int U = a.U;
     const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
     ActPin pin;
-    if (a.xq_x) {
-        pin_quantize(pack, a.c, a.xq_x, 8 * nb, warp, lane, W, blockIdx.x == 0);
-    } else {
-        pin_stage_views(pack, a.c, 8 * nb, (int)threadIdx.x, 32 * W);
+    {
+        const uint32_t xraw = base + (uint32_t)a.off_xraw, act_bar = base + 200;
+        const uint32_t K = (uint32_t)a.c.K;
+        if (threadIdx.x == 0) {
+            if (a.xq_x) {
+                mbar_expect_tx(act_bar, 4u * K);
+                bulk_g2s(xraw, a.xq_x, 4u * K, act_bar);
+            } else {
+                mbar_expect_tx(act_bar, K + K / 2);
+                bulk_g2s(xraw, a.c.x8, K, act_bar);
+                bulk_g2s(xraw + K, a.c.xmeta, K / 4, act_bar);
+                bulk_g2s(xraw + K + K / 4, a.c.xsumq, K / 4, act_bar);
+            }
+        }
+        if (!mbar_wait(act_bar, 0, &g_pin_status)) {
+            return;
+        }
+        if (threadIdx.x == 0) {
+            PIN_STAMP(7);
+        }
+        if (a.xq_x) {
+            pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0);
+        } else {
+            pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
+        }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
     pin_from_pack(pack, unit, pin);
     if (threadIdx.x == 0) {
         asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(started), "r"(1u) : "memory");
+        PIN_STAMP(2);
     }
 
     PinRing pos{0, 0, 0, 0};
-    const int n_calls = a.next.cnt ? 1 : a.c.n_segs; // paired mode walks both segments at once
+    const int n_calls = a.paired ? 1 : a.c.n_segs; // paired mode walks both segments at once
     for (int si = 0; si < n_calls; si++) {
         bool ok;
         switch (a.c.seg[si].type) {
@@ -570,6 +686,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         if (!ok) {
             return;
         }
+    }
+    if (threadIdx.x == 0) {
+        PIN_STAMP(4);
     }
 }
 
@@ -599,12 +718,15 @@ static void pick_shape(int U, bool even_rows, int & W, int & R) {
     }
 }
 
-static uint32_t pin_grid(const CallDev & c, const PinArgs & a) {
-    const int steps = (c.total_rows + a.R - 1) / a.R;
+static uint32_t pin_grid(const CallDev & c, const PinArgs & a, int next_mode) {
+    const int steps = next_mode ? c.seg[0].n_rows / 32 : (c.total_rows + a.R - 1) / a.R; // whole groups in next mode
     return (uint32_t)(steps < kSMs ? steps : kSMs);
 }
 
-static bool pin_plan(const CallDev & c, bool paired, PinArgs & a) {
+// next_mode: 0 = plain call, 1 = one segment whose output is quantized for the next call,
+// 2 = gate|up pairs (silu(gate)*up quantized for the next call)
+static bool pin_plan(const CallDev & c, int next_mode, bool fp32_in, PinArgs & a) {
+    const bool paired = next_mode == 2;
     if (c.TB != 1 || (c.K & 255)) {
         return false;
     }
@@ -620,6 +742,12 @@ static bool pin_plan(const CallDev & c, bool paired, PinArgs & a) {
             return false;
         }
     }
+    if (next_mode == 1) { // at most 32 rows per step
+        R = R > 32 ? 32 : R;
+        if (c.n_segs != 1) {
+            return false;
+        }
+    }
     int max_sbb = 0;
     for (int i = 0; i < c.n_segs; i++) {
         max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
@@ -630,18 +758,21 @@ static bool pin_plan(const CallDev & c, bool paired, PinArgs & a) {
         seg *= 2;
     }
     const int P = U / seg, Ppad = P | 1; // odd row pitch: the epilogue's lanes hit distinct banks
-    const size_t pack_bytes = (size_t)nb * kPackSB;
+    const size_t pack_bytes = (size_t)U * kPinUnitBytes;
     for (;; R -= paired ? 2 : 1) { // fewer row slots when two stages of R rows do not fit
         if (R < 1) {
             return false;
         }
         const size_t red_bytes = ((size_t)R * Ppad * 4 + 15) / 16 * 16;
-        const size_t off_pack = kPinHdr + kRedBufs * red_bytes + (paired ? 512 : 0); // + the epilogue's value ring
-        const size_t off_tiles = (off_pack + pack_bytes + 127) / 128 * 128;
+        const size_t off_pack = kPinHdr + kRedBufs * red_bytes + (next_mode ? 512 : 0); // + the epilogue's value ring
+        const size_t off_xraw = (off_pack + pack_bytes + 15) / 16 * 16;
+        // room for the fp32 vector, or for the three quantized views (K + K/4 + K/4 bytes)
+        const size_t off_tiles = (off_xraw + (fp32_in ? 4 : 1) * (size_t)c.K + (fp32_in ? 0 : c.K / 2) + 127) / 128 * 128;
         const size_t half = ((size_t)(R / 2) * row_max + 32 + 15) / 16 * 16;
         const size_t stage = paired ? (2 * half + 127) / 128 * 128 : ((size_t)R * row_max + 32 + 127) / 128 * 128;
         a.H = paired ? R / 2 : R;
         a.half_off = paired ? (int32_t)half : 0;
+        a.paired = paired ? 1 : 0;
         if (off_tiles + 2 * stage > (size_t)kPinSmem || stage >= (1u << 20)) {
             continue;
         }
@@ -651,43 +782,75 @@ static bool pin_plan(const CallDev & c, bool paired, PinArgs & a) {
         a.stage_bytes = (int32_t)stage;
         a.red_bytes = (int32_t)red_bytes;
         a.off_pack = (int32_t)off_pack;
+        a.off_xraw = (int32_t)off_xraw;
         a.off_tiles = (int32_t)off_tiles;
         break;
     }
-    return cost_split(c, pin_grid(c, a), a.cost);
+    a.next_mode = next_mode;
+    return cost_split(c, pin_grid(c, a, next_mode), a.cost);
+}
+
+static bool views_aligned(const CallDev & c) { // bulk copies start on 16-byte boundaries
+    return ((reinterpret_cast<uintptr_t>(c.x8) | reinterpret_cast<uintptr_t>(c.xmeta) | reinterpret_cast<uintptr_t>(c.xsumq)) & 15) == 0;
 }
 
 bool pinned_supported(const CallDev & c) {
     PinArgs a;
-    return pin_plan(c, false, a);
+    return views_aligned(c) && pin_plan(c, 0, false, a);
 }
 
-bool pinned_pairs_supported(const CallDev & c) {
+bool pinned_next_supported(const CallDev & c) { // one segment, or gate|up pairs
     PinArgs a;
-    return pin_plan(c, true, a);
+    return views_aligned(c) && pin_plan(c, c.n_segs == 2 ? 2 : 1, true, a);
 }
 
 bool pinned_quantizes(const CallDev & c, const float * x, const float * act_up) {
     // the fused silu(x)*up form evaluates a double-precision exp per value: every CTA repeating
     // that costs more than a launch; the vector loads of the in-kernel quantizer need 16-byte alignment
-    return c.TB == 1 && !act_up && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && pinned_supported(c);
+    PinArgs a;
+    return c.TB == 1 && !act_up && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && views_aligned(c) &&
+           pin_plan(c, 0, true, a);
 }
 
-cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next) {
+cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next,
+                               const PeerSync * sync, const WeightsHint * hint) {
     PinArgs a;
     a.c = c;
     a.xq_x = xq_x;
-    a.next = next ? *next : NextAct{nullptr, nullptr, nullptr, nullptr};
-    if (!pin_plan(c, a.next.cnt != nullptr, a)) {
+    a.next = next ? *next : NextAct{nullptr, nullptr, nullptr};
+    memset(&a.sync, 0, sizeof(a.sync));
+    if (sync) {
+        a.sync = *sync;
+    }
+    memset(&a.hint, 0, sizeof(a.hint));
+    if (hint && hint->n > 0) {
+        a.hint = *hint;
+        unsigned long long total = 0;
+        for (int i = 0; i < hint->n; i++) {
+            total += hint->bytes[i];
+        }
+        // what HBM delivers while a launch drains and the next one gets going (about 6 us), shared out
+        const unsigned long long share = total / kSMs, cap = 288 * 1024;
+        a.hint.per_cta = (uint32_t)((share < cap ? share : cap) & ~15ull);
+    }
+    if (!pin_plan(c, a.next.x8 ? (c.n_segs == 2 ? 2 : 1) : 0, xq_x != nullptr, a)) {
         return cudaErrorInvalidConfiguration;
     }
+#ifdef B200Q_TUNING
+    {
+        static int launches = 0;
+        const char * tp = getenv("B200Q_TRACE_PTR");
+        a.trace = tp ? reinterpret_cast<unsigned long long *>(strtoull(tp, nullptr, 0)) : nullptr;
+        a.launch_idx = launches++;
+    }
+#endif
     const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
     cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_pinned_kernel), kPinSmem);
     if (e != cudaSuccess) {
         return e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(pin_grid(c, a));
+    cfg.gridDim = dim3(pin_grid(c, a, a.next_mode));
     cfg.blockDim = dim3((unsigned)(32 * (a.W + 2)));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;

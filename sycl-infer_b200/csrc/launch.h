@@ -4,17 +4,21 @@
 
 namespace b200q {
 
+// wait_for != nullptr: the quantizer first waits for the peers' signals (row-sharded calls)
 cudaError_t launch_xq(cudaStream_t s, const float * x, const float * up, int x_stride, int up_stride, int8_t * x8,
-                      float * xmeta, int32_t * xsumq, int TB, int K, bool pdl_primary);
+                      float * xmeta, int32_t * xsumq, int TB, int K, bool pdl_primary,
+                      const PeerSync * wait_for = nullptr);
+cudaError_t read_xq_status(int * status, bool clear);
 cudaError_t launch_gemv_rows(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 bool stream_supported(const CallDev & call);
 cudaError_t launch_gemv_stream(cudaStream_t s, const CallDev & call, bool pdl_secondary);
 cudaError_t read_device_status(int * status, bool clear);
 // single-token kernel with the activation pinned in registers (gemv_pinned.cu)
 bool pinned_supported(const CallDev & call);
-bool pinned_pairs_supported(const CallDev & call); // gate|up with the next call's activation
+bool pinned_next_supported(const CallDev & call); // a call that also emits the next call's activation
 bool pinned_quantizes(const CallDev & call, const float * x, const float * act_up);
-cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next);
+cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next,
+                               const PeerSync * sync = nullptr, const WeightsHint * hint = nullptr);
 cudaError_t read_pin_status(int * status, bool clear);
 // cudaFuncAttributeMaxDynamicSharedMemorySize is per device: set once per (kernel, device)
 cudaError_t ensure_dynamic_smem(const void * func, int bytes);

@@ -42,14 +42,16 @@ class DenseLayer:
         self.o_out = new(TB, hidden)
         self.gu = new(TB, 2 * n_ff)
         self.out = new(TB, hidden)  # the layer's output when the caller passes none
+        self.next_layer = None  # the layer whose q|k|v follows this layer's down call (weights prefetch hint)
+        self.exchange = True  # False: leave the cross-GPU exchange out (timing of the compute alone; wrong results)
         if self.arena:
             self._peers, self._flags = self.arena.peers(), self.arena.flag_ptrs()
+            self._sync = (self._flags, world, rank)
         self.act_h = alloc_act(TB, hidden, dev)
         self.act_q = alloc_act(TB, self.q_dim, dev)
         self.act_f = alloc_act(TB, n_ff, dev)
         # one token on one GPU: the gate|up GEMV leaves the quantized silu(gate)*up for the down call
         self.fused_h = TB == 1 and world == 1
-        self.h_counters = torch.zeros(n_ff // 32, dtype=torch.int32, device=dev) if self.fused_h else None
         self._staging = {}
 
     def weight_bytes(self):
@@ -81,20 +83,32 @@ class DenseLayer:
         ]
         return [([s for s, _ in call], [g for _, g in call]) for call in plan]
 
+    def _next_weights(self, i):
+        """Weight tensors of the call after call i (the next layer's q|k|v after down)."""
+        order = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))
+        if i + 1 < len(order):
+            return [self.w[n] for n in order[i + 1]]
+        return [self.next_layer.w[n] for n in order[0]] if self.next_layer is not None else None
+
     def forward(self, x, out, calls=None):
         for i, (segs, gathers) in enumerate(calls or self.calls(x, out)):
-            if self.fused_h and i >= 2:
-                if i == 2:
-                    self.be.quant_gemv_ex(segs, 1, next_act=self.act_f, counters=self.h_counters)
-                else:
-                    self.be.quant_gemv_ex(segs, 1, prequantized=True)
+            if self.fused_h:
+                # one launch per call: q|k|v and o quantize in the GEMV's prologue, gate|up emits down's
+                # quantized activation; every launch pulls the head of the next call's weights into L2
+                self.be.quant_gemv_ex(segs, 1, prequantized=(i == 3), next_act=self.act_f if i == 2 else None,
+                                      prefetch=self._next_weights(i))
                 continue
-            if self.arena:
-                self.be.quant_gemv_scatter(segs, self.TB, self._peers)
-                self.be.peer_barrier(self._flags, self.world, self.rank, 0)  # device-numbered: graph-safe
+            if self.arena and self.exchange:
+                if self.TB == 1:
+                    # the launch waits for the peers' rows of the previous call, stores its own rows on
+                    # every GPU and signals: no barrier kernel between two calls
+                    self.be.quant_gemv_ex(segs, 1, peers=self._peers, sync=self._sync, wait=True, signal=True)
+                else:
+                    self.be.quant_gemv_scatter(segs, self.TB, self._peers)
+                    self.be.peer_barrier(self._flags, self.world, self.rank, 0)  # device-numbered: graph-safe
                 continue
             self.be.quant_gemv(segs, self.TB)
-            if self.world > 1:
+            if self.world > 1 and self.exchange:
                 for buf, n, col0 in gathers:
                     key = (n, self.TB)
                     if self.TB > 1 and key not in self._staging:
@@ -106,8 +120,8 @@ class DenseLayer:
     def launches_per_step(self):
         # single token on one GPU: q|k|v, o and gate|up quantize in the GEMV's prologue and gate|up
         # also emits down's quantized activation: one launch per call; otherwise a quantizer + GEMV per call
-        if self.arena is not None:  # GEMV with peer stores (+ quantizer where it is a kernel of its own) + flag barrier
-            return 9 if self.TB == 1 else 12
+        if self.arena is not None:  # GEMV with peer stores; down keeps its silu(gate)*up quantizer launch
+            return 5 if self.TB == 1 else 12
         if self.fused_h:
             return 4
         return 5 if self.TB == 1 else 8
