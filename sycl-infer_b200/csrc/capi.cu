@@ -133,9 +133,10 @@ int build_call(const b200q_seg * segs, int n_segs, int TB, const int8_t * x8, co
     return B200Q_OK;
 }
 
-// Kernel choice.  One token: the pinned-activation streaming kernel (gemv_pinned.cu).  Two to
-// four tokens: the streaming kernel with one shared-memory activation pack per token.  More
-// tokens (or packs that do not fit): the tcgen05 kernel.  The warp-per-row kernel takes what is left.
+// Kernel choice.  One token: the pinned-activation streaming kernel (gemv_pinned.cu).  Two to 32
+// tokens: the register-fragment int8 MMA kernel (gemm_frag.cu).  More tokens: the tcgen05 kernel
+// (gemm_mma.cu).  What those cannot take (misaligned views, exotic shapes) falls to the streaming
+// kernel with shared-memory packs (2..4 tokens), the tcgen05 kernel, or the warp-per-row kernel.
 #ifdef B200Q_TUNING
 static bool force_rows() {
     static const bool v = [] {
@@ -155,22 +156,36 @@ static int mma_from_env() {
 static bool force_rows() { return false; }
 static int mma_from_env() { return 0; }
 #endif
-// Fewest tokens that take the tensor-core kernel.  Measured on 17408x5120: the streaming kernel
-// needs 14.6 / 23.0 / 27.7 us for two / three / four tokens of Q4_K against a flat 28 us of the
-// tensor-core kernel up to eight tokens; Q6_K 21.8 / 33.0 / 40.5 against 75, Q8_0 20.4 / 29.1 / 30.2 against 50.
-static int mma_from() {
-    const int env = mma_from_env();
-    return env > 0 ? env : 5;
+#ifdef B200Q_TUNING
+static bool frag_off() {
+    static const bool v = [] {
+        const char * e = getenv("B200Q_FRAG");
+        return e && atoi(e) == 0;
+    }();
+    return v;
 }
-bool gemv_takes_pinned(const CallDev & c) {
-    return !force_rows() && c.TB == 1 && pinned_supported(c);
-}
-bool gemv_takes_stream(const CallDev & c) {
-    return !force_rows() && c.TB < mma_from() && stream_supported(c);
+#else
+static bool frag_off() { return false; }
+#endif
+// Measured (us per launch, B200).  17408 x 5120 Q4_K: two tokens stream in 14.0 against 19.4 on
+// fragments; 3..8 tokens 23..29 (streaming / tcgen05) against 19.1; 16 tokens 38.8 (tcgen05) against
+// 29.7; 32 tokens 51.9 against 44.9.  5120 x 17408 Q6_K: 48..49 against 78 up to 8 tokens, 84
+// against 91 at 16, 167 against 384 at 32 (40 row tiles of 128 leave most SMs of the tcgen05 kernel idle).
+bool gemv_takes_frag(const CallDev & c) {
+    if (force_rows() || frag_off() || c.TB < 2 || c.TB > 32) {
+        return false;
+    }
+    if (c.TB == 2 && stream_supported(c)) {
+        return false;
+    }
+    return frag_supported(c);
 }
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     if (gemv_takes_pinned(c)) {
         return launch_gemv_pinned(s, c, nullptr, nullptr);
+    }
+    if (gemv_takes_frag(c)) {
+        return launch_gemm_frag(s, c);
     }
     if (!force_rows() && c.TB >= mma_from()) {
         return launch_gemm_mma(s, c, pdl_secondary);
@@ -402,11 +417,11 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
         return B200Q_EINVAL;
     }
     // Same rule as the GEMV dispatch, so the sums come out of the code that serves such a call:
-    // one token: the half-superblock decoders of the pinned kernel; two to four: the streaming
-    // kernel's quarter units; five and more: the tcgen05 kernel, whose epilogue then stores the
-    // accumulators it read from tensor memory instead of folding them.
+    // one token: the half-superblock decoders of the pinned kernel; 2..32 tokens: the
+    // register-fragment MMA kernel, which then stores its accumulator fragments; more tokens: the
+    // tcgen05 kernel, whose epilogue stores the accumulators it read from tensor memory.
     const uint8_t * wb = static_cast<const uint8_t *>(w);
-    if (TB >= mma_from()) {
+    if (TB >= 2) {
         CallDev c;
         memset(&c, 0, sizeof(c));
         c.K = K;
@@ -425,7 +440,13 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
         c.seg[0].n_rows = n_rows;
         c.seg[0].out_stride = n_rows;
         c.seg[0].row_end = n_rows;
-        B200Q_CUDA_OK(launch_gemm_mma((cudaStream_t)stream, c, false, wd, t));
+        if (gemv_takes_frag(c)) {
+            B200Q_CUDA_OK(launch_gemm_frag((cudaStream_t)stream, c, wd, t));
+        } else if (TB >= mma_from()) {
+            B200Q_CUDA_OK(launch_gemm_mma((cudaStream_t)stream, c, false, wd, t));
+        } else {
+            B200Q_CUDA_OK(launch_unit_dots((cudaStream_t)stream, wb, (int)type, K, n_rows, x8, TB, t, wd));
+        }
     } else if (TB == 1 && K > 65536) { // beyond the streaming kernels: the warp-per-row kernel's decoders
         B200Q_CUDA_OK(launch_block_dots((cudaStream_t)stream, wb, (int)type, K, n_rows, x8, TB, t, wd));
     } else {
@@ -576,6 +597,9 @@ int b200q_device_status(int * status, int clear) {
     int xq = 0;
     B200Q_CUDA_OK(read_xq_status(&xq, clear != 0));
     *status = *status ? *status : xq;
+    int frag = 0;
+    B200Q_CUDA_OK(read_frag_status(&frag, clear != 0));
+    *status = *status ? *status : frag;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }

@@ -26,6 +26,10 @@ cudaError_t ensure_dynamic_smem(const void * func, int bytes);
 cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & call, bool pdl_secondary, int32_t * dump = nullptr,
                             int dump_t = 0);
 cudaError_t read_mma_status(int * status, bool clear);
+// batched decode (2..32 tokens) on register-fragment int8 MMAs (gemm_frag.cu); dump as for launch_gemm_mma
+bool frag_supported(const CallDev & call);
+cudaError_t launch_gemm_frag(cudaStream_t s, const CallDev & call, int32_t * dump = nullptr, int dump_t = 0);
+cudaError_t read_frag_status(int * status, bool clear);
 cudaError_t launch_unit_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8, int TB,
                              int t, int32_t * wd);
 cudaError_t launch_block_dots(cudaStream_t s, const uint8_t * w, int type, int K, int n_rows, const int8_t * x8,

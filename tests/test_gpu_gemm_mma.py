@@ -160,3 +160,49 @@ def test_batch32_layer_shapes_iq4xs_q5k(be, orc, pkg, t, N, K):
     sub = np.concatenate([w[r * rb:(r + 1) * rb] for r in rows])
     ref, ab = orc.gemm(t, sub, K, 96, a), orc.gemm_abs(t, sub, K, 96, a)
     assert float(np.max(np.abs(got[:, rows] - ref) / ab)) <= TOL
+
+
+@pytest.mark.parametrize("t", (12, 13, 14, 8, 23))
+@pytest.mark.parametrize("TB,N,K", [(2, 16, 256), (7, 45, 768), (9, 130, 1024), (16, 700, 512), (17, 300, 2560),
+                                    (32, 129, 768), (4, 5120, 1024), (24, 96, 4352)])
+def test_fragment_kernel_geometry(be, orc, pkg, t, TB, N, K):
+    """2..32 tokens (the register-fragment MMA kernel): one and two token halves, 8- and 16-column
+    warps, row tiles from 16 to 128 rows with 1..8 K slices, ragged rows and tokens, and row pitches
+    that need 1, 2, 4 or 8 alignment classes (Q6_K with 1, 3, 4, 10, 17 superblocks per row).
+    Outputs against the oracle, and the raw int32 sums of one token bit for bit."""
+    w = pkg.synth.make_weight(t, N, K, 1900 + t)
+    a = orc.xq(pkg.synth.make_activation(TB, K, 1901), None, TB)
+    res = pkg.synth.make_activation(TB, N, 1902)
+    ref = orc.gemm(t, w, K, N, a, residual=res.copy(), alpha=0.5)
+    ab = orc.gemm_abs(t, w, K, N, a, alpha=0.5) + np.abs(res)
+    got = _gemm(be, t, w, K, N, a, TB, residual=res, alpha=0.5)
+    assert float(np.max(np.abs(got - ref) / ab)) <= TOL
+    tok = TB - 1
+    assert np.array_equal(_dots(be, t, w, K, N, a, TB, tok), orc.block_dots(t, w, K, N, a, tok))
+
+
+def test_fragment_kernel_mixed_segments(be, orc, pkg):
+    """q|k|v at batch 8: three segments, two weight types (Q4_K rows of pitch 16k, Q6_K rows in
+    two alignment classes), one launch."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()  # noqa: E731
+    K, TB = 5120, 8
+    shapes = [(12, 640), (12, 128), (14, 128)]
+    x = pkg.synth.make_activation(TB, K, 2001)
+    a = orc.xq(x, None, TB)
+    x8, xm, xs = alloc_act(TB, K)
+    dx = dev(x)
+    segs, outs, ws = [], [], []
+    for i, (t, n) in enumerate(shapes):
+        w = pkg.synth.make_weight(t, n, K, 2010 + i)
+        ws.append(w)
+        o = torch.zeros(TB * n, dtype=torch.float32, device="cuda")
+        outs.append(o)
+        segs.append(gemv_seg(w=dev(w), type=t, K=K, n_rows=n, x=dx, x_stride=K, out=o, out_stride=n, x8=x8, xmeta=xm,
+                             xsumq=xs))
+    be.quant_gemv(segs, TB)
+    be.synchronize()
+    assert be.device_status() == 0
+    for (t, n), w, o in zip(shapes, ws, outs):
+        ref, ab = orc.gemm(t, w, K, n, a), orc.gemm_abs(t, w, K, n, a)
+        assert float(np.max(np.abs(o.cpu().numpy().reshape(TB, n) - ref) / ab)) <= TOL
