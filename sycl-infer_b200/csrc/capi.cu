@@ -180,6 +180,17 @@ bool gemv_takes_frag(const CallDev & c) {
     }
     return frag_supported(c);
 }
+// Fewest tokens that take the tensor-core kernel when the fragment kernel does not apply.
+static int mma_from() {
+    const int env = mma_from_env();
+    return env > 0 ? env : 5;
+}
+bool gemv_takes_pinned(const CallDev & c) {
+    return !force_rows() && c.TB == 1 && pinned_supported(c);
+}
+bool gemv_takes_stream(const CallDev & c) {
+    return !force_rows() && c.TB < mma_from() && stream_supported(c);
+}
 cudaError_t launch_gemv(cudaStream_t s, const CallDev & c, bool pdl_secondary) {
     if (gemv_takes_pinned(c)) {
         return launch_gemv_pinned(s, c, nullptr, nullptr);
