@@ -216,8 +216,6 @@ def make_layers(ctx, mix, TB, L, rank, world, arena=None, seed0=100):
     torch, pkg = ctx.torch, ctx.pkg
     layers = [DenseLayer(ctx.be, mix, seed=seed0 + i, TB=TB, rank=rank, world=world, arena=arena,
                          group=None) for i in range(L)]
-    for i, ly in enumerate(layers):
-        ly.next_layer = layers[(i + 1) % L]  # the step that follows replays the next weight set
     hidden, q_dim = layers[0].hidden, layers[0].q_dim
     # a step's two inputs (hidden state and attention output) share one device buffer per weight
     # set, so the end-to-end loop moves them with ONE host-to-device copy

@@ -135,27 +135,12 @@ typedef struct b200q_next_act {
     int32_t * xsumq;  /* [n_rows/32][2] */
 } b200q_next_act;
 
-/* Weights of the call that will run NEXT in the stream (a hint; results never depend on it).
- * A decode step is a chain of dependent launches; while one launch drains its last tiles and
- * the next one waits for its activation, HBM would idle.  With this hint every CTA, once it
- * has requested its last own weights, asks the memory system to bring the first part of the
- * next call's weights into L2 (cp.async.bulk.prefetch.L2), so the next launch starts on warm
- * L2 lines.  The reference has no counterpart (its GPU kernels rely on the hardware prefetcher
- * of in-order queues); the plan that lists the calls of a layer (seg_plan,
- * src/engine/engine_types.h:11-133) is where an engine takes the pointers from. */
-typedef struct b200q_weights_hint {
-    const void * w[B200Q_MAX_SEGS]; /* 16-byte aligned */
-    size_t bytes[B200Q_MAX_SEGS];
-    int32_t n;
-} b200q_weights_hint;
-
 struct b200q_peers;
 typedef struct b200q_call_opts {
     uint32_t flags;                  /* B200Q_OPT_* */
     const struct b200q_peers * peers; /* host; NULL = outputs stay on this GPU (see b200q_quant_gemv_scatter) */
     const b200q_next_act * next;     /* host; NULL = off */
     const b200q_peer_sync * sync;    /* host; needed by B200Q_OPT_WAIT_PEERS / B200Q_OPT_SIGNAL_PEERS */
-    const b200q_weights_hint * prefetch; /* host; NULL = none */
 } b200q_call_opts;
 
 /* b200q_quant_gemv with options: the general form of the fused decode launch

@@ -124,14 +124,13 @@ class cuda_backend:
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
     def quant_gemv_ex(self, segs, TB=1, prequantized=False, peers=None, next_act=None, sync=None, wait=False,
-                      signal=False, prefetch=None):
+                      signal=False):
         """quant_gemv with options: `prequantized` skips the quantizer (the segments' scratch holds
         the activation already); `peers` scatters the outputs; `next_act` = (x8, xmeta, xsumq) makes
         the call emit its output (gate|up: silu(gate)*up) quantized as the following call's activation;
         `sync` = (flag pointer array, world, rank) with `wait` / `signal` folds the cross-GPU flag
-        exchange of a row-sharded call into the launch; `prefetch` = weight tensors of the call
-        that follows (their head is pulled into L2 while this launch drains)."""
-        from .capi import CallOpts, NextAct, PeerSync, WeightsHint, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
+        exchange of a row-sharded call into the launch."""
+        from .capi import CallOpts, NextAct, PeerSync, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
         arr, n = _pack(segs)
         s0 = segs[0]
         opts = CallOpts()
@@ -144,14 +143,6 @@ class cuda_backend:
             na = NextAct(_ptr(next_act[0]), _ptr(next_act[1]), _ptr(next_act[2]))
             keep.append(na)
             opts.next = C.pointer(na)
-        if prefetch:
-            wh = WeightsHint()
-            wh.n = len(prefetch)
-            for i, w in enumerate(prefetch):
-                wh.w[i] = _ptr(w)
-                wh.bytes[i] = int(w.numel())
-            keep.append(wh)
-            opts.prefetch = C.pointer(wh)
         if sync is not None:
             ps = PeerSync(C.cast(sync[0], C.POINTER(C.c_void_p)), sync[1], sync[2])
             keep.append(ps)

@@ -35,15 +35,10 @@ class PeerSync(C.Structure):
     _fields_ = [("flags", C.POINTER(_vp)), ("world", C.c_int32), ("rank", C.c_int32)]
 
 
-class WeightsHint(C.Structure):
-    """struct b200q_weights_hint."""
-    _fields_ = [("w", _vp * 8), ("bytes", C.c_size_t * 8), ("n", C.c_int32)]
-
-
 class CallOpts(C.Structure):
     """struct b200q_call_opts."""
     _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct)),
-                ("sync", C.POINTER(PeerSync)), ("prefetch", C.POINTER(WeightsHint))]
+                ("sync", C.POINTER(PeerSync))]
 
 
 OPT_PREQUANTIZED, OPT_WAIT_PEERS, OPT_SIGNAL_PEERS = 1, 2, 4

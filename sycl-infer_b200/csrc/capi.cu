@@ -295,24 +295,6 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             return B200Q_EUNSUPPORTED;
         }
     }
-    WeightsHint hint;
-    memset(&hint, 0, sizeof(hint));
-    if (opts && opts->prefetch) {
-        const b200q_weights_hint & h = *opts->prefetch;
-        if (h.n < 0 || h.n > B200Q_MAX_SEGS) {
-            set_error("%s: prefetch hint holds 0..%d weight ranges (got %d)", who, B200Q_MAX_SEGS, h.n);
-            return B200Q_EINVAL;
-        }
-        for (int i = 0; i < h.n; i++) {
-            if (!h.w[i] || !aligned(h.w[i], 16)) {
-                set_error("%s: prefetch hint range %d is null or not 16-byte aligned", who, i);
-                return B200Q_EINVAL;
-            }
-            hint.w[i] = static_cast<const uint8_t *>(h.w[i]);
-            hint.bytes[i] = h.bytes[i];
-        }
-        hint.n = h.n; // only the single-token kernel acts on it
-    }
     if (gemv_takes_pinned(c)) {
         const bool inside = !prequant && pinned_quantizes(c, s0.x, s0.act_up);
         if (!prequant && !inside) { // a quantizer launch of its own: it is the one that waits for the peers
@@ -321,7 +303,7 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             sync.wait = 0;
         }
         B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.x8 ? &next : nullptr,
-                                         (sync.wait || sync.signal) ? &sync : nullptr, hint.n ? &hint : nullptr));
+                                         (sync.wait || sync.signal) ? &sync : nullptr));
         return B200Q_OK;
     }
     if (!prequant) {

@@ -133,14 +133,6 @@ struct NextAct {
     int32_t * xsumq;
 };
 
-// weights of the call that follows, to be pulled into L2 (b200q_weights_hint)
-struct WeightsHint {
-    const uint8_t * w[B200Q_MAX_SEGS];
-    unsigned long long bytes[B200Q_MAX_SEGS];
-    int32_t n;
-    uint32_t per_cta; // bytes each CTA asks for
-};
-
 // cross-GPU flag exchange folded into a GEMV launch (b200q_peer_sync)
 struct PeerSync {
     uint32_t * flag[B200Q_MAX_PEERS + 1]; // rank p's flag array as mapped on this GPU

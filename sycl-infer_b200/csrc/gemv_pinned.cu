@@ -61,7 +61,6 @@ struct PinArgs {
     const float * xq_x; // when set, every CTA quantizes this fp32 activation itself
     NextAct next;       // the call's output, quantized, as the following call's activation (x8 == nullptr: off)
     PeerSync sync;      // row-sharded calls: wait for / signal the peers inside this launch
-    WeightsHint hint;   // the next call's weights, for the L2 prefetch at the end of the producer's work
     int32_t W, R, U, seg, P, Ppad; // P = U / seg partials per row, rows Ppad words apart
     // paired mode (next.cnt != nullptr): a step is H gate rows and the H up rows of the same
     // indices; the up rows sit half_off bytes into the stage
@@ -451,32 +450,6 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
                 }
             }
         }
-        if (alive && a.hint.n > 0) {
-            // This CTA's own weights are all requested: warm L2 with the part of the next call's
-            // weight stream that the same-numbered CTA of the next launch will ask for first.
-            unsigned long long total = 0;
-            for (int i = 0; i < a.hint.n; i++) {
-                total += a.hint.bytes[i];
-            }
-            unsigned long long off = (total / gridDim.x * blockIdx.x) & ~15ull, left = a.hint.per_cta;
-            for (int i = 0; i < a.hint.n && left > 0; i++) {
-                if (off >= a.hint.bytes[i]) {
-                    off -= a.hint.bytes[i];
-                    continue;
-                }
-                unsigned long long n = a.hint.bytes[i] - off;
-                n = n < left ? n : left;
-                const uint8_t * p = a.hint.w[i] + off;
-                for (unsigned long long done = 0; done < n; done += 32768) {
-                    const uint32_t sz = (uint32_t)((n - done < 32768 ? n - done : 32768) & ~15ull);
-                    if (sz) {
-                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + done), "r"(sz) : "memory");
-                    }
-                }
-                left -= n;
-                off = 0;
-            }
-        }
         if (!alive) { // leaving early: wait (bounded) until the copies still in flight have landed
             for (int s = 0; s < S && s < issued; s++) {
                 const int last = ((issued - 1 - s) / S) * S + s; // last step that filled stage s
@@ -813,7 +786,7 @@ bool pinned_quantizes(const CallDev & c, const float * x, const float * act_up) 
 }
 
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next,
-                               const PeerSync * sync, const WeightsHint * hint) {
+                               const PeerSync * sync) {
     PinArgs a;
     a.c = c;
     a.xq_x = xq_x;
@@ -821,17 +794,6 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     memset(&a.sync, 0, sizeof(a.sync));
     if (sync) {
         a.sync = *sync;
-    }
-    memset(&a.hint, 0, sizeof(a.hint));
-    if (hint && hint->n > 0) {
-        a.hint = *hint;
-        unsigned long long total = 0;
-        for (int i = 0; i < hint->n; i++) {
-            total += hint->bytes[i];
-        }
-        // what HBM delivers while a launch drains and the next one gets going (about 6 us), shared out
-        const unsigned long long share = total / kSMs, cap = 288 * 1024;
-        a.hint.per_cta = (uint32_t)((share < cap ? share : cap) & ~15ull);
     }
     if (!pin_plan(c, a.next.x8 ? (c.n_segs == 2 ? 2 : 1) : 0, xq_x != nullptr, a)) {
         return cudaErrorInvalidConfiguration;

@@ -18,7 +18,7 @@ bool pinned_supported(const CallDev & call);
 bool pinned_next_supported(const CallDev & call); // a call that also emits the next call's activation
 bool pinned_quantizes(const CallDev & call, const float * x, const float * act_up);
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next,
-                               const PeerSync * sync = nullptr, const WeightsHint * hint = nullptr);
+                               const PeerSync * sync = nullptr);
 cudaError_t read_pin_status(int * status, bool clear);
 // cudaFuncAttributeMaxDynamicSharedMemorySize is per device: set once per (kernel, device)
 cudaError_t ensure_dynamic_smem(const void * func, int bytes);

@@ -42,7 +42,6 @@ class DenseLayer:
         self.o_out = new(TB, hidden)
         self.gu = new(TB, 2 * n_ff)
         self.out = new(TB, hidden)  # the layer's output when the caller passes none
-        self.next_layer = None  # the layer whose q|k|v follows this layer's down call (weights prefetch hint)
         self.exchange = True  # False: leave the cross-GPU exchange out (timing of the compute alone; wrong results)
         if self.arena:
             self._peers, self._flags = self.arena.peers(), self.arena.flag_ptrs()
@@ -83,20 +82,12 @@ class DenseLayer:
         ]
         return [([s for s, _ in call], [g for _, g in call]) for call in plan]
 
-    def _next_weights(self, i):
-        """Weight tensors of the call after call i (the next layer's q|k|v after down)."""
-        order = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))
-        if i + 1 < len(order):
-            return [self.w[n] for n in order[i + 1]]
-        return [self.next_layer.w[n] for n in order[0]] if self.next_layer is not None else None
-
     def forward(self, x, out, calls=None):
         for i, (segs, gathers) in enumerate(calls or self.calls(x, out)):
             if self.fused_h:
                 # one launch per call: q|k|v and o quantize in the GEMV's prologue, gate|up emits down's
-                # quantized activation; every launch pulls the head of the next call's weights into L2
-                self.be.quant_gemv_ex(segs, 1, prequantized=(i == 3), next_act=self.act_f if i == 2 else None,
-                                      prefetch=self._next_weights(i))
+                # quantized activation
+                self.be.quant_gemv_ex(segs, 1, prequantized=(i == 3), next_act=self.act_f if i == 2 else None)
                 continue
             if self.arena and self.exchange:
                 if self.TB == 1:
