@@ -276,6 +276,18 @@ struct PinBars {
     uint32_t full, empty, red_full, red_empty;
 };
 
+// The hot loop polls two mbarriers per step; nearly always the first try succeeds, and the
+// bounded spin (clock reads, status word) is only entered when it does not.
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok ? true : mbar_wait(bar, parity, &g_pin_status);
+}
+
 // Rows [lo, hi) of weight w0 - and, in paired mode, the same rows of w1 in the slots from H on.
 template <int TYPE>
 __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_t * w0, const uint8_t * w1, int lo,
@@ -290,28 +302,23 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_
     const uint32_t wbase = (uint32_t)(reinterpret_cast<uintptr_t>(part ? w1 : w0) & 15);
     const uint32_t my_off = (uint32_t)(part * a.half_off) + (uint32_t)sl * row_bytes + (uint32_t)(unit >> 1) * SB;
     const int seg = a.seg;
-    const uint32_t red_off = (uint32_t)(slot * a.Ppad + unit / seg) * 4u;
-    const bool writer = (lane & (seg - 1)) == 0;
+    const bool writer = (lane & (seg - 1)) == 0 && mine;
     const int h = unit & 1;
-    for (int row0 = lo; row0 < hi; row0 += H) {
-#ifdef B200Q_TUNING
-        if (threadIdx.x == 0 && row0 == lo) {
-            PIN_STAMP(6);
-        }
-#endif
-        if (!mbar_wait(bars.full + 8 * pos.stage, pos.phase, &g_pin_status)) {
+    // everything that moves with the ring is kept as an address and stepped, not recomputed
+    const uint32_t stage_bytes = (uint32_t)a.stage_bytes, red_bytes = (uint32_t)a.red_bytes;
+    uint32_t st_addr = tiles + (uint32_t)pos.stage * stage_bytes + my_off;
+    uint32_t rd_addr = red + (uint32_t)pos.rb * red_bytes + (uint32_t)(slot * a.Ppad + unit / seg) * 4u;
+    // where a row's bytes start inside its 16-byte line: only the low four address bits matter
+    uint32_t mis = (wbase + (uint32_t)lo * row_bytes) & 15u;
+    const uint32_t mis_step = ((uint32_t)H * row_bytes) & 15u;
+    for (int left = hi - lo; left > 0; left -= H) {
+        if (!mbar_wait_fast(bars.full + 8 * pos.stage, pos.phase)) {
             return false;
         }
-        const bool active = mine && sl < hi - row0;
-#ifdef B200Q_TUNING
-        if (threadIdx.x == 0 && row0 == lo) {
-            PIN_STAMP(3);
-        }
-#endif
+        const bool active = sl < left;
         float v = 0.f;
-        if (active) {
-            const uint32_t mis = (wbase + (uint32_t)row0 * row_bytes) & 15u; // only the low four bits matter
-            v = pinned_term<TYPE>(tiles + (uint32_t)(pos.stage * a.stage_bytes) + mis + my_off, h, pin);
+        if (mine && active) {
+            v = pinned_term<TYPE>(st_addr + mis, h, pin);
         }
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { // all lanes of a segment belong to the same row slot
@@ -319,22 +326,35 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_
                 v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
             }
         }
-        if (!mbar_wait(bars.red_empty + 8 * pos.rb, pos.rphase ^ 1, &g_pin_status)) {
+        if (!mbar_wait_fast(bars.red_empty + 8 * pos.rb, pos.rphase ^ 1)) {
             return false;
         }
         if (writer && active) {
-            sts32(red + (uint32_t)(pos.rb * a.red_bytes) + red_off, __float_as_uint(v));
+            sts32(rd_addr, __float_as_uint(v));
         }
         __syncwarp();
         if (lane == 0) {
             mbar_arrive(bars.red_full + 8 * pos.rb);
             mbar_arrive(bars.empty + 8 * pos.stage);
         }
-        pos.advance(S);
+        mis = (mis + mis_step) & 15u;
+        if (++pos.stage == S) {
+            pos.stage = 0;
+            pos.phase ^= 1;
+            st_addr -= (uint32_t)(S - 1) * stage_bytes;
+        } else {
+            st_addr += stage_bytes;
+        }
+        if (++pos.rb == kRedBufs) {
+            pos.rb = 0;
+            pos.rphase ^= 1;
+            rd_addr -= (kRedBufs - 1) * red_bytes;
+        } else {
+            rd_addr += red_bytes;
+        }
     }
     return true;
 }
-
 template <int TYPE>
 __device__ __forceinline__ bool pin_consume_call(const PinArgs & a, int si, uint32_t cost_lo, uint32_t cost_hi,
                                                  uint32_t tiles, uint32_t red, const PinBars & bars, const ActPin & pin,
