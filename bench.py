@@ -372,7 +372,7 @@ def cell_layer_split(ctx, mix, TB, n_layers=8, steps=10):
             "us": us, "us_per_layer": us / n_layers, "bytes": nbytes, "GB/s": gbs,
             "frac_of_P_x_measured_hbm": gbs / (world * ctx.peaks["hbm_gbs"]),
             "tok_s_64_layers": TB * 1e6 / (us / n_layers * LAYERS_PER_TOKEN), "launch": "host launches",
-            "note": "one batch in flight: per-token latency form; throughput with P batches pipelined is up to P x"}
+            "note": "consecutive steps overlap across ranks (rank 0 starts step s+1 while rank 1 runs step s): a pipelined figure, not a per-token latency"}
 
 
 def safe(cells, fn, *a, **kw):

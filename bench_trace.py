@@ -1,0 +1,75 @@
+"""Timeline of the single-token GEMV kernel inside a dense layer step.
+
+Builds a variant of the library with -DB200Q_TUNING (kernels then stamp %globaltimer at their
+milestones into a buffer named by B200Q_TRACE_PTR; the product build has none of this), replays
+CUDA graphs of the layer's four launches and prints, per launch, when its CTAs entered, passed
+griddepcontrol.wait, had their activation in registers, got their first tile, finished consuming,
+and stored their last output - microseconds from the first CTA's entry, mean over CTAs.
+
+    python bench_trace.py [fused|plain]      (plain: separate quantizer launch for down)
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+spec = importlib.util.spec_from_file_location("b200q_build", os.path.join(ROOT, "sycl-infer_b200", "build.py"))
+build = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(build)
+os.environ["B200Q_LIB"] = build.build_native(extra=["-DB200Q_TUNING"],
+                                             out=os.path.join(ROOT, "sycl-infer_b200", "libb200q_tuning.so"))
+import torch  # noqa: E402
+
+trace = torch.zeros(64 * 160 * 8, dtype=torch.int64, device="cuda")
+os.environ["B200Q_TRACE_PTR"] = str(trace.data_ptr())
+import __graft_entry__ as graft  # noqa: E402
+
+pkg = graft.load_package()
+from sycl_infer_b200.layer import DenseLayer  # noqa: E402
+
+be = pkg.make_cuda_backend(0)
+L = 4
+layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1) for i in range(L)]
+xs = [torch.from_numpy(pkg.synth.make_activation(1, 5120, 10 + i)).cuda() for i in range(L)]
+out = torch.zeros(1, 5120, device="cuda")
+mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+if mode == "plain":
+    for ly in layers:
+        ly.fused_h = False
+st = torch.cuda.Stream()
+be._stream = st
+with torch.cuda.stream(st):
+    for i in range(L):
+        layers[i].forward(xs[i], out)
+    st.synchronize()
+    graphs = []
+    for i in range(L):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            layers[i].forward(xs[i], out)
+        graphs.append(gr)
+    st.synchronize()
+    trace.zero_()
+    for i in range(8):
+        graphs[i % L].replay()
+    st.synchronize()
+t = trace.cpu().numpy().reshape(64, 160, 8).astype(np.float64)
+idx = [i for i in range(64) if (t[i, :, 0] > 0).any()]  # a graph's kernel nodes keep the launch index of their capture
+names = ["entry", "wait_done", "act_ready", "first_tile", "cons_done", "epi_done", "pre_wait", "act_landed"]
+t0 = min(t[i, :, 0][t[i, :, 0] > 0].min() for i in idx)
+rows = []
+for i in idx:
+    n = int((t[i, :, 0] > 0).sum())
+    rows.append((t[i, :n, 0].min(), i, n, t[i, :n]))
+rows.sort(key=lambda r: r[0])
+print(f"mode={mode}: last replay of every captured launch; microseconds from the earliest entry (mean over CTAs)")
+for _, i, n, c in rows:
+    cells = []
+    for k, nm in enumerate(names):
+        col = c[:, k][c[:, k] > 0]
+        cells.append(f"{nm}={((col.mean() - t0) / 1e3) if col.size else float('nan'):7.2f}")
+    last = c[:, 5][c[:, 5] > 0]
+    print(f"launch {i:2d} ctas={n:3d} " + "  ".join(cells) + f"  last_store={((last.max() - t0) / 1e3) if last.size else float('nan'):7.2f}")

@@ -34,19 +34,22 @@ def _digest():
     return h.hexdigest()
 
 
-def build_native(force=False, verbose=False, extra=()):
-    """Compile every .cu under csrc/ into libb200q.so; skipped when sources are unchanged."""
-    dig = _digest()
-    if not force and os.path.exists(LIB) and os.path.exists(STAMP) and open(STAMP).read() == dig:
-        return LIB
-    os.makedirs(os.path.dirname(STAMP), exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", LIB, *sources()]
+def build_native(force=False, verbose=False, extra=(), out=None):
+    """Compile every .cu under csrc/ into libb200q.so; skipped when sources are unchanged.
+    `out` builds a variant (e.g. with -DB200Q_TUNING in `extra`) under another name."""
+    lib = out or LIB
+    stamp = STAMP if out is None else os.path.join(HERE, "build", os.path.basename(out) + ".stamp")
+    dig = _digest() + " ".join(extra)
+    if not force and os.path.exists(lib) and os.path.exists(stamp) and open(stamp).read() == dig:
+        return lib
+    os.makedirs(os.path.dirname(stamp), exist_ok=True)
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", lib, *sources()]
     if verbose:
         print(" ".join(cmd))
     subprocess.run(cmd, check=True)
-    with open(STAMP, "w") as fh:
+    with open(stamp, "w") as fh:
         fh.write(dig)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":

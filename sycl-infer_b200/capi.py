@@ -7,7 +7,9 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200q.so")
+# B200Q_LIB selects another build of the same library (bench_trace.py loads one compiled with
+# -DB200Q_TUNING, whose kernels record timeline stamps); the default is the in-tree product build.
+LIB_PATH = os.environ.get("B200Q_LIB") or os.path.join(HERE, "libb200q.so")
 
 _vp = C.c_void_p
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT = 0, 1, 2, 3, 4
