@@ -6,7 +6,14 @@ CUDA graphs of the layer's four launches and prints, per launch, when its CTAs e
 griddepcontrol.wait, had their activation in registers, got their first tile, finished consuming,
 and stored their last output - microseconds from the first CTA's entry, mean over CTAs.
 
-    python bench_trace.py [fused|plain]      (plain: separate quantizer launch for down)
+    python bench_trace.py [chain|fused|plain|chain1]
+        chain:  q|k|v, then o -> gate|up -> down as one launch (the default of a one-GPU layer)
+        fused:  four launches, the quantizers inside them
+        plain:  separate quantizer launch for down
+        chain1: as chain, with q|k|v through the chain kernel too (one kernel image in the stream)
+
+For a chained launch every call has its own line: "entry" is when the CTA's consumers reached the
+call, "wait_done" when they saw every CTA's rows of the previous call stored.
 """
 import importlib.util
 import os
@@ -35,9 +42,12 @@ L = 4
 layers = [DenseLayer(be, "Q4_K_M", seed=100 + i, TB=1) for i in range(L)]
 xs = [torch.from_numpy(pkg.synth.make_activation(1, 5120, 10 + i)).cuda() for i in range(L)]
 out = torch.zeros(1, 5120, device="cuda")
-mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
-if mode == "plain":
-    for ly in layers:
+mode = sys.argv[1] if len(sys.argv) > 1 else "chain"
+if mode == "chain1":
+    os.environ["B200Q_CHAIN1"] = "1"
+for ly in layers:
+    ly.chain = mode in ("chain", "chain1")
+    if mode == "plain":
         ly.fused_h = False
 st = torch.cuda.Stream()
 be._stream = st
@@ -53,9 +63,13 @@ with torch.cuda.stream(st):
         graphs.append(gr)
     st.synchronize()
     trace.zero_()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
     for i in range(8):
         graphs[i % L].replay()
+    e1.record(st)
     st.synchronize()
+    print(f"{e0.elapsed_time(e1) / 8 * 1e3:.2f} us per layer step (tuning build, stamps on)")
 t = trace.cpu().numpy().reshape(64, 160, 8).astype(np.float64)
 idx = [i for i in range(64) if (t[i, :, 0] > 0).any()]  # a graph's kernel nodes keep the launch index of their capture
 names = ["entry", "wait_done", "act_ready", "first_tile", "cons_done", "epi_done", "pre_wait", "act_landed"]

@@ -149,6 +149,28 @@ typedef struct b200q_call_opts {
 int b200q_quant_gemv_ex(void * stream, const b200q_seg * segs /*host*/, int n_segs, int TB, int8_t * x8, float * xmeta,
                         int32_t * xsumq, const b200q_call_opts * opts /*host, may be NULL*/);
 
+/* Several single-token calls, each consuming what the one before it produced, as ONE launch where
+ * the kernels allow it: the consecutive calls of a forward plan that the reference replays back to
+ * back (seg_plan, src/engine/engine_types.h:11-60; record_forward, src/engine/engine.h:1269), e.g.
+ * o -> gate|up -> down.  The results are those of b200q_quant_gemv_ex(stream, segs, n_segs, 1, x8,
+ * xmeta, xsumq, {flags, next}) called for each entry in order: call i+1 starts on a CTA only after
+ * every CTA has stored its rows of call i.  Between two calls the launch neither drains nor
+ * restarts: the weights of call i+1 stream into shared memory while call i finishes.  When the
+ * calls do not fit that form (more than four, a shape the single-token kernel does not take, a
+ * quantizer that needs its own launch, too little shared memory for one common ring) they run as
+ * separate launches, with the same results.  Chain launches of one device must not overlap each
+ * other (one stream, or ordered streams): they share one device-side counter. */
+typedef struct b200q_chain_call {
+    const b200q_seg * segs;      /* host */
+    int32_t n_segs;
+    int8_t * x8;                 /* device: this call's quantized activation (scratch, or input with PREQUANTIZED) */
+    float * xmeta;
+    int32_t * xsumq;
+    uint32_t flags;              /* B200Q_OPT_PREQUANTIZED or 0 */
+    const b200q_next_act * next; /* host; NULL = off */
+} b200q_chain_call;
+int b200q_quant_gemv_chain(void * stream, const b200q_chain_call * calls /*host*/, int n_calls);
+
 /* ---- row-sharded calls across the GPUs of one box (new relative to the reference, which has no
  * tensor parallelism: its only multi-device mode is the layer split, src/engine/engine.cpp:3505-3570).
  * Every rank owns a contiguous slice of each weight's rows and all ranks need the whole output.

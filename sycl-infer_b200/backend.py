@@ -150,6 +150,25 @@ class cuda_backend:
         self.lib.check(self.lib.quant_gemv_ex(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq),
                                               C.byref(opts)))
 
+    def quant_gemv_chain(self, calls):
+        """Several dependent one-token calls as one launch where the kernels allow it (same results
+        as quant_gemv_ex call by call).  `calls`: a list of (segs, prequantized, next_act)."""
+        from .capi import ChainCall, NextAct, OPT_PREQUANTIZED
+        arr = (ChainCall * len(calls))()
+        keep = []
+        for cc, (segs, prequantized, next_act) in zip(arr, calls):
+            sa, n = _pack(segs)
+            keep.append(sa)
+            s0 = segs[0]
+            cc.segs, cc.n_segs = sa, n
+            cc.x8, cc.xmeta, cc.xsumq = _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)
+            cc.flags = OPT_PREQUANTIZED if prequantized else 0
+            if next_act is not None:
+                na = NextAct(_ptr(next_act[0]), _ptr(next_act[1]), _ptr(next_act[2]))
+                keep.append(na)
+                cc.next = C.pointer(na)
+        self.lib.check(self.lib.quant_gemv_chain(self._s(), arr, len(calls)))
+
     def quant_gemv_scatter(self, segs, TB, peers):
         """quant_gemv whose outputs are also stored into the peers' copies of the output arena."""
         arr, n = _pack(segs)

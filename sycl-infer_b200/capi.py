@@ -53,6 +53,12 @@ class Seg(C.Structure):
                 ("residual", _vp), ("alpha", C.c_float), ("x8", _vp), ("xmeta", _vp), ("xsumq", _vp)]
 
 
+class ChainCall(C.Structure):
+    """struct b200q_chain_call."""
+    _fields_ = [("segs", C.POINTER(Seg)), ("n_segs", C.c_int32), ("x8", _vp), ("xmeta", _vp), ("xsumq", _vp),
+                ("flags", C.c_uint32), ("next", C.POINTER(NextAct))]
+
+
 _SIGS = {
     "b200q_last_error": (C.c_char_p, []),
     "b200q_version": (C.c_int, []),
@@ -62,6 +68,7 @@ _SIGS = {
     "b200q_i8_gemm": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int]),
     "b200q_quant_gemv": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp]),
     "b200q_quant_gemv_ex": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(CallOpts)]),
+    "b200q_quant_gemv_chain": (C.c_int, [_vp, C.POINTER(ChainCall), C.c_int]),
     "b200q_quant_gemv_scatter": (C.c_int, [_vp, C.POINTER(Seg), C.c_int, C.c_int, _vp, _vp, _vp, C.POINTER(Peers)]),
     "b200q_peer_barrier": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, C.c_uint32]),
     "b200q_moe_route": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),

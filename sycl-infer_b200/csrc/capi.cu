@@ -373,6 +373,61 @@ int b200q_quant_gemv_ex(void * stream, const b200q_seg * segs, int n_segs, int T
     return quant_gemv_call("b200q_quant_gemv_ex", (cudaStream_t)stream, segs, n_segs, TB, x8, xmeta, xsumq, opts);
 }
 
+int b200q_quant_gemv_chain(void * stream, const b200q_chain_call * calls, int n_calls) {
+    if (!calls || n_calls < 1) {
+        set_error("b200q_quant_gemv_chain: calls must be non-null, n_calls >= 1");
+        return B200Q_EINVAL;
+    }
+    // One launch when every call is one the single-token kernel takes as it stands; the
+    // call-by-call path below validates and reports errors either way.
+    bool fused = n_calls >= 2 && n_calls <= 4;
+    CallDev cd[4];
+    const float * xq_x[4];
+    NextAct next[4];
+    for (int i = 0; i < n_calls && fused; i++) {
+        const b200q_chain_call & cc = calls[i];
+        const bool prequant = (cc.flags & B200Q_OPT_PREQUANTIZED) != 0;
+        fused = cc.segs && cc.x8 && cc.xmeta && cc.xsumq && !(cc.flags & ~B200Q_OPT_PREQUANTIZED) &&
+                build_call(cc.segs, cc.n_segs, 1, cc.x8, cc.xmeta, cc.xsumq, cd[i]) == B200Q_OK && gemv_takes_pinned(cd[i]);
+        if (!fused) {
+            break;
+        }
+        xq_x[i] = nullptr;
+        if (!prequant) {
+            const b200q_seg & s0 = cc.segs[0];
+            fused = s0.x && s0.x_stride >= s0.K && pinned_quantizes(cd[i], s0.x, s0.act_up);
+            for (int j = 1; j < cc.n_segs && fused; j++) {
+                fused = cc.segs[j].x == s0.x && cc.segs[j].act_up == s0.act_up && cc.segs[j].x_stride == s0.x_stride;
+            }
+            xq_x[i] = s0.x;
+        }
+        next[i] = NextAct{nullptr, nullptr, nullptr};
+        if (fused && cc.next) {
+            const b200q_next_act & n = *cc.next;
+            fused = n.x8 && n.xmeta && n.xsumq && aligned(n.xmeta, 8) && aligned(n.xsumq, 8) && cc.n_segs <= 2 &&
+                    (cc.n_segs == 1 || cc.segs[0].n_rows == cc.segs[1].n_rows) && !(cc.segs[0].n_rows & 31) &&
+                    pinned_next_supported(cd[i]);
+            next[i] = NextAct{n.x8, n.xmeta, n.xsumq};
+        }
+    }
+    if (fused && chain_supported(cd, xq_x, next, n_calls)) {
+        B200Q_CUDA_OK(launch_gemv_chain((cudaStream_t)stream, cd, xq_x, next, n_calls));
+        return B200Q_OK;
+    }
+    for (int i = 0; i < n_calls; i++) {
+        const b200q_chain_call & cc = calls[i];
+        b200q_call_opts opts = {};
+        opts.flags = cc.flags;
+        opts.next = cc.next;
+        const int rc = quant_gemv_call("b200q_quant_gemv_chain", (cudaStream_t)stream, cc.segs, cc.n_segs, 1, cc.x8,
+                                       cc.xmeta, cc.xsumq, &opts);
+        if (rc != B200Q_OK) {
+            return rc;
+        }
+    }
+    return B200Q_OK;
+}
+
 int b200q_quant_gemv_scatter(void * stream, const b200q_seg * segs, int n_segs, int TB, int8_t * x8, float * xmeta,
                              int32_t * xsumq, const b200q_peers * peers) {
     if (!peers) {

@@ -83,6 +83,13 @@ __device__ __forceinline__ void pin_stamp(const PinArgs & a, int ev) {
     }
 }
 #define PIN_STAMP(ev) pin_stamp(a, ev)
+static int g_trace_launches = 0; // every call, chained or not, gets its own slot of the trace
+static void trace_slot(PinArgs & a, bool count) {
+    const char * tp = getenv("B200Q_TRACE_PTR");
+    a.trace = tp ? reinterpret_cast<unsigned long long *>(strtoull(tp, nullptr, 0)) : nullptr;
+    a.launch_idx = g_trace_launches;
+    g_trace_launches += count ? 1 : 0;
+}
 #else
 #define PIN_STAMP(ev)
 #endif
@@ -290,12 +297,13 @@ __device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity) {
 
 // Rows [lo, hi) of weight w0 - and, in paired mode, the same rows of w1 in the slots from H on.
 template <int TYPE>
-__device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_t * w0, const uint8_t * w1, int lo,
-                                                 int hi, uint32_t tiles, uint32_t red, const PinBars & bars,
-                                                 const ActPin & pin, int slot, int unit, PinRing & pos) {
+__device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const PinArgs & g, const uint8_t * w0,
+                                                 const uint8_t * w1, int lo, int hi, uint32_t tiles, uint32_t red,
+                                                 const PinBars & bars, const ActPin & pin, int slot, int unit,
+                                                 PinRing & pos) {
     constexpr uint32_t SB = Fmt<TYPE>::SB;
     const int lane = threadIdx.x & 31;
-    const int H = a.H, S = a.stages;
+    const int H = a.H, S = g.stages;
     const uint32_t row_bytes = (uint32_t)(a.c.K >> 8) * SB;
     const int part = slot >= H ? 1 : 0, sl = slot - part * H; // normal mode: H == R, part 0 only
     const bool mine = slot < a.R;
@@ -305,7 +313,7 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_
     const bool writer = (lane & (seg - 1)) == 0 && mine;
     const int h = unit & 1;
     // everything that moves with the ring is kept as an address and stepped, not recomputed
-    const uint32_t stage_bytes = (uint32_t)a.stage_bytes, red_bytes = (uint32_t)a.red_bytes;
+    const uint32_t stage_bytes = (uint32_t)g.stage_bytes, red_bytes = (uint32_t)g.red_bytes;
     uint32_t st_addr = tiles + (uint32_t)pos.stage * stage_bytes + my_off;
     uint32_t rd_addr = red + (uint32_t)pos.rb * red_bytes + (uint32_t)(slot * a.Ppad + unit / seg) * 4u;
     // where a row's bytes start inside its 16-byte line: only the low four address bits matter
@@ -356,15 +364,15 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const uint8_
     return true;
 }
 template <int TYPE>
-__device__ __forceinline__ bool pin_consume_call(const PinArgs & a, int si, uint32_t cost_lo, uint32_t cost_hi,
+__device__ __forceinline__ bool pin_consume_call(const PinArgs & a, const PinArgs & g, int si, uint32_t cost_lo, uint32_t cost_hi,
                                                  uint32_t tiles, uint32_t red, const PinBars & bars, const ActPin & pin,
                                                  int slot, int unit, PinRing & pos) {
     if (a.paired) { // gate rows and up rows together
         const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
-        return pin_consume_rows<TYPE>(a, a.c.seg[0].w, a.c.seg[1].w, pr.lo, pr.hi, tiles, red, bars, pin, slot, unit, pos);
+        return pin_consume_rows<TYPE>(a, g, a.c.seg[0].w, a.c.seg[1].w, pr.lo, pr.hi, tiles, red, bars, pin, slot, unit, pos);
     }
     const RowRange rr = a.next.x8 ? group_rows(a.c, blockIdx.x, gridDim.x) : cta_rows(a.c, si, cost_lo, cost_hi);
-    return pin_consume_rows<TYPE>(a, a.c.seg[si].w, a.c.seg[si].w, rr.lo, rr.hi, tiles, red, bars, pin, slot, unit, pos);
+    return pin_consume_rows<TYPE>(a, g, a.c.seg[si].w, a.c.seg[si].w, rr.lo, rr.hi, tiles, red, bars, pin, slot, unit, pos);
 }
 
 // Rows [32g, 32g+32) of the call's output as the next call's activation, quantized as b200q_xq
@@ -384,31 +392,263 @@ __device__ __forceinline__ void next_act_group(const PinArgs & a, int g, int lan
     }
 }
 
+// ---- the roles, one call each: both kernels below are built from these --------------------------
+// a = the call; g = where the shared-memory geometry comes from (a itself, or the first call of a
+// chain, whose geometry every call of the chain shares: a fixed place in the kernel parameters).
+struct PinProd {
+    int stage;
+    uint32_t par; // parity of the empty barrier: a fresh slot is free
+    int issued;
+};
+
+// Producer thread: one bulk copy (two in paired mode) per step of this CTA's rows of call a.
+__device__ __forceinline__ bool pin_produce(const PinArgs & a, const PinArgs & g, uint32_t tiles, const PinBars & bars,
+                                            uint32_t started, PinProd & pr) {
+    const int S = g.stages, R = a.R, nb = a.c.K >> 8;
+    bool alive = true;
+    if (a.paired) { // H gate rows and the H up rows of the same indices per stage
+        const RowRange rg = group_rows(a.c, blockIdx.x, gridDim.x);
+        const size_t row_bytes = (size_t)nb * sb_bytes(a.c.seg[0].type);
+        for (int p0 = rg.lo; p0 < rg.hi; p0 += a.H) {
+            const int rows = min(a.H, rg.hi - p0);
+            uintptr_t A0[2];
+            uint32_t len[2];
+            for (int e = 0; e < 2; e++) {
+                const uintptr_t A = reinterpret_cast<uintptr_t>(a.c.seg[e].w + (size_t)p0 * row_bytes);
+                A0[e] = A & ~uintptr_t(15);
+                len[e] = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0[e]);
+            }
+            alive = mbar_wait_gated(bars.empty + 8 * pr.stage, pr.par, &g_pin_status, started);
+            if (!alive) {
+                return false;
+            }
+            mbar_expect_tx(bars.full + 8 * pr.stage, len[0] + len[1]);
+            const uint32_t dst = tiles + (uint32_t)(pr.stage * g.stage_bytes);
+            bulk_g2s(dst, reinterpret_cast<const void *>(A0[0]), len[0], bars.full + 8 * pr.stage);
+            bulk_g2s(dst + (uint32_t)a.half_off, reinterpret_cast<const void *>(A0[1]), len[1], bars.full + 8 * pr.stage);
+            pr.issued++;
+            if (++pr.stage == S) {
+                pr.stage = 0;
+                pr.par ^= 1;
+            }
+        }
+        return true;
+    }
+    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+    for (int si = 0; si < a.c.n_segs; si++) {
+        const SegDev & sg = a.c.seg[si];
+        const RowRange rr = a.next.x8 ? group_rows(a.c, blockIdx.x, gridDim.x) : cta_rows(a.c, si, cost_lo, cost_hi);
+        const size_t row_bytes = (size_t)nb * sb_bytes(sg.type);
+        for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
+            const int rows = min(R, rr.hi - row0);
+            const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
+            const uintptr_t A0 = A & ~uintptr_t(15);
+            const uint32_t len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
+            alive = mbar_wait_gated(bars.empty + 8 * pr.stage, pr.par, &g_pin_status, started);
+            if (!alive) {
+                return false;
+            }
+            mbar_expect_tx(bars.full + 8 * pr.stage, len);
+            bulk_g2s(tiles + (uint32_t)(pr.stage * g.stage_bytes), reinterpret_cast<const void *>(A0), len,
+                     bars.full + 8 * pr.stage);
+            pr.issued++;
+            if (++pr.stage == S) {
+                pr.stage = 0;
+                pr.par ^= 1;
+            }
+        }
+    }
+    return true;
+}
+
+// A producer that leaves early waits (bounded) until the copies still in flight have landed.
+__device__ __forceinline__ void pin_produce_drain(const PinBars & bars, int S, const PinProd & pr) {
+    for (int s = 0; s < S && s < pr.issued; s++) {
+        const int last = ((pr.issued - 1 - s) / S) * S + s; // last step that filled stage s
+        mbar_wait(bars.full + 8 * s, (uint32_t)(last / S) & 1u, &g_pin_status);
+    }
+}
+
+// Epilogue warp: partial sums of each step -> alpha, residual, outputs (and the next call's
+// activation).  rb / rphase walk the ring of partial-sum buffers and carry over between calls.
+__device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & g, uint32_t red, const PinBars & bars,
+                                             int & rb, uint32_t & rphase) {
+    const int lane = threadIdx.x & 31;
+    const int P = a.P, Ppad = a.Ppad, R = a.R;
+    if (a.next.x8) {
+        // The call's output doubles as the next call's activation.  One segment: lane = row
+        // slot.  Two segments (gate|up, paired mode): lanes 0..15 take gate slots, lanes 16..31
+        // the up slots of the same pairs, sixteen pairs at a time.  Every stored value is also
+        // kept in a 64-row ring in shared memory; when a 32-row group completes, lane i takes
+        // its row's value(s) from the ring and the warp quantizes the group (a CTA's range
+        // is made of whole groups).
+        const uint32_t ring = red + (uint32_t)(kRedBufs * g.red_bytes); // 2 x 64 floats behind the partials
+        const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
+        const int H = a.H, per = a.paired ? 16 : 32;
+        const int e = a.paired ? lane >> 4 : 0, li = lane & (per - 1);
+        const SegDev & sg = a.c.seg[e];
+        for (int p0 = pr.lo; p0 < pr.hi; p0 += H) {
+            const int rows = min(H, pr.hi - p0);
+            if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
+                return false;
+            }
+            const uint32_t rbuf = red + (uint32_t)(rb * g.red_bytes);
+            for (int c0 = 0; c0 < rows; c0 += per) {
+                if (c0 + li < rows) {
+                    const uint32_t p = rbuf + (uint32_t)((e * H + c0 + li) * Ppad) * 4u;
+                    float sum = 0.f;
+                    for (int j = 0; j < P; j++) {
+                        sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
+                    }
+                    const int row = p0 + c0 + li;
+                    float v = sg.alpha * sum;
+                    if (sg.residual) {
+                        v += __ldcg(&sg.residual[row]);
+                    }
+                    sg.out[row] = v;
+                    sts32(ring + (uint32_t)(e * 64 + (row & 63)) * 4u, __float_as_uint(v));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bars.red_empty + 8 * rb);
+            }
+            if (++rb == kRedBufs) {
+                rb = 0;
+                rphase ^= 1;
+            }
+            // groups whose last row was stored in this step (H <= 32: at most two)
+            for (int gi = p0 >> 5; 32 * gi + 32 <= p0 + rows; gi++) {
+                const float gv = __uint_as_float(lds32(ring + (uint32_t)((32 * gi + lane) & 63) * 4u));
+                const float uv = __uint_as_float(lds32(ring + (uint32_t)(64 + ((32 * gi + lane) & 63)) * 4u));
+                next_act_group(a, gi, lane, gv, uv);
+                __syncwarp();
+            }
+        }
+        return true;
+    }
+    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+    for (int si = 0; si < a.c.n_segs; si++) {
+        const SegDev & sg = a.c.seg[si];
+        const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
+        for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
+            const int rows = min(R, rr.hi - row0);
+            if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
+                return false;
+            }
+            const uint32_t rbuf = red + (uint32_t)(rb * g.red_bytes);
+            for (int c0 = 0; c0 < rows; c0 += 32) { // lane = row slot; partials added in a fixed order
+                if (c0 + lane < rows) {
+                    const uint32_t p = rbuf + (uint32_t)((c0 + lane) * Ppad) * 4u;
+                    float sum = 0.f;
+                    for (int j = 0; j < P; j++) {
+                        sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
+                    }
+                    const size_t o = (size_t)(row0 + c0 + lane); // one token
+                    float v = sg.alpha * sum;
+                    if (sg.residual) {
+                        v += __ldcg(&sg.residual[o]);
+                    }
+                    store_out(a.c, &sg.out[o], v);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bars.red_empty + 8 * rb);
+            }
+            if (++rb == kRedBufs) {
+                rb = 0;
+                rphase ^= 1;
+            }
+        }
+    }
+    return true;
+}
+
+// Consumer warps: fetch the call's activation with bulk copies (thread 0 issues them), quantize
+// or re-lay it into the pack, and take this thread's unit into registers.
+__device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs & g, uint32_t base, uint32_t parity,
+                                               int unit, ActPin & pin) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int W = a.W, nb = a.c.K >> 8;
+    const uint32_t pack = base + (uint32_t)g.off_pack, xraw = base + (uint32_t)g.off_xraw, act_bar = base + 200;
+    const uint32_t K = (uint32_t)a.c.K;
+    if (threadIdx.x == 0) {
+        if (a.xq_x) {
+            mbar_expect_tx(act_bar, 4u * K);
+            bulk_g2s(xraw, a.xq_x, 4u * K, act_bar);
+        } else {
+            mbar_expect_tx(act_bar, K + K / 2);
+            bulk_g2s(xraw, a.c.x8, K, act_bar);
+            bulk_g2s(xraw + K, a.c.xmeta, K / 4, act_bar);
+            bulk_g2s(xraw + K + K / 4, a.c.xsumq, K / 4, act_bar);
+        }
+    }
+    if (!mbar_wait(act_bar, parity, &g_pin_status)) {
+        return false;
+    }
+    if (threadIdx.x == 0) {
+        PIN_STAMP(7);
+    }
+    if (a.xq_x) {
+        pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0);
+    } else {
+        pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
+    pin_from_pack(pack, unit, pin);
+    return true;
+}
+
+// Consumer warps: every step of this CTA's share of call a.
+__device__ __forceinline__ bool pin_consume(const PinArgs & a, const PinArgs & g, uint32_t tiles, uint32_t red,
+                                            const PinBars & bars, const ActPin & pin, int slot, int unit, PinRing & pos) {
+    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+    const int n_calls = a.paired ? 1 : a.c.n_segs; // paired mode walks both segments at once
+    for (int si = 0; si < n_calls; si++) {
+        bool ok;
+        switch (a.c.seg[si].type) {
+        case kQ4_K: ok = pin_consume_call<kQ4_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kQ5_K: ok = pin_consume_call<kQ5_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kQ6_K: ok = pin_consume_call<kQ6_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kIQ4_XS: ok = pin_consume_call<kIQ4_XS>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        default: ok = pin_consume_call<kQ8_0>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        }
+        if (!ok) {
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void pin_init_barriers(const PinBars & bars, uint32_t base, int S, int W) {
+    for (int s = 0; s < S; s++) {
+        mbar_init(bars.full + 8 * s, 1);
+        mbar_init(bars.empty + 8 * s, (uint32_t)W);
+    }
+    for (int b = 0; b < kRedBufs; b++) {
+        mbar_init(bars.red_full + 8 * b, (uint32_t)W);
+        mbar_init(bars.red_empty + 8 * b, 1);
+    }
+    mbar_init(base + 200, 1); // the activation's bulk copies
+    sts32(base + 192, 0);     // "consumers have started": gates the producer's clock budget
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __grid_constant__ PinArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     const PinBars bars{base, base + 64, base + 128, base + 160};
     const uint32_t started = base + 192;
-    const uint32_t red = base + kPinHdr, pack = base + (uint32_t)a.off_pack, tiles = base + (uint32_t)a.off_tiles;
+    const uint32_t red = base + kPinHdr, tiles = base + (uint32_t)a.off_tiles;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int W = a.W, R = a.R, S = a.stages, nb = a.c.K >> 8;
-    const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+    const int W = a.W;
 
     // let the next kernel of the stream be scheduled as soon as this grid is resident
     asm volatile("griddepcontrol.launch_dependents;");
     if (threadIdx.x == 0) {
         PIN_STAMP(0);
-        for (int s = 0; s < S; s++) {
-            mbar_init(bars.full + 8 * s, 1);
-            mbar_init(bars.empty + 8 * s, (uint32_t)W);
-        }
-        for (int b = 0; b < kRedBufs; b++) {
-            mbar_init(bars.red_full + 8 * b, (uint32_t)W);
-            mbar_init(bars.red_empty + 8 * b, 1);
-        }
-        mbar_init(base + 200, 1); // the activation's bulk copies
-        sts32(started, 0);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pin_init_barriers(bars, base, a.stages, W);
     }
     __syncthreads();
 
@@ -417,64 +657,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         if (lane != 0) {
             return;
         }
-        int stage = 0, issued = 0;
-        uint32_t par = 1; // parity of the empty barrier: a fresh slot is free
-        bool alive = true;
-        if (a.paired) { // H gate rows and the H up rows of the same indices per stage
-            const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
-            const size_t row_bytes = (size_t)nb * sb_bytes(a.c.seg[0].type);
-            for (int p0 = pr.lo; p0 < pr.hi; p0 += a.H) {
-                const int rows = min(a.H, pr.hi - p0);
-                uintptr_t A0[2];
-                uint32_t len[2];
-                for (int e = 0; e < 2; e++) {
-                    const uintptr_t A = reinterpret_cast<uintptr_t>(a.c.seg[e].w + (size_t)p0 * row_bytes);
-                    A0[e] = A & ~uintptr_t(15);
-                    len[e] = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0[e]);
-                }
-                alive = mbar_wait_gated(bars.empty + 8 * stage, par, &g_pin_status, started);
-                if (!alive) {
-                    break;
-                }
-                mbar_expect_tx(bars.full + 8 * stage, len[0] + len[1]);
-                const uint32_t dst = tiles + (uint32_t)(stage * a.stage_bytes);
-                bulk_g2s(dst, reinterpret_cast<const void *>(A0[0]), len[0], bars.full + 8 * stage);
-                bulk_g2s(dst + (uint32_t)a.half_off, reinterpret_cast<const void *>(A0[1]), len[1], bars.full + 8 * stage);
-                issued++;
-                if (++stage == S) {
-                    stage = 0;
-                    par ^= 1;
-                }
-            }
-        }
-        for (int si = 0; si < a.c.n_segs && alive && !a.paired; si++) {
-            const SegDev & sg = a.c.seg[si];
-            const RowRange rr = a.next.x8 ? group_rows(a.c, blockIdx.x, gridDim.x) : cta_rows(a.c, si, cost_lo, cost_hi);
-            const size_t row_bytes = (size_t)nb * sb_bytes(sg.type);
-            for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
-                const int rows = min(R, rr.hi - row0);
-                const uintptr_t A = reinterpret_cast<uintptr_t>(sg.w + (size_t)row0 * row_bytes);
-                const uintptr_t A0 = A & ~uintptr_t(15);
-                const uint32_t len = (uint32_t)(((A + (size_t)rows * row_bytes + 15) & ~uintptr_t(15)) - A0);
-                alive = mbar_wait_gated(bars.empty + 8 * stage, par, &g_pin_status, started);
-                if (!alive) {
-                    break;
-                }
-                mbar_expect_tx(bars.full + 8 * stage, len);
-                bulk_g2s(tiles + (uint32_t)(stage * a.stage_bytes), reinterpret_cast<const void *>(A0), len,
-                         bars.full + 8 * stage);
-                issued++;
-                if (++stage == S) {
-                    stage = 0;
-                    par ^= 1;
-                }
-            }
-        }
-        if (!alive) { // leaving early: wait (bounded) until the copies still in flight have landed
-            for (int s = 0; s < S && s < issued; s++) {
-                const int last = ((issued - 1 - s) / S) * S + s; // last step that filled stage s
-                mbar_wait(bars.full + 8 * s, (uint32_t)(last / S) & 1u, &g_pin_status);
-            }
+        PinProd pr{0, 1, 0};
+        if (!pin_produce(a, a, tiles, bars, started, pr)) {
+            pin_produce_drain(bars, a.stages, pr);
         }
         return;
     }
@@ -489,92 +674,8 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         // ---------------------------------------------------------------- epilogue warp
         int rb = 0;
         uint32_t rphase = 0;
-        const int P = a.P, Ppad = a.Ppad;
-        if (a.next.x8) {
-            // The call's output doubles as the next call's activation.  One segment: lane = row
-            // slot.  Two segments (gate|up, paired mode): lanes 0..15 take gate slots, lanes 16..31
-            // the up slots of the same pairs, sixteen pairs at a time.  Every stored value is also
-            // kept in a 64-row ring in shared memory; when a 32-row group completes, lane i takes
-            // its row's value(s) from the ring and the warp quantizes the group (a CTA's range
-            // is made of whole groups).
-            const uint32_t ring = red + (uint32_t)(kRedBufs * a.red_bytes); // 2 x 64 floats behind the partials
-            const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
-            const int H = a.H, per = a.paired ? 16 : 32;
-            const int e = a.paired ? lane >> 4 : 0, li = lane & (per - 1);
-            const SegDev & sg = a.c.seg[e];
-            for (int p0 = pr.lo; p0 < pr.hi; p0 += H) {
-                const int rows = min(H, pr.hi - p0);
-                if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
-                    return;
-                }
-                const uint32_t rbuf = red + (uint32_t)(rb * a.red_bytes);
-                for (int c0 = 0; c0 < rows; c0 += per) {
-                    if (c0 + li < rows) {
-                        const uint32_t p = rbuf + (uint32_t)((e * H + c0 + li) * Ppad) * 4u;
-                        float sum = 0.f;
-                        for (int j = 0; j < P; j++) {
-                            sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
-                        }
-                        const int row = p0 + c0 + li;
-                        float v = sg.alpha * sum;
-                        if (sg.residual) {
-                            v += sg.residual[row];
-                        }
-                        sg.out[row] = v;
-                        sts32(ring + (uint32_t)(e * 64 + (row & 63)) * 4u, __float_as_uint(v));
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bars.red_empty + 8 * rb);
-                }
-                if (++rb == kRedBufs) {
-                    rb = 0;
-                    rphase ^= 1;
-                }
-                // groups whose last row was stored in this step (H <= 32: at most two)
-                for (int g = p0 >> 5; 32 * g + 32 <= p0 + rows; g++) {
-                    const float gv = __uint_as_float(lds32(ring + (uint32_t)((32 * g + lane) & 63) * 4u));
-                    const float uv = __uint_as_float(lds32(ring + (uint32_t)(64 + ((32 * g + lane) & 63)) * 4u));
-                    next_act_group(a, g, lane, gv, uv);
-                    __syncwarp();
-                }
-            }
+        if (!pin_epilogue(a, a, red, bars, rb, rphase)) {
             return;
-        }
-        for (int si = 0; si < a.c.n_segs; si++) {
-            const SegDev & sg = a.c.seg[si];
-            const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
-            for (int row0 = rr.lo; row0 < rr.hi; row0 += R) {
-                const int rows = min(R, rr.hi - row0);
-                if (!mbar_wait(bars.red_full + 8 * rb, rphase, &g_pin_status)) {
-                    return;
-                }
-                const uint32_t rbuf = red + (uint32_t)(rb * a.red_bytes);
-                for (int c0 = 0; c0 < rows; c0 += 32) { // lane = row slot; partials added in a fixed order
-                    if (c0 + lane < rows) {
-                        const uint32_t p = rbuf + (uint32_t)((c0 + lane) * Ppad) * 4u;
-                        float sum = 0.f;
-                        for (int j = 0; j < P; j++) {
-                            sum += __uint_as_float(lds32(p + 4u * (uint32_t)j));
-                        }
-                        const size_t o = (size_t)(row0 + c0 + lane); // one token
-                        float v = sg.alpha * sum;
-                        if (sg.residual) {
-                            v += sg.residual[o];
-                        }
-                        store_out(a.c, &sg.out[o], v);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bars.red_empty + 8 * rb);
-                }
-                if (++rb == kRedBufs) {
-                    rb = 0;
-                    rphase ^= 1;
-                }
-            }
         }
         if (a.sync.signal) {
             // every CTA: publish its peer stores system-wide, then count itself; the last one
@@ -632,65 +733,167 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
     const int U = a.U;
     const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
     ActPin pin;
-    {
-        const uint32_t xraw = base + (uint32_t)a.off_xraw, act_bar = base + 200;
-        const uint32_t K = (uint32_t)a.c.K;
-        if (threadIdx.x == 0) {
-            if (a.xq_x) {
-                mbar_expect_tx(act_bar, 4u * K);
-                bulk_g2s(xraw, a.xq_x, 4u * K, act_bar);
-            } else {
-                mbar_expect_tx(act_bar, K + K / 2);
-                bulk_g2s(xraw, a.c.x8, K, act_bar);
-                bulk_g2s(xraw + K, a.c.xmeta, K / 4, act_bar);
-                bulk_g2s(xraw + K + K / 4, a.c.xsumq, K / 4, act_bar);
-            }
-        }
-        if (!mbar_wait(act_bar, 0, &g_pin_status)) {
-            return;
-        }
-        if (threadIdx.x == 0) {
-            PIN_STAMP(7);
-        }
-        if (a.xq_x) {
-            pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0);
-        } else {
-            pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
-        }
+    if (!pin_activation(a, a, base, 0, unit, pin)) {
+        return;
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
-    pin_from_pack(pack, unit, pin);
     if (threadIdx.x == 0) {
         asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(started), "r"(1u) : "memory");
         PIN_STAMP(2);
     }
-
     PinRing pos{0, 0, 0, 0};
-    const int n_calls = a.paired ? 1 : a.c.n_segs; // paired mode walks both segments at once
-    for (int si = 0; si < n_calls; si++) {
-        bool ok;
-        switch (a.c.seg[si].type) {
-        case kQ4_K: ok = pin_consume_call<kQ4_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kQ5_K: ok = pin_consume_call<kQ5_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kQ6_K: ok = pin_consume_call<kQ6_K>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kIQ4_XS: ok = pin_consume_call<kIQ4_XS>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        default: ok = pin_consume_call<kQ8_0>(a, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        }
-        if (!ok) {
-            return;
-        }
+    if (!pin_consume(a, a, tiles, red, bars, pin, slot, unit, pos)) {
+        return;
     }
     if (threadIdx.x == 0) {
         PIN_STAMP(4);
     }
 }
 
+// ---- several dependent calls in one launch ------------------------------------------------------
+// Calls whose activation is the previous call's output (o -> gate|up -> down) pay, as separate
+// launches, a start-up and a drain each during which HBM does not stream for them.  Here the
+// same roles walk the calls one after the other inside ONE launch: the producer keeps the ring
+// full across the boundaries (weights depend on nothing), the epilogue warp counts its CTA in
+// when its rows of a call are stored, and the consumers of every CTA wait for that count to reach
+// (calls so far) x (CTAs) before they fetch the next activation.  All CTAs are resident (one per
+// SM, at most one CTA per SM in the grid), so the wait cannot starve; it is bounded like every
+// other wait.  All calls share one ring geometry and the same kChainW consumer warps.
+constexpr int kChainMax = 4;
+constexpr int kChainW = 17; // consumer warps of every call of a chain
+struct ChainArgs {
+    PinArgs call[kChainMax];
+    int32_t n;
+};
+// CTAs that have finished call 0, 1, ... of the running chain launch; the last arrival of the
+// last call puts it back to zero.  One chain launch at a time per device.
+__device__ uint32_t g_chain_count = 0;
+
+__global__ void __launch_bounds__(32 * (kChainW + 2), 1) gemv_chain_kernel(const __grid_constant__ ChainArgs ch) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const PinBars bars{base, base + 64, base + 128, base + 160};
+    const uint32_t started = base + 192;
+    const uint32_t red = base + kPinHdr, tiles = base + (uint32_t)ch.call[0].off_tiles;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = ch.n, S = ch.call[0].stages;
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (threadIdx.x == 0) {
+        {
+            [[maybe_unused]] const PinArgs & a = ch.call[0];
+            PIN_STAMP(0);
+        }
+        pin_init_barriers(bars, base, S, kChainW);
+    }
+    __syncthreads();
+
+    if (warp == kChainW) {
+        // ---------------------------------------------------------------- producer (one thread)
+        if (lane != 0) {
+            return;
+        }
+        PinProd pr{0, 1, 0};
+        for (int ci = 0; ci < n; ci++) {
+            if (!pin_produce(ch.call[ci], ch.call[0], tiles, bars, started, pr)) {
+                pin_produce_drain(bars, S, pr);
+                return;
+            }
+        }
+        return;
+    }
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        [[maybe_unused]] const PinArgs & a = ch.call[0];
+        PIN_STAMP(1);
+    }
+
+    if (warp == kChainW + 1) {
+        // ---------------------------------------------------------------- epilogue warp
+        int rb = 0;
+        uint32_t rphase = 0;
+        for (int ci = 0; ci < n; ci++) {
+            const PinArgs & a = ch.call[ci];
+            if (!pin_epilogue(a, ch.call[0], red, bars, rb, rphase)) {
+                return;
+            }
+            __threadfence(); // this CTA's outputs of the call, before it is counted in
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t old = atomicAdd(&g_chain_count, 1u);
+                if (old == (uint32_t)n * gridDim.x - 1u) {
+                    atomicExch(&g_chain_count, 0u);
+                }
+                PIN_STAMP(5);
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    PinRing pos{0, 0, 0, 0};
+    for (int ci = 0; ci < n; ci++) {
+        const PinArgs & a = ch.call[ci];
+        if (ci > 0) {
+            if (threadIdx.x == 0) {
+                PIN_STAMP(0);
+            }
+            // every consumer has taken its unit of the previous call out of the pack
+            asm volatile("bar.sync 1, %0;" ::"r"(32 * kChainW) : "memory");
+            if (threadIdx.x == 0) { // all CTAs have stored their rows of the previous call
+                const uint32_t target = (uint32_t)ci * gridDim.x;
+                const long long t0 = clock64();
+                for (;;) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&g_chain_count) : "memory");
+                    if (v >= target) {
+                        break;
+                    }
+                    if (clock64() - t0 > kSpinCycles) {
+                        atomicExch(&g_pin_status, B200Q_ETIMEOUT);
+                        break;
+                    }
+                }
+                // the bulk copies below read, through the asynchronous proxy, what other CTAs stored
+                asm volatile("fence.proxy.async;" ::: "memory");
+                PIN_STAMP(1);
+            }
+        }
+        const int U = a.U;
+        const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
+        ActPin pin;
+        if (!pin_activation(a, ch.call[0], base, (uint32_t)ci & 1u, unit, pin)) {
+            return;
+        }
+        if (ci == 0 && threadIdx.x == 0) {
+            asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(started), "r"(1u) : "memory");
+        }
+        if (threadIdx.x == 0) {
+            PIN_STAMP(2);
+        }
+        if (!pin_consume(a, ch.call[0], tiles, red, bars, pin, slot, unit, pos)) {
+            return;
+        }
+        if (threadIdx.x == 0) {
+            PIN_STAMP(4);
+        }
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 // Consumer warps W and row slots R for U units per row: the most warps whose lane use
-// R*U / (32*W) is within 4 % of the best (more warps hide more latency).
-static void pick_shape(int U, bool even_rows, int & W, int & R) {
+// R*U / (32*W) is within 4 % of the best (more warps hide more latency).  w_fixed > 0: that W.
+static void pick_shape(int U, bool even_rows, int w_fixed, int & W, int & R) {
     W = 0;
     R = 0;
+    if (w_fixed > 0) {
+        const int r = even_rows ? (32 * w_fixed / U) & ~1 : 32 * w_fixed / U;
+        if (r >= 1) {
+            W = w_fixed;
+            R = r;
+        }
+        return;
+    }
     double best = -1.0;
     for (int pass = 0; pass < 2; pass++) {
         for (int w = kPinMaxW; w >= 8; w--) {
@@ -716,16 +919,16 @@ static uint32_t pin_grid(const CallDev & c, const PinArgs & a, int next_mode) {
     return (uint32_t)(steps < kSMs ? steps : kSMs);
 }
 
-// next_mode: 0 = plain call, 1 = one segment whose output is quantized for the next call,
-// 2 = gate|up pairs (silu(gate)*up quantized for the next call)
-static bool pin_plan(const CallDev & c, int next_mode, bool fp32_in, PinArgs & a) {
+// Thread geometry of a call.  next_mode: 0 = plain call, 1 = one segment whose output is quantized
+// for the next call, 2 = gate|up pairs (silu(gate)*up quantized for the next call).
+static bool pin_shape(const CallDev & c, int next_mode, int w_fixed, PinArgs & a) {
     const bool paired = next_mode == 2;
     if (c.TB != 1 || (c.K & 255)) {
         return false;
     }
-    const int nb = c.K >> 8, U = c.K >> 7;
+    const int U = c.K >> 7;
     int W, R;
-    pick_shape(U, paired, W, R);
+    pick_shape(U, paired, w_fixed, W, R);
     if (W == 0) {
         return false;
     }
@@ -741,46 +944,99 @@ static bool pin_plan(const CallDev & c, int next_mode, bool fp32_in, PinArgs & a
             return false;
         }
     }
-    int max_sbb = 0;
-    for (int i = 0; i < c.n_segs; i++) {
-        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
-    }
-    const size_t row_max = (size_t)nb * max_sbb;
     int seg = 1; // lanes summed by shuffles: the largest power of two dividing U, at most a warp
     while (seg < 32 && U % (2 * seg) == 0) {
         seg *= 2;
     }
-    const int P = U / seg, Ppad = P | 1; // odd row pitch: the epilogue's lanes hit distinct banks
-    const size_t pack_bytes = (size_t)U * kPinUnitBytes;
-    for (;; R -= paired ? 2 : 1) { // fewer row slots when two stages of R rows do not fit
+    a.W = W, a.R = R, a.U = U, a.seg = seg, a.P = U / seg;
+    a.Ppad = a.P | 1; // odd row pitch: the epilogue's lanes hit distinct banks
+    a.paired = paired ? 1 : 0;
+    a.next_mode = next_mode;
+    return true;
+}
+
+// Shared memory a call needs with R row slots: partial sums per buffer, pack, landing zone of the
+// raw activation (the fp32 vector, or the three quantized views: K + K/4 + K/4 bytes), one stage.
+struct PinNeed {
+    size_t red, pack, xraw, half, stage;
+};
+static PinNeed pin_need(const CallDev & c, const PinArgs & a, bool fp32_in, int R) {
+    int max_sbb = 0;
+    for (int i = 0; i < c.n_segs; i++) {
+        max_sbb = max_sbb > sb_bytes(c.seg[i].type) ? max_sbb : sb_bytes(c.seg[i].type);
+    }
+    const size_t row_max = (size_t)(c.K >> 8) * max_sbb;
+    PinNeed n;
+    n.red = ((size_t)R * a.Ppad * 4 + 15) / 16 * 16;
+    n.pack = (size_t)a.U * kPinUnitBytes;
+    n.xraw = (fp32_in ? 4 : 1) * (size_t)c.K + (fp32_in ? 0 : c.K / 2);
+    n.half = ((size_t)(R / 2) * row_max + 32 + 15) / 16 * 16;
+    n.stage = a.paired ? (2 * n.half + 127) / 128 * 128 : ((size_t)R * row_max + 32 + 127) / 128 * 128;
+    return n;
+}
+static void pin_set_layout(PinArgs & a, int R, const PinNeed & n, size_t red, size_t pack, size_t xraw, size_t stage) {
+    const size_t off_pack = kPinHdr + kRedBufs * red + 512; // + the epilogue's value ring
+    const size_t off_xraw = (off_pack + pack + 15) / 16 * 16;
+    const size_t off_tiles = (off_xraw + xraw + 127) / 128 * 128;
+    const int stages = off_tiles < (size_t)kPinSmem ? (int)(((size_t)kPinSmem - off_tiles) / stage) : 0;
+    a.R = R;
+    a.H = a.paired ? R / 2 : R;
+    a.half_off = a.paired ? (int32_t)n.half : 0;
+    a.stages = stages > 8 ? 8 : stages;
+    a.stage_bytes = (int32_t)stage;
+    a.red_bytes = (int32_t)red;
+    a.off_pack = (int32_t)off_pack;
+    a.off_xraw = (int32_t)off_xraw;
+    a.off_tiles = (int32_t)off_tiles;
+}
+
+static bool pin_plan(const CallDev & c, int next_mode, bool fp32_in, PinArgs & a) {
+    if (!pin_shape(c, next_mode, 0, a)) {
+        return false;
+    }
+    for (int R = a.R;; R -= a.paired ? 2 : 1) { // fewer row slots when two stages of R rows do not fit
         if (R < 1) {
             return false;
         }
-        const size_t red_bytes = ((size_t)R * Ppad * 4 + 15) / 16 * 16;
-        const size_t off_pack = kPinHdr + kRedBufs * red_bytes + (next_mode ? 512 : 0); // + the epilogue's value ring
-        const size_t off_xraw = (off_pack + pack_bytes + 15) / 16 * 16;
-        // room for the fp32 vector, or for the three quantized views (K + K/4 + K/4 bytes)
-        const size_t off_tiles = (off_xraw + (fp32_in ? 4 : 1) * (size_t)c.K + (fp32_in ? 0 : c.K / 2) + 127) / 128 * 128;
-        const size_t half = ((size_t)(R / 2) * row_max + 32 + 15) / 16 * 16;
-        const size_t stage = paired ? (2 * half + 127) / 128 * 128 : ((size_t)R * row_max + 32 + 127) / 128 * 128;
-        a.H = paired ? R / 2 : R;
-        a.half_off = paired ? (int32_t)half : 0;
-        a.paired = paired ? 1 : 0;
-        if (off_tiles + 2 * stage > (size_t)kPinSmem || stage >= (1u << 20)) {
-            continue;
+        const PinNeed n = pin_need(c, a, fp32_in, R);
+        pin_set_layout(a, R, n, n.red, n.pack, n.xraw, n.stage);
+        if (a.stages >= 2 && n.stage < (1u << 20)) {
+            break;
         }
-        int stages = (int)(((size_t)kPinSmem - off_tiles) / stage);
-        a.W = W, a.R = R, a.U = U, a.seg = seg, a.P = P, a.Ppad = Ppad;
-        a.stages = stages > 8 ? 8 : stages;
-        a.stage_bytes = (int32_t)stage;
-        a.red_bytes = (int32_t)red_bytes;
-        a.off_pack = (int32_t)off_pack;
-        a.off_xraw = (int32_t)off_xraw;
-        a.off_tiles = (int32_t)off_tiles;
-        break;
     }
-    a.next_mode = next_mode;
     return cost_split(c, pin_grid(c, a, next_mode), a.cost);
+}
+
+// One geometry for all calls of a chain: every call on kChainW consumer warps, the largest
+// need of any call for each region, at least three stages.
+static bool chain_plan(const CallDev * calls, const float * const * xq_x, const NextAct * next, int n, ChainArgs & ch) {
+    if (n < 1 || n > kChainMax) {
+        return false;
+    }
+    PinNeed need[kChainMax];
+    size_t red = 0, pack = 0, xraw = 0, stage = 0;
+    for (int i = 0; i < n; i++) {
+        PinArgs & a = ch.call[i];
+        const CallDev & c = calls[i];
+        const int next_mode = next[i].x8 ? (c.n_segs == 2 ? 2 : 1) : 0;
+        if (c.n_peers > 0 || !pin_shape(c, next_mode, kChainW, a)) {
+            return false;
+        }
+        need[i] = pin_need(c, a, xq_x[i] != nullptr, a.R);
+        red = red > need[i].red ? red : need[i].red;
+        pack = pack > need[i].pack ? pack : need[i].pack;
+        xraw = xraw > need[i].xraw ? xraw : need[i].xraw;
+        stage = stage > need[i].stage ? stage : need[i].stage;
+    }
+    for (int i = 0; i < n; i++) {
+        PinArgs & a = ch.call[i];
+        pin_set_layout(a, a.R, need[i], red, pack, xraw, stage);
+        if (a.stages < 3 || stage >= (1u << 20) || !cost_split(calls[i], kSMs, a.cost)) {
+            return false;
+        }
+    }
+    ch.n = n;
+    return true;
 }
 
 static bool views_aligned(const CallDev & c) { // bulk copies start on 16-byte boundaries
@@ -819,12 +1075,13 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
         return cudaErrorInvalidConfiguration;
     }
 #ifdef B200Q_TUNING
-    {
-        static int launches = 0;
-        const char * tp = getenv("B200Q_TRACE_PTR");
-        a.trace = tp ? reinterpret_cast<unsigned long long *>(strtoull(tp, nullptr, 0)) : nullptr;
-        a.launch_idx = launches++;
+    if (getenv("B200Q_CHAIN1")) { // A/B: the chain kernel for single calls too (one kernel image in the stream)
+        const NextAct nx = a.next;
+        if (!sync) {
+            return launch_gemv_chain(s, &c, &xq_x, &nx, 1);
+        }
     }
+    trace_slot(a, true);
 #endif
     const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
     cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_pinned_kernel), kPinSmem);
@@ -844,11 +1101,74 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     return cudaLaunchKernelEx(&cfg, gemv_pinned_kernel, a);
 }
 
+static void chain_fill(ChainArgs & ch, const CallDev * calls, const float * const * xq_x, const NextAct * next, int n,
+                       bool launching = false) {
+    memset(&ch, 0, sizeof(ch));
+    for (int i = 0; i < n; i++) {
+        ch.call[i].c = calls[i];
+        ch.call[i].xq_x = xq_x[i];
+        ch.call[i].next = next[i];
+#ifdef B200Q_TUNING
+        trace_slot(ch.call[i], launching);
+#endif
+    }
+}
+
+bool chain_supported(const CallDev * calls, const float * const * xq_x, const NextAct * next, int n) {
+    if (n < 2 || n > kChainMax) {
+        return false;
+    }
+    // the waits between calls need every CTA of the grid resident: one per SM
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms < kSMs) {
+        return false;
+    }
+    ChainArgs ch;
+    chain_fill(ch, calls, xq_x, next, n);
+    for (int i = 0; i < n; i++) {
+        if (!views_aligned(calls[i]) || (reinterpret_cast<uintptr_t>(xq_x[i]) & 15)) {
+            return false;
+        }
+    }
+    return chain_plan(calls, xq_x, next, n, ch);
+}
+
+cudaError_t launch_gemv_chain(cudaStream_t s, const CallDev * calls, const float * const * xq_x, const NextAct * next,
+                              int n) {
+    ChainArgs ch;
+    chain_fill(ch, calls, xq_x, next, n, true);
+    if (!chain_plan(calls, xq_x, next, n, ch)) {
+        return cudaErrorInvalidConfiguration;
+    }
+    const PinArgs & a = ch.call[0];
+    const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_chain_kernel), kPinSmem);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kSMs); // one CTA per SM: all resident, which the waits between calls rely on
+    cfg.blockDim = dim3(32 * (kChainW + 2));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_chain_kernel, ch);
+}
+
 cudaError_t read_pin_status(int * status, bool clear) {
     cudaError_t e = cudaMemcpyFromSymbol(status, g_pin_status, sizeof(int));
     if (e == cudaSuccess && clear && *status != 0) {
         const int zero = 0;
         e = cudaMemcpyToSymbol(g_pin_status, &zero, sizeof(int));
+        if (e == cudaSuccess) { // a chain launch that gave up may have left its count behind
+            const uint32_t none = 0;
+            e = cudaMemcpyToSymbol(g_chain_count, &none, sizeof(none));
+        }
     }
     return e;
 }

@@ -19,6 +19,11 @@ bool pinned_next_supported(const CallDev & call); // a call that also emits the 
 bool pinned_quantizes(const CallDev & call, const float * x, const float * act_up);
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next,
                                const PeerSync * sync = nullptr);
+// two to four dependent single-token calls in one launch (gemv_pinned.cu); xq_x[i] != nullptr: call i
+// quantizes that fp32 vector itself; next[i].x8 != nullptr: call i emits the next call's activation
+bool chain_supported(const CallDev * calls, const float * const * xq_x, const NextAct * next, int n);
+cudaError_t launch_gemv_chain(cudaStream_t s, const CallDev * calls, const float * const * xq_x, const NextAct * next,
+                              int n);
 cudaError_t read_pin_status(int * status, bool clear);
 // cudaFuncAttributeMaxDynamicSharedMemorySize is per device: set once per (kernel, device)
 cudaError_t ensure_dynamic_smem(const void * func, int bytes);

@@ -51,6 +51,8 @@ class DenseLayer:
         self.act_f = alloc_act(TB, n_ff, dev)
         # one token on one GPU: the gate|up GEMV leaves the quantized silu(gate)*up for the down call
         self.fused_h = TB == 1 and world == 1
+        # ... and o, gate|up and down (each consumes the previous one's output) go out as one launch
+        self.chain = self.fused_h
         self._staging = {}
 
     def weight_bytes(self):
@@ -83,7 +85,13 @@ class DenseLayer:
         return [([s for s, _ in call], [g for _, g in call]) for call in plan]
 
     def forward(self, x, out, calls=None):
-        for i, (segs, gathers) in enumerate(calls or self.calls(x, out)):
+        calls = calls or self.calls(x, out)
+        if self.fused_h and self.chain:
+            self.be.quant_gemv_ex(calls[0][0], 1)
+            self.be.quant_gemv_chain([(calls[1][0], False, None), (calls[2][0], False, self.act_f),
+                                      (calls[3][0], True, None)])
+            return out
+        for i, (segs, gathers) in enumerate(calls):
             if self.fused_h:
                 # one launch per call: q|k|v and o quantize in the GEMV's prologue, gate|up emits down's
                 # quantized activation
@@ -114,5 +122,5 @@ class DenseLayer:
         if self.arena is not None:  # GEMV with peer stores; down keeps its silu(gate)*up quantizer launch
             return 5 if self.TB == 1 else 12
         if self.fused_h:
-            return 4
+            return 2 if self.chain else 4
         return 5 if self.TB == 1 else 8
