@@ -71,6 +71,8 @@ with torch.cuda.stream(st):
     st.synchronize()
     print(f"{e0.elapsed_time(e1) / 8 * 1e3:.2f} us per layer step (tuning build, stamps on)")
 t = trace.cpu().numpy().reshape(64, 160, 8).astype(np.float64)
+if os.environ.get("B200Q_TRACE_SAVE"):  # the raw stamps, for a closer look than the means below
+    np.save(os.environ["B200Q_TRACE_SAVE"], t)
 idx = [i for i in range(64) if (t[i, :, 0] > 0).any()]  # a graph's kernel nodes keep the launch index of their capture
 names = ["entry", "wait_done", "act_ready", "first_tile", "cons_done", "epi_done", "pre_wait", "act_landed"]
 t0 = min(t[i, :, 0][t[i, :, 0] > 0].min() for i in idx)

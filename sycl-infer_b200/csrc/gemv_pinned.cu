@@ -224,7 +224,9 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, u
     }
 }
 
-__device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & a) {
+// Only what TYPE's decoder reads is loaded (Q4_K / Q5_K: scales and scale x sum; Q6_K: scales and
+// the two 16-value sums; the others: scales), so the rest costs no registers in that type's loop.
+template <int TYPE> __device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & a) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint32_t p = pin_pack_addr(pack, 4 * unit + i);
@@ -232,9 +234,9 @@ __device__ __forceinline__ void pin_from_pack(uint32_t pack, int unit, ActPin & 
         a.x[i][0] = x0.x, a.x[i][1] = x0.y, a.x[i][2] = x0.z, a.x[i][3] = x0.w;
         a.x[i][4] = x1.x, a.x[i][5] = x1.y, a.x[i][6] = x1.z, a.x[i][7] = x1.w;
         a.sx[i] = __uint_as_float(m.x);
-        a.xs[i][0] = (int)m.y;
-        a.xs[i][1] = (int)m.z;
-        a.c[i] = __uint_as_float(m.w);
+        a.xs[i][0] = TYPE == kQ6_K ? (int)m.y : 0;
+        a.xs[i][1] = TYPE == kQ6_K ? (int)m.z : 0;
+        a.c[i] = (TYPE == kQ4_K || TYPE == kQ5_K) ? __uint_as_float(m.w) : 0.0f;
     }
 }
 
@@ -365,8 +367,10 @@ __device__ __forceinline__ bool pin_consume_rows(const PinArgs & a, const PinArg
 }
 template <int TYPE>
 __device__ __forceinline__ bool pin_consume_call(const PinArgs & a, const PinArgs & g, int si, uint32_t cost_lo, uint32_t cost_hi,
-                                                 uint32_t tiles, uint32_t red, const PinBars & bars, const ActPin & pin,
+                                                 uint32_t tiles, uint32_t red, const PinBars & bars, uint32_t pack,
                                                  int slot, int unit, PinRing & pos) {
+    ActPin pin; // this thread's unit of the activation, for the whole segment
+    pin_from_pack<TYPE>(pack, unit, pin);
     if (a.paired) { // gate rows and up rows together
         const RowRange pr = group_rows(a.c, blockIdx.x, gridDim.x);
         return pin_consume_rows<TYPE>(a, g, a.c.seg[0].w, a.c.seg[1].w, pr.lo, pr.hi, tiles, red, bars, pin, slot, unit, pos);
@@ -565,10 +569,9 @@ __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & 
     return true;
 }
 
-// Consumer warps: fetch the call's activation with bulk copies (thread 0 issues them), quantize
-// or re-lay it into the pack, and take this thread's unit into registers.
-__device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs & g, uint32_t base, uint32_t parity,
-                                               int unit, ActPin & pin) {
+// Consumer warps: fetch the call's activation with bulk copies (thread 0 issues them) and quantize
+// or re-lay it into the pack, from which every thread then takes its unit into registers.
+__device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs & g, uint32_t base, uint32_t parity) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = a.W, nb = a.c.K >> 8;
     const uint32_t pack = base + (uint32_t)g.off_pack, xraw = base + (uint32_t)g.off_xraw, act_bar = base + 200;
@@ -596,23 +599,22 @@ __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs 
         pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
-    pin_from_pack(pack, unit, pin);
     return true;
 }
 
 // Consumer warps: every step of this CTA's share of call a.
 __device__ __forceinline__ bool pin_consume(const PinArgs & a, const PinArgs & g, uint32_t tiles, uint32_t red,
-                                            const PinBars & bars, const ActPin & pin, int slot, int unit, PinRing & pos) {
+                                            const PinBars & bars, uint32_t pack, int slot, int unit, PinRing & pos) {
     const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
     const int n_calls = a.paired ? 1 : a.c.n_segs; // paired mode walks both segments at once
     for (int si = 0; si < n_calls; si++) {
         bool ok;
         switch (a.c.seg[si].type) {
-        case kQ4_K: ok = pin_consume_call<kQ4_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kQ5_K: ok = pin_consume_call<kQ5_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kQ6_K: ok = pin_consume_call<kQ6_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        case kIQ4_XS: ok = pin_consume_call<kIQ4_XS>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
-        default: ok = pin_consume_call<kQ8_0>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pin, slot, unit, pos); break;
+        case kQ4_K: ok = pin_consume_call<kQ4_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pack, slot, unit, pos); break;
+        case kQ5_K: ok = pin_consume_call<kQ5_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pack, slot, unit, pos); break;
+        case kQ6_K: ok = pin_consume_call<kQ6_K>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pack, slot, unit, pos); break;
+        case kIQ4_XS: ok = pin_consume_call<kIQ4_XS>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pack, slot, unit, pos); break;
+        default: ok = pin_consume_call<kQ8_0>(a, g, si, cost_lo, cost_hi, tiles, red, bars, pack, slot, unit, pos); break;
         }
         if (!ok) {
             return false;
@@ -732,8 +734,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
     }
     const int U = a.U;
     const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
-    ActPin pin;
-    if (!pin_activation(a, a, base, 0, unit, pin)) {
+    if (!pin_activation(a, a, base, 0)) {
         return;
     }
     if (threadIdx.x == 0) {
@@ -741,7 +742,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         PIN_STAMP(2);
     }
     PinRing pos{0, 0, 0, 0};
-    if (!pin_consume(a, a, tiles, red, bars, pin, slot, unit, pos)) {
+    if (!pin_consume(a, a, tiles, red, bars, base + (uint32_t)a.off_pack, slot, unit, pos)) {
         return;
     }
     if (threadIdx.x == 0) {
@@ -759,7 +760,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
 // SM, at most one CTA per SM in the grid), so the wait cannot starve; it is bounded like every
 // other wait.  All calls share one ring geometry and the same kChainW consumer warps.
 constexpr int kChainMax = 4;
-constexpr int kChainW = 17; // consumer warps of every call of a chain
+constexpr int kChainW = kPinMaxW; // consumer warps of every call of a chain
 struct ChainArgs {
     PinArgs call[kChainMax];
     int32_t n;
@@ -861,8 +862,7 @@ __global__ void __launch_bounds__(32 * (kChainW + 2), 1) gemv_chain_kernel(const
         }
         const int U = a.U;
         const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
-        ActPin pin;
-        if (!pin_activation(a, ch.call[0], base, (uint32_t)ci & 1u, unit, pin)) {
+        if (!pin_activation(a, ch.call[0], base, (uint32_t)ci & 1u)) {
             return;
         }
         if (ci == 0 && threadIdx.x == 0) {
@@ -871,7 +871,7 @@ __global__ void __launch_bounds__(32 * (kChainW + 2), 1) gemv_chain_kernel(const
         if (threadIdx.x == 0) {
             PIN_STAMP(2);
         }
-        if (!pin_consume(a, ch.call[0], tiles, red, bars, pin, slot, unit, pos)) {
+        if (!pin_consume(a, ch.call[0], tiles, red, bars, base + (uint32_t)ch.call[0].off_pack, slot, unit, pos)) {
             return;
         }
         if (threadIdx.x == 0) {

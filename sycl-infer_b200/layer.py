@@ -51,8 +51,11 @@ class DenseLayer:
         self.act_f = alloc_act(TB, n_ff, dev)
         # one token on one GPU: the gate|up GEMV leaves the quantized silu(gate)*up for the down call
         self.fused_h = TB == 1 and world == 1
-        # ... and o, gate|up and down (each consumes the previous one's output) go out as one launch
-        self.chain = self.fused_h
+        # True: o, gate|up and down (each consumes the previous one's output) go out as ONE launch
+        # (quant_gemv_chain).  Off by default: measured equal to three launches on its own (47.9 us
+        # against ~49) and slower in a step where it alternates with the q|k|v launch (73.7 us against
+        # 58.3): two large kernel images taking turns on the SMs cost more than the boundaries save.
+        self.chain = False
         self._staging = {}
 
     def weight_bytes(self):

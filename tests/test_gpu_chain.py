@@ -16,7 +16,7 @@ FULL = dict(hidden=5120, n_head=40, n_kv=8, head_dim=128, n_ff=17408)
 def _run(pkg, be, mix, kw, chain, steps, seed=21):
     from sycl_infer_b200.layer import DenseLayer
     ly = DenseLayer(be, mix, seed=seed, TB=1, **kw)
-    ly.chain = chain
+    ly.chain = chain  # the layer's default is separate launches
     x = torch.from_numpy(pkg.synth.make_activation(1, kw["hidden"], 31)).cuda()
     ly.attn.copy_(torch.from_numpy(pkg.synth.make_activation(1, kw["n_head"] * kw["head_dim"], 32)).cuda())
     out = torch.zeros(1, kw["hidden"], device="cuda")
