@@ -227,6 +227,17 @@ int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uin
                       const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
                       int n_ff_exp, int top_k);
 
+/* b200q_moe_gate_up followed by b200q_xq(h, NULL, h_stride, 0, h8, hmeta, hsumq, n_tok*top_k, n_ff_exp) as
+ * one call: the same h, and its quantization (group-major, TB = n_tok*top_k) for b200q_moe_down.  In the
+ * decode regime the expert kernel's epilogue quantizes each 32-value group of h as it completes and no
+ * quantizer launch runs (the reference quantizes h in a launch of its own, moe_actq_launch,
+ * kernels.h:626-627); otherwise this is the two launches.  n_ff_exp must be a multiple of 32. */
+int b200q_moe_gate_up_q(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
+                        size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                        const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                        const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                        int n_ff_exp, int top_k, int8_t * h8, float * hmeta, int32_t * hsumq);
+
 /* moe_grp_down_launch (kernels.h:718-721): acc[p*acc_stride + r] = down_e[r] . h_p on the pairs'
  * re-quantized intermediate (h8/hmeta/hsumq with TB = n_pairs, from b200q_xq on h). */
 int b200q_moe_down(void * stream, const void * dbank, uint32_t dtype, size_t slot_db, const int32_t * off,

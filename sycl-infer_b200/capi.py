@@ -77,6 +77,9 @@ _SIGS = {
     "b200q_moe_csr": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "b200q_moe_gate_up": (C.c_int, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp,
                                     C.c_int, _vp, _vp, _vp, C.c_int, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "b200q_moe_gate_up_q": (C.c_int, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp,
+                                      C.c_int, _vp, _vp, _vp, C.c_int, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
+                                      _vp]),
     "b200q_moe_down": (C.c_int, [_vp, _vp, C.c_uint32, C.c_size_t, _vp, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp,
                                  C.c_int, _vp, C.c_int, C.c_int, C.c_int]),
     "b200q_moe_reduce": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int]),

@@ -563,30 +563,59 @@ static int moe_check(const char * who, const void * bank, uint32_t type, int K, 
     return B200Q_OK;
 }
 
-int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
-                      size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
-                      const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
-                      const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
-                      int n_ff_exp, int top_k) {
-    int rc = moe_check("b200q_moe_gate_up", gbank, gtype, n_embd, n_ff_exp, off, pair, active, n_active);
+static int moe_gate_up_call(const char * who, void * stream, const void * gbank, const void * ubank, uint32_t gtype,
+                            uint32_t utype, size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                            const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                            const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                            int n_ff_exp, int top_k, const NextAct * hq) {
+    int rc = moe_check(who, gbank, gtype, n_embd, n_ff_exp, off, pair, active, n_active);
     if (rc == B200Q_OK) {
-        rc = moe_check("b200q_moe_gate_up", ubank, utype, n_embd, n_ff_exp, x8, xmeta, xsumq, h);
+        rc = moe_check(who, ubank, utype, n_embd, n_ff_exp, x8, xmeta, xsumq, h);
     }
     if (rc != B200Q_OK) {
         return rc;
     }
     if (!aligned(x8, 16) || !aligned(xmeta, 8) || !aligned(xsumq, 8)) {
-        set_error("b200q_moe_gate_up: x8 must be 16-byte aligned, xmeta and xsumq 8-byte aligned");
+        set_error("%s: x8 must be 16-byte aligned, xmeta and xsumq 8-byte aligned", who);
         return B200Q_EINVAL;
     }
     if (n_act_max < 1 || n_tok < 1 || top_k < 1 || h_stride < n_ff_exp || (slot_gb & 15) || (slot_ub & 15)) {
-        set_error("b200q_moe_gate_up: bad n_act_max/n_tok/top_k/h_stride or plane bytes not a multiple of 16");
+        set_error("%s: bad n_act_max/n_tok/top_k/h_stride or plane bytes not a multiple of 16", who);
         return B200Q_EINVAL;
     }
+    if (hq && (!hq->x8 || !hq->xmeta || !hq->xsumq || !aligned(hq->x8, 16) || !aligned(hq->xmeta, 8) ||
+               !aligned(hq->xsumq, 8) || (n_ff_exp & 31))) {
+        set_error("%s: h8/hmeta/hsumq must be non-null and aligned (16/8/8 bytes), n_ff_exp a multiple of 32", who);
+        return B200Q_EINVAL;
+    }
+    const bool inside = hq && moe_rows_takes_pinned((int)gtype, (int)utype, n_embd, n_ff_exp, 1, n_tok, top_k, n_act_max, true);
     B200Q_CUDA_OK(launch_moe_rows((cudaStream_t)stream, gbank, ubank, (int)gtype, (int)utype, slot_gb, slot_ub, off,
                                   pair, active, n_active, n_act_max, x8, xmeta, xsumq, n_tok, top_k, n_embd, n_ff_exp,
-                                  h, h_stride, 1));
+                                  h, h_stride, 1, inside ? hq : nullptr));
+    if (hq && !inside) { // the kernel that served this shape leaves h in fp32 only
+        B200Q_CUDA_OK(launch_xq((cudaStream_t)stream, h, nullptr, h_stride, h_stride, hq->x8, hq->xmeta, hq->xsumq,
+                                n_tok * top_k, n_ff_exp, false));
+    }
     return B200Q_OK;
+}
+
+int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
+                      size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                      const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                      const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                      int n_ff_exp, int top_k) {
+    return moe_gate_up_call("b200q_moe_gate_up", stream, gbank, ubank, gtype, utype, slot_gb, slot_ub, off, pair, active,
+                            n_active, n_act_max, x8, xmeta, xsumq, n_tok, h, h_stride, n_embd, n_ff_exp, top_k, nullptr);
+}
+
+int b200q_moe_gate_up_q(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
+                        size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
+                        const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                        const float * xmeta, const int32_t * xsumq, int n_tok, float * h, int h_stride, int n_embd,
+                        int n_ff_exp, int top_k, int8_t * h8, float * hmeta, int32_t * hsumq) {
+    const NextAct hq{h8, hmeta, hsumq};
+    return moe_gate_up_call("b200q_moe_gate_up_q", stream, gbank, ubank, gtype, utype, slot_gb, slot_ub, off, pair, active,
+                            n_active, n_act_max, x8, xmeta, xsumq, n_tok, h, h_stride, n_embd, n_ff_exp, top_k, &hq);
 }
 
 int b200q_moe_down(void * stream, const void * dbank, uint32_t dtype, size_t slot_db, const int32_t * off,

@@ -1174,3 +1174,5 @@ cudaError_t read_pin_status(int * status, bool clear) {
 }
 
 } // namespace b200q
+
+#include "moe_pinned.cuh"

@@ -50,7 +50,7 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
                             size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
                             const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                             const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
-                            float * out, int out_stride, int fuse_silu);
+                            float * out, int out_stride, int fuse_silu, const NextAct * hq = nullptr);
 // streaming form of the grouped expert rows (decode: a few routed tokens per expert)
 bool moe_stream_supported(int type_a, int type_b, int K, int n_rows, int fuse_silu);
 cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
@@ -58,6 +58,17 @@ cudaError_t launch_moe_stream(cudaStream_t s, const void * bank_a, const void * 
                               const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                               const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
                               float * out, int out_stride, int fuse_silu);
+// grouped expert rows on the pinned-activation kernel (moe_pinned.cuh): every routed pair as a GEMV of
+// its own; hq != nullptr (gate|up only): also emits h quantized for the down launch
+bool moe_pinned_supported(int type_a, int type_b, int K, int n_rows, int fuse_silu, long long n_pairs, bool want_hq);
+cudaError_t launch_moe_pinned(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
+                              size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
+                              const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                              const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
+                              float * out, int out_stride, int fuse_silu, const NextAct * hq);
+// which kernel launch_moe_rows picks for a shape: true = the pinned one (which can emit hq itself)
+bool moe_rows_takes_pinned(int type_a, int type_b, int K, int n_rows, int fuse_silu, int TB, int top_k, int n_act_max,
+                           bool want_hq = false);
 cudaError_t read_moe_status(int * status, bool clear);
 cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
                               int acc_stride, float * out, int out_stride);

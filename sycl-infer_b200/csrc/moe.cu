@@ -13,71 +13,96 @@
 namespace b200q {
 
 // ---- router --------------------------------------------------------------------------------
-// Logits gate_inp . x with double accumulation: one CTA per expert, its warps splitting K, up to
-// kRouteTok tokens per pass - a router row is read once for all tokens, every load of a pass is
-// independent, and the grid covers the experts (a CTA per token would leave most SMs idle and
-// re-read the whole router for every token).
+// Logits gate_inp . x with double accumulation: one CTA per kRouteExp experts, its warps splitting
+// K, up to kRouteTok tokens per pass.  Every load of a sweep is independent of the others (the
+// kernel is bound by memory latency, not by the fp64 pipe), a router row is read once for all
+// tokens, and an activation row once per kRouteExp experts: with a CTA per expert the 256 CTAs of
+// a 256-expert router re-read the same 128 KB of activations 256 times, and that L2 traffic
+// (32 MB against 2 MB of router weights) was most of the kernel's time.
 constexpr int kRouteTok = 16;
+constexpr int kRouteExp = 2;
 __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
                                                          int x_stride, int n_tok, int n_embd, int n_expert,
                                                          float * __restrict__ logits) {
     // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ double part[8][kRouteTok];
-    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float * w = gate_inp + (size_t)e * n_embd;
+    __shared__ double part[8][kRouteExp][kRouteTok];
+    const int e0 = blockIdx.x * kRouteExp, ne = min(kRouteExp, n_expert - e0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float * w = gate_inp + (size_t)e0 * n_embd;
+    const bool vec = (n_embd & 3) == 0 && (x_stride & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+    const int n_vec = vec ? n_embd : 0;
     for (int t0 = 0; t0 < n_tok; t0 += kRouteTok) {
-        double a[kRouteTok];
+        double a[kRouteExp][kRouteTok];
 #pragma unroll
-        for (int i = 0; i < kRouteTok; i++) {
-            a[i] = 0.0;
+        for (int j = 0; j < kRouteExp; j++) {
+#pragma unroll
+            for (int i = 0; i < kRouteTok; i++) {
+                a[j][i] = 0.0;
+            }
         }
-        // four values per load, every load of a sweep independent of the others: the kernel is
-        // bound by memory latency, not by the fp64 pipe
-        const bool vec = (n_embd & 3) == 0 && (x_stride & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
-        const int n_vec = vec ? n_embd : 0;
         for (int k = 4 * threadIdx.x; k < n_vec; k += 4 * 256) {
-            const float4 wk = __ldg(reinterpret_cast<const float4 *>(w + k));
-            float4 xv[kRouteTok];
+            float4 xv[kRouteTok], wk[kRouteExp];
+#pragma unroll
+            for (int j = 0; j < kRouteExp; j++) {
+                wk[j] = j < ne ? __ldg(reinterpret_cast<const float4 *>(w + (size_t)j * n_embd + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
             for (int i = 0; i < kRouteTok; i++) {
                 xv[i] = t0 + i < n_tok ? __ldg(reinterpret_cast<const float4 *>(x + (size_t)(t0 + i) * x_stride + k))
                                        : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int i = 0; i < kRouteTok; i++) { // element order k, k+1, k+2, k+3 within a thread
-                a[i] += (double)wk.x * (double)xv[i].x;
-                a[i] += (double)wk.y * (double)xv[i].y;
-                a[i] += (double)wk.z * (double)xv[i].z;
-                a[i] += (double)wk.w * (double)xv[i].w;
+            for (int j = 0; j < kRouteExp; j++) {
+                if (j < ne) { // uniform
+#pragma unroll
+                    for (int i = 0; i < kRouteTok; i++) { // element order k, k+1, k+2, k+3 within a thread
+                        a[j][i] += (double)wk[j].x * (double)xv[i].x;
+                        a[j][i] += (double)wk[j].y * (double)xv[i].y;
+                        a[j][i] += (double)wk[j].z * (double)xv[i].z;
+                        a[j][i] += (double)wk[j].w * (double)xv[i].w;
+                    }
+                }
             }
         }
         for (int k = n_vec + threadIdx.x; k < n_embd; k += 256) {
-            const double wk = (double)__ldg(w + k);
 #pragma unroll
-            for (int i = 0; i < kRouteTok; i++) {
-                if (t0 + i < n_tok) { // uniform
-                    a[i] += wk * (double)__ldg(x + (size_t)(t0 + i) * x_stride + k);
+            for (int j = 0; j < kRouteExp; j++) {
+                if (j < ne) {
+                    const double wkj = (double)__ldg(w + (size_t)j * n_embd + k);
+#pragma unroll
+                    for (int i = 0; i < kRouteTok; i++) {
+                        if (t0 + i < n_tok) { // uniform
+                            a[j][i] += wkj * (double)__ldg(x + (size_t)(t0 + i) * x_stride + k);
+                        }
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int i = 0; i < kRouteTok; i++) {
-            for (int o = 16; o > 0; o >>= 1) {
-                a[i] += __shfl_xor_sync(0xFFFFFFFFu, a[i], o);
-            }
-            if (lane == 0) {
-                part[warp][i] = a[i];
+        for (int j = 0; j < kRouteExp; j++) {
+#pragma unroll
+            for (int i = 0; i < kRouteTok; i++) {
+                for (int o = 16; o > 0; o >>= 1) {
+                    a[j][i] += __shfl_xor_sync(0xFFFFFFFFu, a[j][i], o);
+                }
+                if (lane == 0) {
+                    part[warp][j][i] = a[j][i];
+                }
             }
         }
         __syncthreads();
-        if (threadIdx.x < kRouteTok && t0 + (int)threadIdx.x < n_tok) {
-            double sum = 0.0;
-            for (int j = 0; j < 8; j++) { // fixed order
-                sum += part[j][threadIdx.x];
+        if (threadIdx.x < kRouteExp * kRouteTok) {
+            const int j = threadIdx.x / kRouteTok, i = threadIdx.x % kRouteTok;
+            if (j < ne && t0 + i < n_tok) {
+                double sum = 0.0;
+                for (int q = 0; q < 8; q++) { // fixed order
+                    sum += part[q][j][i];
+                }
+                logits[(size_t)(t0 + i) * n_expert + e0 + j] = (float)sum;
             }
-            logits[(size_t)(t0 + threadIdx.x) * n_expert + e] = (float)sum;
         }
         __syncthreads();
     }
@@ -182,12 +207,17 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
         p[e] = lg[e];
     }
     __syncthreads();
-    if (tid == 0) {
+    if (tid < 32) { // the maximum is exact in any order
         float mx = -3.402823466e38f;
-        for (int e = 0; e < n_expert; e++) {
+        for (int e = tid; e < n_expert; e += 32) {
             mx = fmaxf(mx, p[e]);
         }
-        s_max = mx;
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        }
+        if (tid == 0) {
+            s_max = mx;
+        }
     }
     __syncthreads();
     for (int e = tid; e < n_expert; e += blockDim.x) {
@@ -195,9 +225,20 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
     }
     __syncthreads();
     if (tid == 0) {
+        // expert order, like the reference's sum; sixteen loads in flight ahead of the chain of adds
         float sum = 0.f;
-        for (int e = 0; e < n_expert; e++) {
-            sum = __fadd_rn(sum, p[e]);
+        for (int e0 = 0; e0 < n_expert; e0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                v[j] = p[min(e0 + j, n_expert - 1)];
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                if (e0 + j < n_expert) {
+                    sum = __fadd_rn(sum, v[j]);
+                }
+            }
         }
         s_inv = __fdiv_rn(1.f, sum);
     }
@@ -219,9 +260,19 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
     __syncthreads();
     if (tid == 0) {
         float wsum = 0.f;
-        for (int e = 0; e < n_expert; e++) { // expert order, like the reference's accumulation
-            if (sel[e] >= 0) {
-                wsum = __fadd_rn(wsum, p[e]);
+        for (int e0 = 0; e0 < n_expert; e0 += 16) { // expert order, like the reference's accumulation
+            float v[16];
+            int sl[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                v[j] = p[min(e0 + j, n_expert - 1)];
+                sl[j] = sel[min(e0 + j, n_expert - 1)];
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                if (e0 + j < n_expert && sl[j] >= 0) {
+                    wsum = __fadd_rn(wsum, v[j]);
+                }
             }
         }
         s_den = fmaxf(wsum, 6.103515625e-5f);
@@ -400,7 +451,7 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
                              int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts,
                              int32_t * off, int32_t * pair, int32_t * active, int32_t * n_active) {
     if (gate_inp) {
-        cudaError_t e = launch_chained(s, moe_logits_kernel, dim3((unsigned)n_expert), dim3(256), 0, gate_inp, x, x_stride, n_tok,
+        cudaError_t e = launch_chained(s, moe_logits_kernel, dim3((unsigned)((n_expert + kRouteExp - 1) / kRouteExp)), dim3(256), 0, gate_inp, x, x_stride, n_tok,
                                        n_embd, n_expert, logits);
         if (e != cudaSuccess) {
             return e;
@@ -424,13 +475,36 @@ cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int
                           in_smem);
 }
 
+bool moe_rows_takes_pinned(int type_a, int type_b, int K, int n_rows, int fuse_silu, int TB, int top_k, int n_act_max,
+                           bool want_hq) {
+#ifdef B200Q_TUNING
+    static const bool off = [] {
+        const char * e = getenv("B200Q_MOE_KERNEL");
+        return e && (strcmp(e, "stream") == 0 || strcmp(e, "rows") == 0);
+    }();
+    if (off) {
+        return false;
+    }
+#endif
+    const long long n_pairs = top_k > 0 ? (long long)TB * top_k : TB;
+    return n_pairs <= 4LL * n_act_max && moe_pinned_supported(type_a, type_b, K, n_rows, fuse_silu, n_pairs, want_hq);
+}
+
 cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
                             size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
                             const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                             const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
-                            float * out, int out_stride, int fuse_silu) {
-    // decode (at most a few routed tokens per expert on average): the streaming kernel
+                            float * out, int out_stride, int fuse_silu, const NextAct * hq) {
+    // decode (at most a few routed tokens per expert on average): every pair as a GEMV of its own on
+    // the pinned-activation kernel; shapes it does not take: the streaming kernel
     const long long n_pairs = top_k > 0 ? (long long)TB * top_k : TB;
+    if (moe_rows_takes_pinned(type_a, type_b, K, n_rows, fuse_silu, TB, top_k, n_act_max, hq != nullptr)) {
+        return launch_moe_pinned(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max,
+                                 x8, xmeta, xsumq, TB, top_k, K, n_rows, out, out_stride, fuse_silu, hq);
+    }
+    if (hq) { // only the pinned kernel quantizes h itself; callers ask moe_rows_takes_pinned first
+        return cudaErrorInvalidConfiguration;
+    }
     if (n_pairs <= 4LL * n_act_max && n_act_max <= 1023 && moe_stream_supported(type_a, type_b, K, n_rows, fuse_silu)) {
         return launch_moe_stream(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max,
                                  x8, xmeta, xsumq, TB, top_k, K, n_rows, out, out_stride, fuse_silu);

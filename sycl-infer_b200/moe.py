@@ -104,6 +104,18 @@ def moe_grp_gate_up_launch(be, M, off, pair, active, n_active, n_act_max, x8, xm
     return True
 
 
+def moe_grp_gate_up_q_launch(be, M, off, pair, active, n_active, n_act_max, x8, xmeta, xsumq, n_tok, h, h_stride, h8,
+                             hmeta, hsumq):
+    """moe_grp_gate_up_launch that also leaves h quantized for the down launch (no quantizer launch
+    in between where the expert kernel can do it in its epilogue)."""
+    be.lib.check(be.lib.moe_gate_up_q(be._s(), _ptr(M.gate_exps), _ptr(M.up_exps), M.gate_type, M.up_type,
+                                      C.c_size_t(M.slot_gb), C.c_size_t(M.slot_ub), _ptr(off), _ptr(pair),
+                                      _ptr(active), _ptr(n_active), n_act_max, _ptr(x8), _ptr(xmeta), _ptr(xsumq),
+                                      n_tok, _ptr(h), h_stride, M.n_embd, M.n_ff_exp, M.top_k, _ptr(h8), _ptr(hmeta),
+                                      _ptr(hsumq)))
+    return True
+
+
 def moe_grp_down_launch(be, M, off, pair, active, n_active, n_act_max, h8, hmeta, hsumq, n_pairs, acc, acc_stride):
     be.lib.check(be.lib.moe_down(be._s(), _ptr(M.down_exps), M.down_type, C.c_size_t(M.slot_db), _ptr(off),
                                  _ptr(pair), _ptr(active), _ptr(n_active), n_act_max, _ptr(h8), _ptr(hmeta),
@@ -116,15 +128,22 @@ def moe_reduce_launch(be, acc, wts, top_k, n_tok, n_embd, acc_stride, out, out_s
                                    out_stride))
 
 
-def moe_call(be, M: moe_t, S: MoeScratch, x, n_tok, out, logits_given=False):
-    """One routed-MoE FFN: out[t] += sum_j w[t,j] * expert_{ids[t,j]}(x[t])."""
+def moe_call(be, M: moe_t, S: MoeScratch, x, n_tok, out, logits_given=False, fused_hq=False):
+    """One routed-MoE FFN: out[t] += sum_j w[t,j] * expert_{ids[t,j]}(x[t]).
+    fused_hq: gate|up also quantizes h (one launch less; measured slower than the quantizer launch
+    at config 3's size, so off by default)."""
     n_pairs = n_tok * M.top_k
     n_act_max = min(M.n_expert, n_pairs)
+    # the token quantizer does not depend on the router: it goes first
+    moe_actq_launch(be, x, x.shape[1], n_tok, M.n_embd, *S.xq)
     moe_router_csr_launch(be, None if logits_given else M.gate_inp, 0, x, x.shape[1], n_tok, M.n_embd, M.n_expert,
                           M.top_k, S.logits, S.ids, S.wts, S.off, S.pair, S.active, S.n_active)
-    moe_actq_launch(be, x, x.shape[1], n_tok, M.n_embd, *S.xq)
-    moe_grp_gate_up_launch(be, M, S.off, S.pair, S.active, S.n_active, n_act_max, *S.xq, n_tok, S.h, M.n_ff_exp)
-    moe_actq_launch(be, S.h, M.n_ff_exp, n_pairs, M.n_ff_exp, *S.hq)
+    if fused_hq and M.n_ff_exp % 32 == 0:
+        moe_grp_gate_up_q_launch(be, M, S.off, S.pair, S.active, S.n_active, n_act_max, *S.xq, n_tok, S.h, M.n_ff_exp,
+                                 *S.hq)
+    else:
+        moe_grp_gate_up_launch(be, M, S.off, S.pair, S.active, S.n_active, n_act_max, *S.xq, n_tok, S.h, M.n_ff_exp)
+        moe_actq_launch(be, S.h, M.n_ff_exp, n_pairs, M.n_ff_exp, *S.hq)
     moe_grp_down_launch(be, M, S.off, S.pair, S.active, S.n_active, n_act_max, *S.hq, n_pairs, S.acc, M.n_embd)
     moe_reduce_launch(be, S.acc, S.wts, M.top_k, n_tok, M.n_embd, M.n_embd, out, out.shape[1])
     return out
