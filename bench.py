@@ -156,6 +156,7 @@ class Ctx:
         self.side = torch.cuda.Stream()
         self.peaks, self.peak_source = measured_peaks()
         self.args = args
+        self.ceilings = {}
 
     def barrier(self):
         if self.world > 1:
@@ -270,6 +271,28 @@ def cell_layer(ctx, name, mix, TB, L=4, steps=40):
             "l2": f"{L} rotating weight sets", "clocks": clocks}
 
 
+def measure_ceilings(ctx):
+    """The two ceilings a copy benchmark and a bf16 GEMM do not give (library instruments): one pass of
+    16-byte loads over 2 GiB, and tcgen05 kind::i8 products with shared-memory-resident operands."""
+    import ctypes as C
+    torch, be = ctx.torch, ctx.be
+    nbytes = 2 << 30
+    buf = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    buf.fill_(7)
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bp, sp = C.c_void_p(buf.data_ptr()), C.c_void_p(sink.data_ptr())
+    ms = ctx.time_ms(lambda i: be.lib.check(be.lib.probe_hbm_read(be._s(), bp, C.c_size_t(nbytes), sp)), 5, warm=2)
+    read_gbs = 5 * nbytes / (ms * 1e-3) / 1e9
+    iters = 20000
+    ms2 = ctx.time_ms(lambda i: be.lib.check(be.lib.probe_i8_mma(be._s(), iters, sp)), 3, warm=1)
+    sms = torch.cuda.get_device_properties(ctx.local).multi_processor_count
+    tops = 3.0 * sms * iters * 2 * 128 * 256 * 32 / (ms2 * 1e-3) / 1e12
+    ok = int(sink.cpu()[0]) == 0 and be.device_status() == 0
+    del buf
+    return {"hbm_read_gbs": read_gbs if ok else None, "i8_mma_tops": tops if ok else None,
+            "how": "b200q_probe_hbm_read over 2 GiB; b200q_probe_i8_mma, 128x256x32 kind::i8, 20000 per SM; CUDA events"}
+
+
 def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
     """Config 2: M tokens x (Q4_K weight of `rows` x K); quantizer + tensor-core GEMM per iteration."""
     torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
@@ -285,8 +308,8 @@ def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
     nbytes = w.numel() + 4 * M * K + 4 * M * rows
     return {"cell": name, "us": us, "int8_ops": ops, "Tops": ops / us / 1e6, "bytes": nbytes, "GB/s": nbytes / us / 1e3,
             "frac_of_measured_hbm": ctx.frac(nbytes / us / 1e3),
-            "frac_of_dense_peak": None, "note": "no measured int8 tcgen05 peak on record; bf16 cuBLAS peak x2 would be "
-            f"{2 * ctx.peaks.get('bf16_tflops', 0):.0f} T int8-op/s", "clocks": clocks}
+            "frac_of_i8_mma_peak": (ops / us / 1e6) / ctx.ceilings["i8_mma_tops"] if ctx.ceilings.get("i8_mma_tops") else None,
+            "clocks": clocks}
 
 
 def cell_moe(ctx, name, tokens=16, experts=256, topk=8, embd=2048, ff=512, copies=2, iters=20):
@@ -440,6 +463,7 @@ def gpu_arm(args):
         ms_gemv = ctx.time_ms(lambda i: gemv_only(), reps)
     clocks = sampler.summary()
 
+    ctx.ceilings = measure_ceilings(ctx) if world == 1 else {}
     cells = []
     if not args.no_cells:
         if world == 1:
@@ -481,12 +505,14 @@ def gpu_arm(args):
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": ctx.peaks["hbm_gbs"] , "unit": "GB/s",
                          "frac": achieved / ctx.peaks["hbm_gbs"],
+                         "frac_of_read_ceiling": achieved / ctx.ceilings["hbm_read_gbs"] if ctx.ceilings.get("hbm_read_gbs") else None,
                          "traffic": ncu_traffic_per_launch() if world == 1 else None, "traffic_source": TRAFFIC_NOTE,
                          "peak_source": ctx.peak_source,
                          "kernel": "gemv_pinned_kernel (one launch per call, 4 per layer), CUDA graph, pre-quantized activations",
                          "bytes_per_launch": alg_launch,
                          "weight_bytes_per_launch": pkg.synth.layer_weight_bytes("Q4_K_M") / 4.0 / world,
                          "us_per_launch": 1e3 * ms_gemv / n_launch},
+            "ceilings": ctx.ceilings,
             "cells": cells,
         }
         if world == 1 and not args.no_cpu:

@@ -283,6 +283,17 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
  * whose kernels have no device-side waits. */
 int b200q_device_status(int * status /*host*/, int clear);
 
+/* Measurement instruments (no reference counterpart): the ceilings a benchmark reports the kernels
+ * against.  The caller times them (events on `stream`).
+ * b200q_probe_hbm_read: one pass of independent 16-byte loads over buf[0, bytes) - what a kernel
+ *   that only READS can reach (a copy benchmark reads and writes).  Use a buffer far larger than L2.
+ * b200q_probe_i8_mma: on every SM, `iters` tensor-core products of 128 x 256 x 32 int8 (tcgen05
+ *   kind::i8, int32 accumulators in tensor memory) with both operands resident in shared memory and
+ *   nothing else in flight: 2 * 128 * 256 * 32 * iters * (SM count) integer operations.
+ * sink: a device word the kernels may bump (keeps the work alive; reports a wait that ran out). */
+int b200q_probe_hbm_read(void * stream, const void * buf, size_t bytes, uint32_t * sink);
+int b200q_probe_i8_mma(void * stream, int iters, uint32_t * sink);
+
 /* compute_backend::synchronize (src/backend/backend.h:123): blocks until the stream drained. */
 int b200q_synchronize(void * stream);
 

@@ -86,6 +86,8 @@ _SIGS = {
     "b200q_quant_gemv_static": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_block_dots": (C.c_int, [_vp, _vp, C.c_uint32, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]),
     "b200q_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "b200q_probe_hbm_read": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
+    "b200q_probe_i8_mma": (C.c_int, [_vp, C.c_int, _vp]),
     "b200q_synchronize": (C.c_int, [_vp]),
 }
 

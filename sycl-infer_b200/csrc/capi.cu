@@ -677,9 +677,30 @@ int b200q_device_status(int * status, int clear) {
     int frag = 0;
     B200Q_CUDA_OK(read_frag_status(&frag, clear != 0));
     *status = *status ? *status : frag;
+    int probe = 0;
+    B200Q_CUDA_OK(read_probe_status(&probe, clear != 0));
+    *status = *status ? *status : probe;
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }
+    return B200Q_OK;
+}
+
+int b200q_probe_hbm_read(void * stream, const void * buf, size_t bytes, uint32_t * sink) {
+    if (!buf || !sink || bytes < 16 || !aligned(buf, 16)) {
+        set_error("b200q_probe_hbm_read: buf (16-byte aligned, at least 16 bytes) and sink must be non-null");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_probe_read((cudaStream_t)stream, buf, bytes, sink));
+    return B200Q_OK;
+}
+
+int b200q_probe_i8_mma(void * stream, int iters, uint32_t * sink) {
+    if (!sink || iters < 1 || iters > (1 << 24)) {
+        set_error("b200q_probe_i8_mma: sink must be non-null, 1 <= iters <= 2^24");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_probe_i8_mma((cudaStream_t)stream, iters, sink));
     return B200Q_OK;
 }
 

@@ -73,6 +73,11 @@ cudaError_t read_moe_status(int * status, bool clear);
 cudaError_t launch_moe_reduce(cudaStream_t s, const float * acc, const float * wts, int top_k, int n_tok, int n_embd,
                               int acc_stride, float * out, int out_stride);
 
+// measurement instruments (probes.cu)
+cudaError_t launch_probe_read(cudaStream_t s, const void * buf, size_t bytes, uint32_t * sink);
+cudaError_t launch_probe_i8_mma(cudaStream_t s, int iters, uint32_t * sink);
+cudaError_t read_probe_status(int * status, bool clear);
+
 cudaError_t launch_peer_barrier(cudaStream_t s, uint32_t * const * flags, int world, int rank, uint32_t seq);
 cudaError_t read_peer_status(int * status, bool clear);
 
