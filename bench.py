@@ -439,10 +439,24 @@ def gpu_arm(args):
     hx = [xin[i].cpu().pin_memory() for i in range(L)]
     hout = torch.zeros(1, hidden, dtype=torch.float32).pin_memory()
 
+    # A decode step as an engine would replay it: ONE graph holding the pinned-host -> device copy of
+    # the step's inputs, the layer's launches and the device -> pinned-host copy of its output; the
+    # host waits for the result every step (the next token depends on it).
+    e2e_graphs = []
+    if graphs and world == 1:
+        def whole(i):
+            xin[i].copy_(hx[i], non_blocking=True)
+            layers[i].forward(xs[i], out)
+            hout.copy_(out, non_blocking=True)
+        e2e_graphs = [ctx.capture(lambda i=i: whole(i)) for i in range(L)]
+
     def e2e_step(i):
-        xin[i % L].copy_(hx[i % L], non_blocking=True)
-        step(i)
-        hout.copy_(out, non_blocking=True)
+        if e2e_graphs:
+            e2e_graphs[i % L].replay()
+        else:
+            xin[i % L].copy_(hx[i % L], non_blocking=True)
+            step(i)
+            hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     ms_e2e = ctx.time_ms(e2e_step, args.steps)
