@@ -293,6 +293,31 @@ def measure_ceilings(ctx):
             "how": "b200q_probe_hbm_read over 2 GiB; b200q_probe_i8_mma, 128x256x32 kind::i8, 20000 per SM; CUDA events"}
 
 
+def cell_token(ctx, layers, n_layers=LAYERS_PER_TOKEN, iters=10):
+    """A whole decode token as one replayed graph: n_layers layer steps, each layer's input the
+    previous layer's output, the weight sets of `layers` cycled (1.7 GB in total: a set is evicted
+    from L2 long before its next use)."""
+    torch = ctx.torch
+    L, hidden = len(layers), layers[0].hidden
+    a = torch.from_numpy(ctx.pkg.synth.make_activation(1, hidden, 77)).cuda()
+    bufs = [a.clone(), torch.zeros(1, hidden, device="cuda")]
+
+    def token():
+        bufs[0].copy_(a)
+        for i in range(n_layers):
+            layers[i % L].forward(bufs[i & 1], bufs[(i + 1) & 1])
+    g = ctx.capture(token)
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: g.replay(), iters))
+    us = 1e3 * ms / iters
+    ok = bool(torch.isfinite(bufs[n_layers & 1]).all()) and ctx.be.device_status() == 0
+    nbytes = n_layers * layer_bytes(ctx.pkg, "Q4_K_M", 1, layers[0])
+    gbs = nbytes / us / 1e3
+    return {"cell": f"config 1: one decode token = {n_layers} chained layer steps in one graph, Q4_K_M, batch 1",
+            "us": us, "us_per_layer": us / n_layers, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": ctx.frac(gbs),
+            "tok_s": 1e6 / us, "finite_and_status_clean": ok, "launches_per_iter": n_layers * layers[0].launches_per_step(),
+            "l2": f"{L} weight sets of 210 MB cycled", "clocks": clocks}
+
+
 def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
     """Config 2: M tokens x (Q4_K weight of `rows` x K); quantizer + tensor-core GEMM per iteration."""
     torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
@@ -431,9 +456,26 @@ def gpu_arm(args):
         else:
             layers[i % L].forward(xs[i % L], out)
 
+    # The engine this path plugs into replays one recorded graph per decode TOKEN (all its layers),
+    # not one per layer: the timed K steps therefore run as graphs of L consecutive layer steps
+    # (K // L replays) plus K % L single-step graphs - the same K steps, the same launches, without a
+    # graph-launch gap after every layer.
+    span = None
+    if graphs and not args.step_graphs:
+        span = ctx.capture(lambda: [layers[i].forward(xs[i], out) for i in range(L)])
+
+    def run_steps(n):
+        """Device time (ms) of exactly n layer steps."""
+        if span is None:
+            return ctx.time_ms(step, n, warm=max(args.warmup, 3))
+        q, r = divmod(n, L)
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        return ctx.time_ms(lambda j: span.replay() if j < q else graphs[j - q].replay(), q + r, warm=1)
+
     sampler = ClockSampler(ctx.local)
     sampler.start()
-    ms = ctx.time_ms(step, args.steps, warm=max(args.warmup, 3))
+    ms = run_steps(args.steps)
 
     # ---- e2e: host buffers, pinned H2D of the step's activations, D2H of its output, every step
     hx = [xin[i].cpu().pin_memory() for i in range(L)]
@@ -481,6 +523,7 @@ def gpu_arm(args):
     cells = []
     if not args.no_cells:
         if world == 1:
+            safe(cells, cell_token, ctx, layers)
             safe(cells, cell_single_matrix, ctx, "config 0: Q4_K 4096x4096 GEMV, batch 1", 12, 4096, 4096)
             safe(cells, cell_layer, ctx, "config 1: dense layer Q4_K_M, batch 16", "Q4_K_M", 16)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=512 x 5120 x 17408 Q4_K", 512)
@@ -505,7 +548,7 @@ def gpu_arm(args):
             "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": per_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
-            "config": {"workload": WORKLOAD, "launch": "cuda graph per step" if graphs else "host launches",
+            "config": {"workload": WORKLOAD, "launch": (f"cuda graph of {L} consecutive layer steps" if span is not None else "cuda graph per step") if graphs else "host launches",
                        "l2": f"inputs larger than L2: {L} rotating weight sets of 210 MB", "bytes_per_step": step_bytes,
                        "parallelism": (f"row-sharded x{world}, " + ("peer-store epilogue, flag exchange inside the GEMV kernels"
                                                                    if arena is not None else "NCCL all-gather"))
@@ -549,6 +592,7 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: GEMV epilogue stores rows on every GPU (peer), or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels from the host instead of CUDA graphs")
+    ap.add_argument("--step-graphs", action="store_true", help="one CUDA graph per layer step instead of one per L steps")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", 0)) != 0:
