@@ -166,6 +166,27 @@ __device__ __forceinline__ void csr_build(const int32_t * ids, int n_pairs, int 
         if (act[e + 1] > act[e]) {
             active[act[e]] = e; // increasing expert order
         }
+    }
+    if (ids_in_smem && n_pairs <= 1024) {
+        // a thread per pair: its place in its expert's list is the number of earlier pairs of the
+        // same expert (a uniform scan of shared memory; the same lists as the loop below)
+        for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+            const int e = idv[i];
+            if (e < 0 || e >= n_expert) {
+                continue;
+            }
+            int before = 0, j = 0;
+            for (; j + 4 <= i; j += 4) {
+                before += (idv[j] == e) + (idv[j + 1] == e) + (idv[j + 2] == e) + (idv[j + 3] == e);
+            }
+            for (; j < i; j++) {
+                before += idv[j] == e;
+            }
+            pair[cnt[e] + before] = i;
+        }
+        return;
+    }
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
         int o = cnt[e];
         const int end = cnt[e + 1];
         for (int i = 0; i < n_pairs && o < end; i++) { // deterministic fill in pair order
@@ -189,20 +210,33 @@ __global__ void __launch_bounds__(256) moe_csr_kernel(const int32_t * __restrict
 // Softmax and top-k of one token's logits (one CTA per token); the logits come from memory.
 // With `off` set, the CTA that finishes last also builds the token -> expert CSR (one launch less).
 __device__ unsigned int g_route_done = 0;
+#ifdef B200Q_TUNING
+__device__ unsigned long long * g_route_trace = nullptr; // [CTA][16] globaltimer stamps (set by the host, A/B only)
+#define ROUTE_STAMP(k)                                                                                       \
+    if (threadIdx.x == 0 && g_route_trace) {                                                                 \
+        unsigned long long t_;                                                                               \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                              \
+        g_route_trace[blockIdx.x * 16 + (k)] = t_;                                                           \
+    }
+#else
+#define ROUTE_STAMP(k)
+#endif
 __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict__ x, int x_stride, int n_embd,
                                                         int n_expert, int top_k, float * __restrict__ logits,
                                                         int32_t * ids, float * __restrict__ wts, int32_t * off,
                                                         int32_t * pair, int32_t * active, int32_t * n_active,
                                                         int ids_in_smem) {
     // chained launch: let the next kernel start its prologue, then wait for the producers of this one's inputs
+    ROUTE_STAMP(0);
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    extern __shared__ float p[]; // n_expert probabilities, then n_expert selection flags
+    ROUTE_STAMP(1);
+    extern __shared__ __align__(16) float p[]; // n_expert probabilities, then n_expert selection flags
     int * sel = reinterpret_cast<int *>(p + n_expert);
     __shared__ float s_max, s_inv, s_den;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     float * lg = logits + (size_t)t * n_expert;
-    (void)x, (void)x_stride, (void)n_embd, (void)lane, (void)warp, (void)nw;
+    (void)x, (void)x_stride, (void)n_embd;
     for (int e = tid; e < n_expert; e += blockDim.x) {
         p[e] = lg[e];
     }
@@ -220,10 +254,12 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
         }
     }
     __syncthreads();
+    ROUTE_STAMP(2);
     for (int e = tid; e < n_expert; e += blockDim.x) {
         p[e] = (float)exp((double)__fsub_rn(p[e], s_max)); // one rounding: a correctly rounded expf
     }
     __syncthreads();
+    ROUTE_STAMP(3);
     if (tid == 0) {
         // expert order, like the reference's sum; sixteen loads in flight ahead of the chain of adds
         float sum = 0.f;
@@ -243,12 +279,15 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
         s_inv = __fdiv_rn(1.f, sum);
     }
     __syncthreads();
+    ROUTE_STAMP(4);
     for (int e = tid; e < n_expert; e += blockDim.x) {
         p[e] = __fmul_rn(p[e], s_inv);
         lg[e] = p[e]; // the reference leaves the probabilities in its logits scratch
     }
     __syncthreads();
+    ROUTE_STAMP(5);
     for (int e = tid; e < n_expert; e += blockDim.x) {
+        // rank = experts that beat this one: larger probability, or equal and a lower index
         const float pe = p[e];
         int rank = 0;
         for (int f = 0; f < n_expert; f++) {
@@ -258,24 +297,31 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
         sel[e] = rank < top_k ? rank : -1;
     }
     __syncthreads();
-    if (tid == 0) {
+    ROUTE_STAMP(6);
+    {
+        // the sum of the selected probabilities in expert order, like the reference's accumulation:
+        // every warp marks its selected experts in a mask, one thread walks the marks
+        __shared__ uint32_t s_mask[8];
         float wsum = 0.f;
-        for (int e0 = 0; e0 < n_expert; e0 += 16) { // expert order, like the reference's accumulation
-            float v[16];
-            int sl[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                v[j] = p[min(e0 + j, n_expert - 1)];
-                sl[j] = sel[min(e0 + j, n_expert - 1)];
+        for (int e0 = 0; e0 < n_expert; e0 += blockDim.x) {
+            const int e = e0 + tid;
+            const uint32_t m = __ballot_sync(0xFFFFFFFFu, e < n_expert && sel[e] >= 0);
+            if (lane == 0) {
+                s_mask[warp] = m;
             }
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                if (e0 + j < n_expert && sl[j] >= 0) {
-                    wsum = __fadd_rn(wsum, v[j]);
+            __syncthreads();
+            if (tid == 0) {
+                for (int w = 0; w < nw; w++) {
+                    for (uint32_t mm = s_mask[w]; mm; mm &= mm - 1) {
+                        wsum = __fadd_rn(wsum, p[e0 + 32 * w + __ffs((int)mm) - 1]);
+                    }
                 }
             }
+            __syncthreads();
         }
-        s_den = fmaxf(wsum, 6.103515625e-5f);
+        if (tid == 0) {
+            s_den = fmaxf(wsum, 6.103515625e-5f);
+        }
     }
     __syncthreads();
     for (int e = tid; e < n_expert; e += blockDim.x) {
@@ -284,6 +330,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
             wts[(size_t)t * top_k + sel[e]] = __fdiv_rn(p[e], s_den);
         }
     }
+    ROUTE_STAMP(7);
     if (off) {
         __shared__ int s_last;
         __syncthreads(); // this CTA's ids are written
@@ -296,9 +343,12 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float * __restrict
             }
         }
         __syncthreads();
+        ROUTE_STAMP(8);
         if (s_last) {
             csr_build(ids, (int)gridDim.x * top_k, n_expert, off, pair, active, n_active, ids_in_smem,
                       reinterpret_cast<int32_t *>(p));
+            __syncthreads();
+            ROUTE_STAMP(9);
         }
     }
 }
@@ -457,6 +507,13 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
             return e;
         }
     }
+#ifdef B200Q_TUNING
+    {
+        const char * tp = getenv("B200Q_ROUTE_TRACE_PTR");
+        unsigned long long * ptr = tp ? reinterpret_cast<unsigned long long *>(strtoull(tp, nullptr, 0)) : nullptr;
+        cudaMemcpyToSymbolAsync(g_route_trace, &ptr, sizeof(ptr), 0, cudaMemcpyHostToDevice, s);
+    }
+#endif
     int in_smem = 0;
     size_t smem = (size_t)n_expert * 8;
     if (off) {
