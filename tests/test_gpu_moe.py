@@ -48,7 +48,7 @@ def test_router_from_logits(be, orc, pkg, n_tok, E, top_k):
     assert np.max(np.abs(logits.cpu().numpy() - p)) <= 1e-7
 
 
-def _run_moe(be, orc, pkg, E, top_k, n_embd, n_ff, n_tok, types, seed):
+def _run_moe(be, orc, pkg, E, top_k, n_embd, n_ff, n_tok, types, seed, fused_hq=False):
     from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_call
     host, dev = make_synthetic_moe(E, top_k, n_embd, n_ff, types, seed)
     x = pkg.synth.make_activation(n_tok, n_embd, seed + 50)
@@ -57,7 +57,7 @@ def _run_moe(be, orc, pkg, E, top_k, n_embd, n_ff, n_tok, types, seed):
     S = MoeScratch(dev, n_tok)
     S.logits.copy_(torch.from_numpy(lg))
     out = torch.from_numpy(base.copy()).cuda()
-    moe_call(be, dev, S, torch.from_numpy(x).cuda(), n_tok, out, logits_given=True)
+    moe_call(be, dev, S, torch.from_numpy(x).cuda(), n_tok, out, logits_given=True, fused_hq=fused_hq)
     be.synchronize()
     assert be.device_status() == 0
     # router
@@ -115,6 +115,33 @@ def test_moe_mixed_gate_up_types(be, orc, pkg, types):
     """gate and up planes of different types (separate row passes), and Q6_K planes whose rows are
     16-byte multiples only when K is a multiple of 2048."""
     _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=2048, n_ff=256, n_tok=3, types=types, seed=9)
+
+
+@pytest.mark.parametrize("cfg", [dict(E=8, top_k=2, n_embd=512, n_ff=256, n_tok=5, types=(12, 12, 12), seed=3),
+                                 dict(E=8, top_k=2, n_embd=512, n_ff=256, n_tok=5, types=(13, 13, 8), seed=4),
+                                 dict(E=16, top_k=4, n_embd=256, n_ff=256, n_tok=1, types=(12, 12, 12), seed=5),
+                                 dict(E=8, top_k=2, n_embd=2048, n_ff=256, n_tok=3, types=(12, 14, 12), seed=9),
+                                 dict(E=8, top_k=2, n_embd=512, n_ff=256, n_tok=40, types=(12, 12, 12), seed=7),
+                                 dict(E=256, top_k=8, n_embd=2048, n_ff=512, n_tok=16, types=(12, 12, 12), seed=0xB3)],
+                         ids=["q4k", "q5k_q8", "one_token", "mixed_types_two_launches", "many_tokens_two_launches", "config3"])
+def test_moe_gate_up_also_quantizes_h(be, orc, pkg, cfg):
+    """b200q_moe_gate_up_q: h and its quantization from one call - inside the expert kernel's
+    epilogue where the pinned kernel serves the shape, else as the two launches.  The harness holds
+    the emitted codes to the host quantizer of the SAME h, bit for bit, and runs down on them."""
+    _run_moe(be, orc, pkg, fused_hq=True, **cfg)
+
+
+def test_moe_gate_up_q_rejects_ragged_ffn(be, pkg):
+    """n_ff_exp not a multiple of 32: no whole quantization groups, EINVAL."""
+    from sycl_infer_b200.capi import B200QError
+    from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_grp_gate_up_q_launch
+    host, dev = make_synthetic_moe(4, 2, 256, 256, (12, 12, 12), 1)
+    S = MoeScratch(dev, 2)
+    import dataclasses
+    dev = dataclasses.replace(dev, n_ff_exp=250)
+    with pytest.raises(B200QError) as ei:
+        moe_grp_gate_up_q_launch(be, dev, S.off, S.pair, S.active, S.n_active, 4, *S.xq, 2, S.h, 256, *S.hq)
+    assert ei.value.code == 1
 
 
 def test_moe_single_token(be, orc, pkg):
