@@ -528,6 +528,7 @@ def gpu_arm(args):
             safe(cells, cell_layer, ctx, "config 1: dense layer Q4_K_M, batch 16", "Q4_K_M", 16)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=512 x 5120 x 17408 Q4_K", 512)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=2048 x 5120 x 17408 Q4_K", 2048)
+            safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=8192 x 5120 x 17408 Q4_K", 8192, iters=2)
             safe(cells, cell_moe, ctx, "config 3: routed MoE, 256 experts top-8, 16 tokens, Q4_K")
             safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer IQ4_XS, batch 1", "IQ4_XS", 1)
             safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer Q5_K, batch 1", "Q5_K", 1)
