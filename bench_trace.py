@@ -7,6 +7,7 @@ griddepcontrol.wait, had their activation in registers, got their first tile, fi
 and stored their last output - microseconds from the first CTA's entry, mean over CTAs.
 
     python bench_trace.py [chain|fused|plain|chain1]
+    python bench_trace.py router [tokens]    # phases of the MoE router kernel (softmax, top-k, CSR)
         chain:  q|k|v, then o -> gate|up -> down as one launch (the default of a one-GPU layer)
         fused:  four launches, the quantizers inside them
         plain:  separate quantizer launch for down
@@ -29,6 +30,34 @@ spec.loader.exec_module(build)
 os.environ["B200Q_LIB"] = build.build_native(extra=["-DB200Q_TUNING"],
                                              out=os.path.join(ROOT, "sycl-infer_b200", "libb200q_tuning.so"))
 import torch  # noqa: E402
+
+if len(sys.argv) > 1 and sys.argv[1] == "router":
+    # MoE router: config 3's shape, host launches (router, then the token quantizer), stamps of the last call
+    rt = torch.zeros(64 * 16, dtype=torch.int64, device="cuda")
+    os.environ["B200Q_ROUTE_TRACE_PTR"] = str(rt.data_ptr())
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    from sycl_infer_b200 import moe as M
+    be = pkg.make_cuda_backend(0)
+    tokens = int(sys.argv[2]) if len(sys.argv) > 2 else 16
+    _, bank = M.make_synthetic_moe(256, 8, 2048, 512, (12, 12, 12), seed=0, with_router=True)
+    S = M.MoeScratch(bank, tokens)
+    x = torch.from_numpy(pkg.synth.make_activation(tokens, 2048, 5)).cuda()
+    for _ in range(6):
+        rt.zero_()
+        M.moe_router_csr_launch(be, bank.gate_inp, 0, x, x.shape[1], tokens, 2048, 256, 8, S.logits, S.ids, S.wts, S.off,
+                                S.pair, S.active, S.n_active)
+        M.moe_actq_launch(be, x, x.shape[1], tokens, 2048, *S.xq)
+    be.synchronize()
+    t = rt.cpu().numpy().reshape(64, 16)[:tokens].astype(np.float64)
+    t0 = t[:, 0].min()
+    print(f"moe_route_kernel, {tokens} tokens: microseconds from the first CTA's entry (mean / latest over the CTAs)")
+    for k, nm in enumerate(["entry", "previous kernel done", "maximum", "exp", "sequential sum", "scaled", "rank count",
+                            "ids written", "counted in", "CSR done (last CTA)"]):
+        col = t[:, k][t[:, k] > 0]
+        if col.size:
+            print(f"  {nm:22s} {(col.mean() - t0) / 1e3:7.2f} {(col.max() - t0) / 1e3:7.2f}")
+    sys.exit(0)
 
 trace = torch.zeros(64 * 160 * 8, dtype=torch.int64, device="cuda")
 os.environ["B200Q_TRACE_PTR"] = str(trace.data_ptr())
