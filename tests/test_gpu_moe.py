@@ -144,6 +144,13 @@ def test_moe_gate_up_q_rejects_ragged_ffn(be, pkg):
     assert ei.value.code == 1
 
 
+def test_moe_many_pairs_per_share(be, orc, pkg):
+    """600 routed pairs on short expert planes: a CTA's share of the expert kernel spans several
+    pairs (its down launch gives every CTA four or five whole pairs), each with its own activation."""
+    n = _run_moe(be, orc, pkg, E=256, top_k=4, n_embd=256, n_ff=256, n_tok=150, types=(12, 12, 12), seed=11)
+    assert n >= 150
+
+
 def test_moe_single_token(be, orc, pkg):
     _run_moe(be, orc, pkg, E=16, top_k=4, n_embd=256, n_ff=256, n_tok=1, types=(12, 12, 12), seed=5)
 
