@@ -136,11 +136,27 @@ typedef struct b200q_next_act {
 } b200q_next_act;
 
 struct b200q_peers;
+/* RMSNorm folded into the call's quantizer: the activation the call consumes is
+ *   rmsnorm(x)[i] = x[i] * (1 / sqrt(sum(x^2) / K + eps)) * weight[i]
+ * (rmsnorm_row, src/backend/cpu/kernels/common.cpp:685-691; device twin
+ * src/backend/gpu/kernels/rmsnorm.cpp - the engine runs it as a launch of its own ahead of the
+ * q|k|v and gate|up calls), quantized as b200q_xq would quantize that row.  The sum of squares is
+ * formed in the order of the reference's AVX-512 helper (common.cpp:278-290: sixteen fused-
+ * multiply-add accumulators over i = 16k + j, halved 16 -> 8 -> 4, then (t0 + t2) + (t1 + t3)), so
+ * the codes are those of the reference on such a host, bit for bit.  One token, plain activation
+ * (no act_up), x and weight 16-byte aligned, a K the single-token kernel takes; otherwise
+ * B200Q_EUNSUPPORTED (run the norm as the engine does and call without this option). */
+typedef struct b200q_norm {
+    const float * weight; /* device, K values */
+    float eps;
+} b200q_norm;
+
 typedef struct b200q_call_opts {
     uint32_t flags;                  /* B200Q_OPT_* */
     const struct b200q_peers * peers; /* host; NULL = outputs stay on this GPU (see b200q_quant_gemv_scatter) */
     const b200q_next_act * next;     /* host; NULL = off */
     const b200q_peer_sync * sync;    /* host; needed by B200Q_OPT_WAIT_PEERS / B200Q_OPT_SIGNAL_PEERS */
+    const b200q_norm * norm;         /* host; NULL = off */
 } b200q_call_opts;
 
 /* b200q_quant_gemv with options: the general form of the fused decode launch

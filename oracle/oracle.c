@@ -242,6 +242,43 @@ static inline float silu_f(float x) { /* kernels/common.h:31-33 */
     return x / (1.0f + expf(-x));
 }
 
+/* RMSNorm of one row, as rmsnorm_row (src/backend/cpu/kernels/common.cpp:685-691): scale =
+ * 1 / sqrt(ss / n + eps), out = x * scale * w, with ss = sum of squares in the order of the
+ * reference's helper for the host's vector width (common.cpp:259-290, 524-530):
+ *   lanes 1   s += a*a, in order (the portable loop; no contraction is assumed)
+ *   lanes 8   eight accumulators acc[j] = fma(a, a, acc[j]) over i = 8k + j, then (acc[j] + acc[j+4]),
+ *             two horizontal adds: (l0 + l1) + (l2 + l3); a tail of n % 8 elements s += a*a
+ *   lanes 16  sixteen accumulators with fma, halved 16 -> 8 -> 4, then (t0 + t2) + (t1 + t3); tail
+ *             of n % 16 elements s += a*a */
+void orc_rmsnorm(const float * x, const float * w, float * out, int n, float eps, int lanes) {
+    float ss = 0.0f;
+    int i = 0;
+    if (lanes == 8 || lanes == 16) {
+        float acc[16] = {0};
+        for (; i + lanes <= n; i += lanes) {
+            for (int j = 0; j < lanes; j++) {
+                acc[j] = fmaf(x[i + j], x[i + j], acc[j]);
+            }
+        }
+        if (lanes == 16) {
+            for (int j = 0; j < 8; j++) {
+                acc[j] = acc[j + 8] + acc[j];
+            }
+        }
+        for (int j = 0; j < 4; j++) {
+            acc[j] = acc[j] + acc[j + 4];
+        }
+        ss = lanes == 16 ? (acc[0] + acc[2]) + (acc[1] + acc[3]) : (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    }
+    for (; i < n; i++) {
+        ss += x[i] * x[i];
+    }
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    for (i = 0; i < n; i++) {
+        out[i] = x[i] * scale * w[i];
+    }
+}
+
 void orc_xq(const float * x, const float * up, int x_stride, int up_stride, int8_t * x8, float * xmeta,
             int32_t * xsumq, int TB, int K) {
     const int G = K / 32;

@@ -42,6 +42,11 @@ size_t orc_row_bytes(uint32_t type, int64_t n);
 int orc_dots_per_row(uint32_t type, int K);
 void orc_dequantize_row(uint32_t type, const void * data, float * y, int64_t n);
 
+/* rmsnorm_row (src/backend/cpu/kernels/common.cpp:685-691).  `lanes` selects the order in which the
+ * reference sums the squares on a host: 1 = the portable loop, 8 = its AVX2 helper (:259-276), 16 = its
+ * AVX-512 helper (:278-290, sixteen fused-multiply-add accumulators combined by halving). */
+void orc_rmsnorm(const float * x, const float * w, float * out, int n, float eps, int lanes);
+
 void orc_xq(const float * x, const float * up, int x_stride, int up_stride, int8_t * x8, float * xmeta,
             int32_t * xsumq, int TB, int K);
 void orc_block_dots(uint32_t type, const void * w, int K, int n_rows, const int8_t * x8, int TB, int t,

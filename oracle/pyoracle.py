@@ -76,6 +76,7 @@ class Oracle:
         L.orc_row_bytes.argtypes = [C.c_uint32, C.c_int64]
         L.orc_dequantize_row.argtypes = [C.c_uint32, _vp, _vp, C.c_int64]
         L.orc_xq.argtypes = [_vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, C.c_int, C.c_int]
+        L.orc_rmsnorm.argtypes = [_vp, _vp, _vp, C.c_int, C.c_float, C.c_int]
         L.orc_block_dots.argtypes = [C.c_uint32, _vp, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]
         L.orc_i8_gemm.argtypes = [C.POINTER(OrcSeg), C.c_int]
         L.orc_i8_gemm_abs.argtypes = [C.POINTER(OrcSeg), C.c_int, _vp]
@@ -96,6 +97,14 @@ class Oracle:
         y = np.zeros(n_rows * K, np.float32)
         self.L.orc_dequantize_row(t, _p(w), _p(y), n_rows * K)
         return y.reshape(n_rows, K)
+
+    def rmsnorm(self, x, w, eps, lanes=16):
+        """One row; lanes 1 / 8 / 16 = the reference's portable, AVX2 or AVX-512 order of the sum of squares."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1)
+        w = np.ascontiguousarray(w, np.float32).reshape(-1)
+        out = np.zeros_like(x)
+        self.L.orc_rmsnorm(_p(x), _p(w), _p(out), x.size, float(eps), int(lanes))
+        return out
 
     def xq(self, x, up=None, TB=1, K=None):
         x = np.ascontiguousarray(x, np.float32).reshape(TB, -1)
@@ -183,6 +192,9 @@ class Ref:
         L.siref_set_threads.argtypes = [C.c_int]
         L.siref_f2h.restype = C.c_uint16
         L.siref_f2h.argtypes = [C.c_float]
+        if hasattr(L, "siref_rmsnorm_row"):  # builds of the shim made before it forwarded this
+            L.siref_isa.restype = C.c_int
+            L.siref_rmsnorm_row.argtypes = [_vp, _vp, _vp, C.c_int, C.c_float]
         L.siref_h2f.restype = C.c_float
         L.siref_h2f.argtypes = [C.c_uint16]
         L.siref_row_bytes.restype = C.c_uint64
@@ -208,6 +220,17 @@ class Ref:
 
     def threads(self):
         return int(self.L.siref_threads())
+
+    def isa_lanes(self):
+        """Accumulators of the sum-of-squares helper this host selects: 1, 8 or 16."""
+        return {0: 1, 1: 8, 2: 16}[int(self.L.siref_isa())]
+
+    def rmsnorm(self, x, w, eps):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1)
+        w = np.ascontiguousarray(w, np.float32).reshape(-1)
+        out = np.zeros_like(x)
+        self.L.siref_rmsnorm_row(_p(x), _p(w), _p(out), x.size, float(eps))
+        return out
 
     def f2h(self, f):
         return int(self.L.siref_f2h(float(f)))

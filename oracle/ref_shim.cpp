@@ -16,6 +16,7 @@
 //   cpu_moe_route          src/backend/cpu/kernels/moe.cpp:72-137
 //   cpu_moe_experts_i8     src/backend/cpu/kernels/moe.cpp:476-559
 //   cpu_moe_reduce         src/backend/cpu/kernels/moe.cpp:562-574
+//   rmsnorm_row            src/backend/cpu/kernels/common.cpp:685-691 (sum of squares dispatched on the host ISA)
 //   dequantize_row         src/common/quant.h
 //   quant_row_bytes        src/common/quant.h:1177-1198
 //   ggml_float_to_half / ggml_half_to_float   src/common/quant.h:67-133
@@ -62,6 +63,14 @@ void siref_set_threads(int n) {
 }
 int siref_i8_supported_isa(void) {
     return isa().qgemv_sb != nullptr ? 1 : 0;
+}
+
+// 0 scalar, 1 AVX2, 2 AVX-512: which variant of the ISA-dispatched helpers (sum of squares) this host runs
+int siref_isa(void) {
+    return (int)cpu_best_isa();
+}
+void siref_rmsnorm_row(const float * x, const float * w, float * out, int n, float eps) {
+    rmsnorm_row(x, w, out, n, eps);
 }
 
 uint16_t siref_f2h(float f) {

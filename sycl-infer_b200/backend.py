@@ -124,13 +124,14 @@ class cuda_backend:
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
     def quant_gemv_ex(self, segs, TB=1, prequantized=False, peers=None, next_act=None, sync=None, wait=False,
-                      signal=False):
+                      signal=False, norm=None):
         """quant_gemv with options: `prequantized` skips the quantizer (the segments' scratch holds
         the activation already); `peers` scatters the outputs; `next_act` = (x8, xmeta, xsumq) makes
         the call emit its output (gate|up: silu(gate)*up) quantized as the following call's activation;
         `sync` = (flag pointer array, world, rank) with `wait` / `signal` folds the cross-GPU flag
-        exchange of a row-sharded call into the launch."""
-        from .capi import CallOpts, NextAct, PeerSync, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
+        exchange of a row-sharded call into the launch; `norm` = (weight, eps) folds the RMSNorm of
+        the activation into the call's quantizer."""
+        from .capi import CallOpts, NextAct, Norm, PeerSync, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
         arr, n = _pack(segs)
         s0 = segs[0]
         opts = CallOpts()
@@ -143,6 +144,10 @@ class cuda_backend:
             na = NextAct(_ptr(next_act[0]), _ptr(next_act[1]), _ptr(next_act[2]))
             keep.append(na)
             opts.next = C.pointer(na)
+        if norm is not None:
+            nm = Norm(_ptr(norm[0]), float(norm[1]))
+            keep.append(nm)
+            opts.norm = C.pointer(nm)
         if sync is not None:
             ps = PeerSync(C.cast(sync[0], C.POINTER(C.c_void_p)), sync[1], sync[2])
             keep.append(ps)

@@ -37,10 +37,15 @@ class PeerSync(C.Structure):
     _fields_ = [("flags", C.POINTER(_vp)), ("world", C.c_int32), ("rank", C.c_int32)]
 
 
+class Norm(C.Structure):
+    """struct b200q_norm."""
+    _fields_ = [("weight", _vp), ("eps", C.c_float)]
+
+
 class CallOpts(C.Structure):
     """struct b200q_call_opts."""
     _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct)),
-                ("sync", C.POINTER(PeerSync))]
+                ("sync", C.POINTER(PeerSync)), ("norm", C.POINTER(Norm))]
 
 
 OPT_PREQUANTIZED, OPT_WAIT_PEERS, OPT_SIGNAL_PEERS = 1, 2, 4

@@ -295,6 +295,20 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             return B200Q_EUNSUPPORTED;
         }
     }
+    NormArgs norm{nullptr, 0.0f};
+    if (opts && opts->norm) {
+        if (!opts->norm->weight || !(opts->norm->eps >= 0.0f)) {
+            set_error("%s: norm needs a weight vector and eps >= 0", who);
+            return B200Q_EINVAL;
+        }
+        if (prequant || TB != 1 || !aligned(opts->norm->weight, 16) || !gemv_takes_pinned(c) ||
+            !pinned_quantizes(c, s0.x, s0.act_up)) {
+            set_error("%s: the folded RMSNorm serves one token with a plain, 16-byte aligned activation and weight "
+                      "and a K the single-token kernel takes (K=%d, TB=%d)", who, c.K, TB);
+            return B200Q_EUNSUPPORTED;
+        }
+        norm = NormArgs{opts->norm->weight, opts->norm->eps};
+    }
     if (gemv_takes_pinned(c)) {
         const bool inside = !prequant && pinned_quantizes(c, s0.x, s0.act_up);
         if (!prequant && !inside) { // a quantizer launch of its own: it is the one that waits for the peers
@@ -303,7 +317,7 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             sync.wait = 0;
         }
         B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.x8 ? &next : nullptr,
-                                         (sync.wait || sync.signal) ? &sync : nullptr));
+                                         (sync.wait || sync.signal) ? &sync : nullptr, norm.w ? &norm : nullptr));
         return B200Q_OK;
     }
     if (!prequant) {

@@ -133,6 +133,12 @@ struct NextAct {
     int32_t * xsumq;
 };
 
+// RMSNorm folded into the in-kernel quantizer (b200q_norm); w == nullptr: off
+struct NormArgs {
+    const float * w;
+    float eps;
+};
+
 // cross-GPU flag exchange folded into a GEMV launch (b200q_peer_sync)
 struct PeerSync {
     uint32_t * flag[B200Q_MAX_PEERS + 1]; // rank p's flag array as mapped on this GPU

@@ -59,6 +59,7 @@ struct PinArgs {
     CallDev c;
     CostSplit cost;
     const float * xq_x; // when set, every CTA quantizes this fp32 activation itself
+    NormArgs norm;      // RMSNorm applied to xq_x before it is quantized (w == nullptr: off)
     NextAct next;       // the call's output, quantized, as the following call's activation (x8 == nullptr: off)
     PeerSync sync;      // row-sharded calls: wait for / signal the peers inside this launch
     int32_t W, R, U, seg, P, Ppad; // P = U / seg partials per row, rows Ppad words apart
@@ -163,8 +164,10 @@ __device__ __forceinline__ uint32_t pin_pack_addr(uint32_t pack, int g) {
 
 // The arithmetic is the standalone quantizer's (xq.cuh), bit for bit: max and integer sums are
 // exact in any order, every fp32 operation is a single correctly rounded one.
+// nw != nullptr: the value quantized is (x * nscale) * nw[i], the RMSNorm of the row (rmsnorm_row,
+// src/backend/cpu/kernels/common.cpp:685-691 of the reference: two roundings, left to right).
 __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, uint32_t xraw, int G, int warp,
-                                             int lane, int W, bool write_views) {
+                                             int lane, int W, bool write_views, const float * nw, float nscale) {
     constexpr int kBatch = 4; // loads of several passes in flight before the first is used
     const int stride = 32 * W, n_tasks = 8 * G;
     for (int base0 = warp * 32; base0 < n_tasks; base0 += kBatch * stride) {
@@ -176,6 +179,13 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, u
             if (task < n_tasks) {
                 const uint4 u = lds128(xraw + 16u * (uint32_t)task);
                 fb[i] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+                if (nw) {
+                    const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw) + task);
+                    fb[i].x = __fmul_rn(__fmul_rn(fb[i].x, nscale), wv.x);
+                    fb[i].y = __fmul_rn(__fmul_rn(fb[i].y, nscale), wv.y);
+                    fb[i].z = __fmul_rn(__fmul_rn(fb[i].z, nscale), wv.z);
+                    fb[i].w = __fmul_rn(__fmul_rn(fb[i].w, nscale), wv.w);
+                }
             }
         }
 #pragma unroll
@@ -594,7 +604,39 @@ __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs 
         PIN_STAMP(7);
     }
     if (a.xq_x) {
-        pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0);
+        float nscale = 1.0f;
+        if (a.norm.w) {
+            // 1 / sqrt(sum(x^2) / K + eps), the sum in the order of the reference's widest host path
+            // (sumsq_f32_avx512, common.cpp:278-290): sixteen accumulators acc[j] = fma(x, x, acc[j])
+            // over i = 16k + j, halved 16 -> 8 -> 4, then (t0 + t2) + (t1 + t3)
+            if (warp == 0) {
+                float acc = 0.f;
+                if (lane < 16) {
+                    for (uint32_t i = (uint32_t)lane; i < K; i += 128) { // K is a multiple of 256
+                        float v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            v[u] = __uint_as_float(lds32(xraw + 4u * (i + 16u * (uint32_t)u)));
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            acc = __fmaf_rn(v[u], v[u], acc);
+                        }
+                    }
+                }
+                acc = __fadd_rn(__shfl_down_sync(0xFFFFFFFFu, acc, 8), acc);
+                acc = __fadd_rn(acc, __shfl_down_sync(0xFFFFFFFFu, acc, 4));
+                acc = __fadd_rn(acc, __shfl_down_sync(0xFFFFFFFFu, acc, 2));
+                acc = __fadd_rn(acc, __shfl_down_sync(0xFFFFFFFFu, acc, 1));
+                if (lane == 0) {
+                    const float sc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(acc, (float)K), a.norm.eps)));
+                    sts32(base + 208, __float_as_uint(sc));
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
+            nscale = __uint_as_float(lds32(base + 208));
+        }
+        pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0, a.norm.w, nscale);
     } else {
         pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
     }
@@ -1062,10 +1104,11 @@ bool pinned_quantizes(const CallDev & c, const float * x, const float * act_up) 
 }
 
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next,
-                               const PeerSync * sync) {
+                               const PeerSync * sync, const NormArgs * norm) {
     PinArgs a;
     a.c = c;
     a.xq_x = xq_x;
+    a.norm = (norm && xq_x) ? *norm : NormArgs{nullptr, 0.0f};
     a.next = next ? *next : NextAct{nullptr, nullptr, nullptr};
     memset(&a.sync, 0, sizeof(a.sync));
     if (sync) {
@@ -1077,7 +1120,7 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
 #ifdef B200Q_TUNING
     if (getenv("B200Q_CHAIN1")) { // A/B: the chain kernel for single calls too (one kernel image in the stream)
         const NextAct nx = a.next;
-        if (!sync) {
+        if (!sync && !a.norm.w) {
             return launch_gemv_chain(s, &c, &xq_x, &nx, 1);
         }
     }

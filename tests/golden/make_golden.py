@@ -112,6 +112,13 @@ def main():
     base = synth.make_activation(n_tok, n_embd, 105)
     g["moe_base"] = base
     g["moe_out_strict"] = RS.moe_reduce(acc, wts, base)
+    # RMSNorm rows.  The reference sums the squares in the order of the host's vector width; the
+    # width of the host that wrote these vectors is recorded beside them (16 = AVX-512).
+    r2 = np.random.default_rng(777)
+    g["rms_lanes"] = np.array([R.isa_lanes()], np.int32)
+    for n in (256, 1000, 5120):
+        xr, wr = r2.normal(0, 1, n).astype(np.float32), r2.normal(1, 0.2, n).astype(np.float32)
+        g[f"rms_x_{n}"], g[f"rms_w_{n}"], g[f"rms_out_{n}"] = xr, wr, R.rmsnorm(xr, wr, 1e-6)
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes")
 

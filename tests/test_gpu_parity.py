@@ -451,3 +451,78 @@ def test_second_device_in_one_process(pkg, orc):
                 ref, ab = orc.gemm(t, w, K, N, a), orc.gemm_abs(t, w, K, N, a)
                 assert rel_err(o.cpu().numpy().reshape(TB, N), ref, ab) <= TOL
             assert be_d.device_status() == 0
+
+
+@pytest.mark.parametrize("t,K,N", [(12, 1024, 96), (12, 5120, 640), (14, 2048, 128)])
+def test_rmsnorm_folded_into_the_quantizer(be, orc, pkg, t, K, N):
+    """b200q_call_opts.norm: the call consumes quantize(rmsnorm(x)).  The codes, scales and sums the
+    launch leaves in the scratch views are the host quantizer's on the oracle's rmsnorm row (the
+    reference's rmsnorm_row in its AVX-512 summation order), bit for bit; outputs against the oracle
+    GEMV on exactly that activation."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    x = pkg.synth.make_activation(1, K, 1201)
+    g = (1.0 + 0.2 * pkg.synth.make_activation(1, K, 1202)).astype(np.float32)
+    w = pkg.synth.make_weight(t, N, K, 1203)
+    eps = 1e-6
+    x8, xm, xs = alloc_act(1, K)
+    out = torch.zeros(N, dtype=torch.float32, device="cuda")
+    alpha = 1.0 / (3.0 * K ** 0.5)
+    seg = gemv_seg(w=dev(w), type=t, K=K, n_rows=N, x=dev(x), x_stride=K, out=out, out_stride=N, alpha=alpha,
+                   x8=x8, xmeta=xm, xsumq=xs)
+    for _ in range(2):
+        x8.zero_()
+        be.quant_gemv_ex([seg], 1, norm=(dev(g), eps))
+        be.synchronize()
+        assert be.device_status() == 0
+        a = orc.xq(orc.rmsnorm(x, g, eps, 16))
+        assert np.array_equal(x8.cpu().numpy(), a.x8)
+        assert np.array_equal(xm.cpu().numpy().view(np.uint32), a.xmeta.view(np.uint32))
+        assert np.array_equal(xs.cpu().numpy(), a.xsumq)
+        ref, ab = orc.gemm(t, w, K, N, a, alpha=alpha), orc.gemm_abs(t, w, K, N, a, alpha=alpha)
+        assert rel_err(out.cpu().numpy().reshape(1, N), ref, ab) <= TOL
+
+
+def test_rmsnorm_with_gate_up_next_activation(be, orc, pkg):
+    """norm -> quantize -> gate|up -> silu(gate)*up -> quantize in ONE launch."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    K, n_ff, t = 1024, 1280, 12
+    x = pkg.synth.make_activation(1, K, 1301)
+    g = (1.0 + 0.2 * pkg.synth.make_activation(1, K, 1302)).astype(np.float32)
+    wg, wu = pkg.synth.make_weight(t, n_ff, K, 1303), pkg.synth.make_weight(t, n_ff, K, 1304)
+    alpha = 1.0 / (3.0 * K ** 0.5)
+    gu = torch.zeros(1, 2 * n_ff, dtype=torch.float32, device="cuda")
+    x8, xm, xs = alloc_act(1, K)
+    h8, hm, hs = alloc_act(1, n_ff)
+    dx = dev(x)
+    segs = [gemv_seg(w=dev(wg), type=t, K=K, n_rows=n_ff, x=dx, x_stride=K, out=gu.view(-1), out_stride=2 * n_ff,
+                     alpha=alpha, x8=x8, xmeta=xm, xsumq=xs),
+            gemv_seg(w=dev(wu), type=t, K=K, n_rows=n_ff, x=dx, x_stride=K, out=gu.view(-1)[n_ff:], out_stride=2 * n_ff,
+                     alpha=alpha, x8=x8, xmeta=xm, xsumq=xs)]
+    be.quant_gemv_ex(segs, 1, next_act=(h8, hm, hs), norm=(dev(g), 1e-5))
+    be.synchronize()
+    assert be.device_status() == 0
+    a = orc.xq(orc.rmsnorm(x, g, 1e-5, 16))
+    assert np.array_equal(x8.cpu().numpy(), a.x8)
+    got = gu.cpu().numpy()
+    for wq, lo in ((wg, 0), (wu, n_ff)):
+        ref, ab = orc.gemm(t, wq, K, n_ff, a, alpha=alpha), orc.gemm_abs(t, wq, K, n_ff, a, alpha=alpha)
+        assert rel_err(got[:, lo:lo + n_ff], ref, ab) <= TOL
+    q8, qm, qs = gpu_xq(be, got[:, :n_ff], got[:, n_ff:], 1)
+    assert np.array_equal(h8.cpu().numpy(), q8.cpu().numpy()) and np.array_equal(hs.cpu().numpy(), qs.cpu().numpy())
+
+
+def test_rmsnorm_option_refused_where_it_cannot_be_folded(be, pkg):
+    """Several tokens, or a pre-quantized activation: B200Q_EUNSUPPORTED, nothing launched."""
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    from sycl_infer_b200.capi import B200QError
+    K, N = 1024, 64
+    w = dev(pkg.synth.make_weight(12, N, K, 1401))
+    g = dev(np.ones(K, np.float32))
+    for TB, preq in ((3, False), (1, True)):
+        x = dev(pkg.synth.make_activation(TB, K, 1402))
+        x8, xm, xs = alloc_act(TB, K)
+        out = torch.zeros(TB * N, dtype=torch.float32, device="cuda")
+        seg = gemv_seg(w=w, type=12, K=K, n_rows=N, x=x, x_stride=K, out=out, out_stride=N, x8=x8, xmeta=xm, xsumq=xs)
+        with pytest.raises(B200QError) as ei:
+            be.quant_gemv_ex([seg], TB, prequantized=preq, norm=(g, 1e-6))
+        assert ei.value.code == 2
