@@ -318,6 +318,26 @@ def cell_token(ctx, layers, n_layers=LAYERS_PER_TOKEN, iters=10):
             "l2": f"{L} weight sets of 210 MB cycled", "clocks": clocks}
 
 
+def cell_layer_norm(ctx, L=4, steps=96):
+    """The layer step with the two RMSNorms a decoder layer has (ahead of q|k|v and of gate|up) folded
+    into those calls' quantizers: still four launches."""
+    from sycl_infer_b200.layer import DenseLayer
+    torch, pkg = ctx.torch, ctx.pkg
+    layers = [DenseLayer(ctx.be, "Q4_K_M", seed=500 + i, TB=1, norm=True) for i in range(L)]
+    xs = [torch.from_numpy(pkg.synth.make_activation(1, layers[0].hidden, 20 + i)).cuda() for i in range(L)]
+    for ly in layers:
+        ly.attn.copy_(torch.from_numpy(pkg.synth.make_activation(1, ly.q_dim, 3)))
+    out = torch.zeros(1, layers[0].hidden, device="cuda")
+    g = ctx.capture(lambda: [layers[i].forward(xs[i], out) for i in range(L)])
+    (ms, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: g.replay(), steps // L))
+    us = 1e3 * ms / (steps // L * L)
+    nbytes = layer_bytes(pkg, "Q4_K_M", 1, layers[0]) + 2 * 4 * layers[0].hidden
+    gbs = nbytes / us / 1e3
+    return {"cell": "config 1 + RMSNorm ahead of q|k|v and gate|up folded into their quantizers, batch 1", "us": us,
+            "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": ctx.frac(gbs), "launches_per_iter": 4,
+            "status_clean": ctx.be.device_status() == 0, "l2": f"{L} rotating weight sets", "clocks": clocks}
+
+
 def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
     """Config 2: M tokens x (Q4_K weight of `rows` x K); quantizer + tensor-core GEMM per iteration."""
     torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
@@ -524,6 +544,7 @@ def gpu_arm(args):
     if not args.no_cells:
         if world == 1:
             safe(cells, cell_token, ctx, layers)
+            safe(cells, cell_layer_norm, ctx)
             safe(cells, cell_single_matrix, ctx, "config 0: Q4_K 4096x4096 GEMV, batch 1", 12, 4096, 4096)
             safe(cells, cell_layer, ctx, "config 1: dense layer Q4_K_M, batch 16", "Q4_K_M", 16)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=512 x 5120 x 17408 Q4_K", 512)

@@ -166,6 +166,7 @@ __device__ __forceinline__ uint32_t pin_pack_addr(uint32_t pack, int g) {
 // exact in any order, every fp32 operation is a single correctly rounded one.
 // nw != nullptr: the value quantized is (x * nscale) * nw[i], the RMSNorm of the row (rmsnorm_row,
 // src/backend/cpu/kernels/common.cpp:685-691 of the reference: two roundings, left to right).
+template <bool NORM>
 __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, uint32_t xraw, int G, int warp,
                                              int lane, int W, bool write_views, const float * nw, float nscale) {
     constexpr int kBatch = 4; // loads of several passes in flight before the first is used
@@ -179,7 +180,7 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, u
             if (task < n_tasks) {
                 const uint4 u = lds128(xraw + 16u * (uint32_t)task);
                 fb[i] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-                if (nw) {
+                if (NORM) {
                     const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw) + task);
                     fb[i].x = __fmul_rn(__fmul_rn(fb[i].x, nscale), wv.x);
                     fb[i].y = __fmul_rn(__fmul_rn(fb[i].y, nscale), wv.y);
@@ -581,6 +582,8 @@ __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & 
 
 // Consumer warps: fetch the call's activation with bulk copies (thread 0 issues them) and quantize
 // or re-lay it into the pack, from which every thread then takes its unit into registers.
+// NORM: the RMSNorm of the row is folded in (a kernel image of its own, so that the plain one carries none of it).
+template <bool NORM>
 __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs & g, uint32_t base, uint32_t parity) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = a.W, nb = a.c.K >> 8;
@@ -605,7 +608,7 @@ __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs 
     }
     if (a.xq_x) {
         float nscale = 1.0f;
-        if (a.norm.w) {
+        if (NORM) {
             // 1 / sqrt(sum(x^2) / K + eps), the sum in the order of the reference's widest host path
             // (sumsq_f32_avx512, common.cpp:278-290): sixteen accumulators acc[j] = fma(x, x, acc[j])
             // over i = 16k + j, halved 16 -> 8 -> 4, then (t0 + t2) + (t1 + t3)
@@ -636,7 +639,7 @@ __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs 
             asm volatile("bar.sync 1, %0;" ::"r"(32 * W) : "memory");
             nscale = __uint_as_float(lds32(base + 208));
         }
-        pin_quantize(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0, a.norm.w, nscale);
+        pin_quantize<NORM>(pack, a.c, xraw, 8 * nb, warp, lane, W, blockIdx.x == 0, a.norm.w, nscale);
     } else {
         pin_stage_views(pack, xraw, 8 * nb, (int)threadIdx.x, 32 * W);
     }
@@ -679,6 +682,7 @@ __device__ __forceinline__ void pin_init_barriers(const PinBars & bars, uint32_t
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+template <bool NORM>
 __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __grid_constant__ PinArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -776,7 +780,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
     }
     const int U = a.U;
     const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
-    if (!pin_activation(a, a, base, 0)) {
+    if (!pin_activation<NORM>(a, a, base, 0)) {
         return;
     }
     if (threadIdx.x == 0) {
@@ -904,7 +908,7 @@ __global__ void __launch_bounds__(32 * (kChainW + 2), 1) gemv_chain_kernel(const
         }
         const int U = a.U;
         const int slot = (int)threadIdx.x / U, unit = (int)threadIdx.x - slot * U;
-        if (!pin_activation(a, ch.call[0], base, (uint32_t)ci & 1u)) {
+        if (!pin_activation<false>(a, ch.call[0], base, (uint32_t)ci & 1u)) {
             return;
         }
         if (ci == 0 && threadIdx.x == 0) {
@@ -1127,7 +1131,9 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     trace_slot(a, true);
 #endif
     const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
-    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemv_pinned_kernel), kPinSmem);
+    const bool normed = a.norm.w != nullptr;
+    cudaError_t e = ensure_dynamic_smem(normed ? reinterpret_cast<const void *>(gemv_pinned_kernel<true>)
+                                               : reinterpret_cast<const void *>(gemv_pinned_kernel<false>), kPinSmem);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1141,7 +1147,7 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_pinned_kernel, a);
+    return normed ? cudaLaunchKernelEx(&cfg, gemv_pinned_kernel<true>, a) : cudaLaunchKernelEx(&cfg, gemv_pinned_kernel<false>, a);
 }
 
 static void chain_fill(ChainArgs & ch, const CallDev * calls, const float * const * xq_x, const NextAct * next, int n,

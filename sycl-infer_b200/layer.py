@@ -18,7 +18,7 @@ from .sharding import gather_rows, shard_rows
 
 class DenseLayer:
     def __init__(self, be, mix="Q4_K_M", seed=0, TB=1, rank=0, world=1, hidden=5120, n_head=40, n_kv=8,
-                 head_dim=128, n_ff=17408, group=None, arena=None):
+                 head_dim=128, n_ff=17408, group=None, arena=None, norm=False):
         """`arena` (sharding.PeerArena): outputs live in memory every rank maps, each call's GEMV
         stores its rows on all ranks and a flag barrier replaces the all-gather."""
         self.be, self.TB, self.rank, self.world, self.group = be, TB, rank, world, group
@@ -50,6 +50,12 @@ class DenseLayer:
         self.act_q = alloc_act(TB, self.q_dim, dev)
         self.act_f = alloc_act(TB, n_ff, dev)
         # one token on one GPU: the gate|up GEMV leaves the quantized silu(gate)*up for the down call
+        # norm: RMSNorm of the layer input ahead of q|k|v and of o's output ahead of gate|up, folded into
+        # those calls' quantizers (one token on one GPU)
+        self.norm = None
+        if norm:
+            rng_w = lambda s: torch.from_numpy((1.0 + 0.1 * synth.make_activation(1, hidden, s)).astype("float32")).to(dev)  # noqa: E731
+            self.norm = (rng_w(seed * 16 + 14).view(-1), rng_w(seed * 16 + 15).view(-1), 1e-6)
         self.fused_h = TB == 1 and world == 1
         # True: o, gate|up and down (each consumes the previous one's output) go out as ONE launch
         # (quant_gemv_chain).  Off by default: measured equal to three launches on its own (47.9 us
@@ -98,7 +104,8 @@ class DenseLayer:
             if self.fused_h:
                 # one launch per call: q|k|v and o quantize in the GEMV's prologue, gate|up emits down's
                 # quantized activation
-                self.be.quant_gemv_ex(segs, 1, prequantized=(i == 3), next_act=self.act_f if i == 2 else None)
+                nm = None if self.norm is None or i not in (0, 2) else (self.norm[0 if i == 0 else 1], self.norm[2])
+                self.be.quant_gemv_ex(segs, 1, prequantized=(i == 3), next_act=self.act_f if i == 2 else None, norm=nm)
                 continue
             if self.arena and self.exchange:
                 if self.TB == 1:
