@@ -151,12 +151,23 @@ typedef struct b200q_norm {
     float eps;
 } b200q_norm;
 
+/* Argmax of the call's outputs as the tail of the same launch (the LM head of a greedy decode step:
+ * the reference runs the head GEMV and then mtp_argmax_launch, src/backend/gpu/kernels/mtp_argmax.cpp;
+ * host twin src/backend/cpu/cpu_backend.cpp:117-128): *idx = the row with the largest output, the
+ * lowest row among equals, *val (may be NULL) its value.  One token, one segment, no peers, no
+ * next-activation.  The outputs themselves are stored as usual. */
+typedef struct b200q_argmax_out {
+    int32_t * idx; /* device */
+    float * val;   /* device, may be NULL */
+} b200q_argmax_out;
+
 typedef struct b200q_call_opts {
     uint32_t flags;                  /* B200Q_OPT_* */
     const struct b200q_peers * peers; /* host; NULL = outputs stay on this GPU (see b200q_quant_gemv_scatter) */
     const b200q_next_act * next;     /* host; NULL = off */
     const b200q_peer_sync * sync;    /* host; needed by B200Q_OPT_WAIT_PEERS / B200Q_OPT_SIGNAL_PEERS */
     const b200q_norm * norm;         /* host; NULL = off */
+    const struct b200q_argmax_out * argmax; /* host; NULL = off */
 } b200q_call_opts;
 
 /* b200q_quant_gemv with options: the general form of the fused decode launch
@@ -298,6 +309,12 @@ int b200q_i8_block_dots(void * stream, const void * w, uint32_t type, int K, int
  * symbol); `clear` != 0 resets the word after reading.  No counterpart in the reference,
  * whose kernels have no device-side waits. */
 int b200q_device_status(int * status /*host*/, int clear);
+
+/* compute_backend::mtp_argmax (src/backend/backend.h:47-48): per row of logits[M][n] the index of
+ * the largest value, the LOWEST index among equals (the host scan's `if (row[i] > row[best])`), and
+ * optionally that value.  Calls (and calls with the argmax option) on one device must not overlap:
+ * they share device-side words. */
+int b200q_argmax(void * stream, const float * logits, int n, int32_t * out_idx, float * out_val /*may be NULL*/, int M);
 
 /* Measurement instruments (no reference counterpart): the ceilings a benchmark reports the kernels
  * against.  The caller times them (events on `stream`).

@@ -124,14 +124,15 @@ class cuda_backend:
         self.lib.check(self.lib.quant_gemv(self._s(), arr, n, TB, _ptr(s0.x8), _ptr(s0.xmeta), _ptr(s0.xsumq)))
 
     def quant_gemv_ex(self, segs, TB=1, prequantized=False, peers=None, next_act=None, sync=None, wait=False,
-                      signal=False, norm=None):
+                      signal=False, norm=None, argmax=None):
         """quant_gemv with options: `prequantized` skips the quantizer (the segments' scratch holds
         the activation already); `peers` scatters the outputs; `next_act` = (x8, xmeta, xsumq) makes
         the call emit its output (gate|up: silu(gate)*up) quantized as the following call's activation;
         `sync` = (flag pointer array, world, rank) with `wait` / `signal` folds the cross-GPU flag
         exchange of a row-sharded call into the launch; `norm` = (weight, eps) folds the RMSNorm of
-        the activation into the call's quantizer."""
-        from .capi import CallOpts, NextAct, Norm, PeerSync, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
+        the activation into the call's quantizer; `argmax` = (idx, val or None) also leaves the row
+        index of the largest output (lowest among equals): the LM head of a greedy step."""
+        from .capi import ArgmaxOut, CallOpts, NextAct, Norm, PeerSync, OPT_PREQUANTIZED, OPT_SIGNAL_PEERS, OPT_WAIT_PEERS
         arr, n = _pack(segs)
         s0 = segs[0]
         opts = CallOpts()
@@ -144,6 +145,10 @@ class cuda_backend:
             na = NextAct(_ptr(next_act[0]), _ptr(next_act[1]), _ptr(next_act[2]))
             keep.append(na)
             opts.next = C.pointer(na)
+        if argmax is not None:
+            am = ArgmaxOut(_ptr(argmax[0]), _ptr(argmax[1]))
+            keep.append(am)
+            opts.argmax = C.pointer(am)
         if norm is not None:
             nm = Norm(_ptr(norm[0]), float(norm[1]))
             keep.append(nm)
@@ -173,6 +178,10 @@ class cuda_backend:
                 keep.append(na)
                 cc.next = C.pointer(na)
         self.lib.check(self.lib.quant_gemv_chain(self._s(), arr, len(calls)))
+
+    # compute_backend::mtp_argmax (backend.h:47-48)
+    def mtp_argmax(self, logits, n, out_idx, out_val, M):
+        self.lib.check(self.lib.argmax(self._s(), _ptr(logits), n, _ptr(out_idx), _ptr(out_val), M))
 
     def quant_gemv_scatter(self, segs, TB, peers):
         """quant_gemv whose outputs are also stored into the peers' copies of the output arena."""

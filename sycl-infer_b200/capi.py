@@ -42,10 +42,15 @@ class Norm(C.Structure):
     _fields_ = [("weight", _vp), ("eps", C.c_float)]
 
 
+class ArgmaxOut(C.Structure):
+    """struct b200q_argmax_out."""
+    _fields_ = [("idx", _vp), ("val", _vp)]
+
+
 class CallOpts(C.Structure):
     """struct b200q_call_opts."""
     _fields_ = [("flags", C.c_uint32), ("peers", C.POINTER(Peers)), ("next", C.POINTER(NextAct)),
-                ("sync", C.POINTER(PeerSync)), ("norm", C.POINTER(Norm))]
+                ("sync", C.POINTER(PeerSync)), ("norm", C.POINTER(Norm)), ("argmax", C.POINTER(ArgmaxOut))]
 
 
 OPT_PREQUANTIZED, OPT_WAIT_PEERS, OPT_SIGNAL_PEERS = 1, 2, 4
@@ -91,6 +96,7 @@ _SIGS = {
     "b200q_quant_gemv_static": (C.c_int, [_vp, C.POINTER(Seg), C.c_int]),
     "b200q_i8_block_dots": (C.c_int, [_vp, _vp, C.c_uint32, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]),
     "b200q_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "b200q_argmax": (C.c_int, [_vp, _vp, C.c_int, _vp, _vp, C.c_int]),
     "b200q_probe_hbm_read": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "b200q_probe_i8_mma": (C.c_int, [_vp, C.c_int, _vp]),
     "b200q_synchronize": (C.c_int, [_vp]),

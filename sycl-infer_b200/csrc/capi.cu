@@ -309,6 +309,20 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
         }
         norm = NormArgs{opts->norm->weight, opts->norm->eps};
     }
+    int32_t * am_idx = nullptr;
+    float * am_val = nullptr;
+    if (opts && opts->argmax) {
+        if (!opts->argmax->idx) {
+            set_error("%s: argmax needs an index output", who);
+            return B200Q_EINVAL;
+        }
+        if (TB != 1 || n_segs != 1 || c.n_peers > 0 || next.x8 || !gemv_takes_pinned(c)) {
+            set_error("%s: the argmax tail serves one token, one segment, no peers, no next-activation", who);
+            return B200Q_EUNSUPPORTED;
+        }
+        am_idx = opts->argmax->idx;
+        am_val = opts->argmax->val;
+    }
     if (gemv_takes_pinned(c)) {
         const bool inside = !prequant && pinned_quantizes(c, s0.x, s0.act_up);
         if (!prequant && !inside) { // a quantizer launch of its own: it is the one that waits for the peers
@@ -317,7 +331,8 @@ int quant_gemv_call(const char * who, cudaStream_t stream, const b200q_seg * seg
             sync.wait = 0;
         }
         B200Q_CUDA_OK(launch_gemv_pinned(stream, c, inside ? s0.x : nullptr, next.x8 ? &next : nullptr,
-                                         (sync.wait || sync.signal) ? &sync : nullptr, norm.w ? &norm : nullptr));
+                                         (sync.wait || sync.signal) ? &sync : nullptr, norm.w ? &norm : nullptr, am_idx,
+                                         am_val));
         return B200Q_OK;
     }
     if (!prequant) {
@@ -697,6 +712,15 @@ int b200q_device_status(int * status, int clear) {
     if (*status != 0) {
         set_error("a bounded device-side wait ran out (status %d)", *status);
     }
+    return B200Q_OK;
+}
+
+int b200q_argmax(void * stream, const float * logits, int n, int32_t * out_idx, float * out_val, int M) {
+    if (!logits || !out_idx || n < 1 || M < 1) {
+        set_error("b200q_argmax: logits and out_idx must be non-null, n >= 1, M >= 1");
+        return B200Q_EINVAL;
+    }
+    B200Q_CUDA_OK(launch_argmax((cudaStream_t)stream, logits, n, out_idx, out_val, M));
     return B200Q_OK;
 }
 

@@ -44,6 +44,7 @@
 
 #include "launch.h"
 #include "stream_core.cuh"
+#include "argmax.cuh"
 
 namespace b200q {
 
@@ -60,6 +61,8 @@ struct PinArgs {
     CostSplit cost;
     const float * xq_x; // when set, every CTA quantizes this fp32 activation itself
     NormArgs norm;      // RMSNorm applied to xq_x before it is quantized (w == nullptr: off)
+    int32_t * am_idx;   // argmax over the call's (single segment's) outputs, lowest index among equals (nullptr: off)
+    float * am_val;
     NextAct next;       // the call's output, quantized, as the following call's activation (x8 == nullptr: off)
     PeerSync sync;      // row-sharded calls: wait for / signal the peers inside this launch
     int32_t W, R, U, seg, P, Ppad; // P = U / seg partials per row, rows Ppad words apart
@@ -486,6 +489,8 @@ __device__ __forceinline__ void pin_produce_drain(const PinBars & bars, int S, c
 
 // Epilogue warp: partial sums of each step -> alpha, residual, outputs (and the next call's
 // activation).  rb / rphase walk the ring of partial-sum buffers and carry over between calls.
+// AMAX: the argmax of the outputs is tracked and contributed (kernel images of their own).
+template <bool AMAX>
 __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & g, uint32_t red, const PinBars & bars,
                                              int & rb, uint32_t & rphase) {
     const int lane = threadIdx.x & 31;
@@ -543,6 +548,8 @@ __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & 
         return true;
     }
     const uint32_t cost_lo = cost_at(a.cost, blockIdx.x, gridDim.x), cost_hi = cost_at(a.cost, blockIdx.x + 1, gridDim.x);
+    float am_best = 0.0f; // this lane's best output so far (argmax option; rows come in increasing order)
+    int am_i = -1;
     for (int si = 0; si < a.c.n_segs; si++) {
         const SegDev & sg = a.c.seg[si];
         const RowRange rr = cta_rows(a.c, si, cost_lo, cost_hi);
@@ -565,6 +572,10 @@ __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & 
                         v += __ldcg(&sg.residual[o]);
                     }
                     store_out(a.c, &sg.out[o], v);
+                    if (AMAX && (am_i < 0 || v > am_best)) {
+                        am_best = v;
+                        am_i = (int)o;
+                    }
                 }
             }
             __syncwarp();
@@ -575,6 +586,12 @@ __device__ __forceinline__ bool pin_epilogue(const PinArgs & a, const PinArgs & 
                 rb = 0;
                 rphase ^= 1;
             }
+        }
+    }
+    if (AMAX) { // one segment (checked on the host): the CTA's best joins the grid's; the last CTA writes the result
+        const unsigned long long k = argmax_warp(am_i >= 0 ? argmax_key(am_best, (uint32_t)am_i) : 0ull);
+        if (lane == 0) {
+            argmax_contribute(0, k, gridDim.x, a.c.seg[0].out, a.am_idx, a.am_val);
         }
     }
     return true;
@@ -682,7 +699,7 @@ __device__ __forceinline__ void pin_init_barriers(const PinBars & bars, uint32_t
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-template <bool NORM>
+template <bool NORM, bool AMAX>
 __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __grid_constant__ PinArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -722,7 +739,7 @@ __global__ void __launch_bounds__(kPinThreads, 1) gemv_pinned_kernel(const __gri
         // ---------------------------------------------------------------- epilogue warp
         int rb = 0;
         uint32_t rphase = 0;
-        if (!pin_epilogue(a, a, red, bars, rb, rphase)) {
+        if (!pin_epilogue<AMAX>(a, a, red, bars, rb, rphase)) {
             return;
         }
         if (a.sync.signal) {
@@ -861,7 +878,7 @@ __global__ void __launch_bounds__(32 * (kChainW + 2), 1) gemv_chain_kernel(const
         uint32_t rphase = 0;
         for (int ci = 0; ci < n; ci++) {
             const PinArgs & a = ch.call[ci];
-            if (!pin_epilogue(a, ch.call[0], red, bars, rb, rphase)) {
+            if (!pin_epilogue<false>(a, ch.call[0], red, bars, rb, rphase)) {
                 return;
             }
             __threadfence(); // this CTA's outputs of the call, before it is counted in
@@ -1108,10 +1125,12 @@ bool pinned_quantizes(const CallDev & c, const float * x, const float * act_up) 
 }
 
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * xq_x, const NextAct * next,
-                               const PeerSync * sync, const NormArgs * norm) {
+                               const PeerSync * sync, const NormArgs * norm, int32_t * am_idx, float * am_val) {
     PinArgs a;
     a.c = c;
     a.xq_x = xq_x;
+    a.am_idx = am_idx;
+    a.am_val = am_val;
     a.norm = (norm && xq_x) ? *norm : NormArgs{nullptr, 0.0f};
     a.next = next ? *next : NextAct{nullptr, nullptr, nullptr};
     memset(&a.sync, 0, sizeof(a.sync));
@@ -1131,9 +1150,16 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     trace_slot(a, true);
 #endif
     const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
-    const bool normed = a.norm.w != nullptr;
-    cudaError_t e = ensure_dynamic_smem(normed ? reinterpret_cast<const void *>(gemv_pinned_kernel<true>)
-                                               : reinterpret_cast<const void *>(gemv_pinned_kernel<false>), kPinSmem);
+    // the variants are kernel images of their own: the plain one carries neither option
+    void (*kern)(PinArgs) = gemv_pinned_kernel<false, false>;
+    if (a.norm.w && a.am_idx) {
+        kern = gemv_pinned_kernel<true, true>;
+    } else if (a.norm.w) {
+        kern = gemv_pinned_kernel<true, false>;
+    } else if (a.am_idx) {
+        kern = gemv_pinned_kernel<false, true>;
+    }
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(kern), kPinSmem);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1147,7 +1173,7 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return normed ? cudaLaunchKernelEx(&cfg, gemv_pinned_kernel<true>, a) : cudaLaunchKernelEx(&cfg, gemv_pinned_kernel<false>, a);
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 static void chain_fill(ChainArgs & ch, const CallDev * calls, const float * const * xq_x, const NextAct * next, int n,
@@ -1218,10 +1244,41 @@ cudaError_t read_pin_status(int * status, bool clear) {
             const uint32_t none = 0;
             e = cudaMemcpyToSymbol(g_chain_count, &none, sizeof(none));
         }
+        if (e == cudaSuccess) { // ... and an argmax tail its key and its count
+            static const unsigned long long zk[kArgmaxRows] = {};
+            static const unsigned int zd[kArgmaxRows] = {};
+            e = cudaMemcpyToSymbol(g_argmax_key, zk, sizeof(zk));
+            e = e == cudaSuccess ? cudaMemcpyToSymbol(g_argmax_done, zd, sizeof(zd)) : e;
+        }
     }
     return e;
 }
 
+} // namespace b200q
+
+namespace b200q {
+cudaError_t launch_argmax(cudaStream_t s, const float * logits, int n, int32_t * out_idx, float * out_val, int M) {
+    for (int r0 = 0; r0 < M; r0 += kArgmaxRows) { // a slot per row of a launch
+        const int m = M - r0 < kArgmaxRows ? M - r0 : kArgmaxRows;
+        int ctas = (n + 16383) / 16384; // at least 64 values per thread
+        ctas = ctas < 1 ? 1 : (ctas > kSMs ? kSMs : ctas);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ctas, (unsigned)m);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_kernel, logits + (size_t)r0 * n, n, out_idx + r0,
+                                           out_val ? out_val + r0 : static_cast<float *>(nullptr));
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
+    return cudaSuccess;
+}
 } // namespace b200q
 
 #include "moe_pinned.cuh"

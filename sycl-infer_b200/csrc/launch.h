@@ -18,7 +18,10 @@ bool pinned_supported(const CallDev & call);
 bool pinned_next_supported(const CallDev & call); // a call that also emits the next call's activation
 bool pinned_quantizes(const CallDev & call, const float * x, const float * act_up);
 cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & call, const float * xq_x, const NextAct * next,
-                               const PeerSync * sync = nullptr, const NormArgs * norm = nullptr);
+                               const PeerSync * sync = nullptr, const NormArgs * norm = nullptr, int32_t * am_idx = nullptr,
+                               float * am_val = nullptr);
+// row argmax, lowest index among equals (argmax.cuh)
+cudaError_t launch_argmax(cudaStream_t s, const float * logits, int n, int32_t * out_idx, float * out_val, int M);
 // two to four dependent single-token calls in one launch (gemv_pinned.cu); xq_x[i] != nullptr: call i
 // quantizes that fp32 vector itself; next[i].x8 != nullptr: call i emits the next call's activation
 bool chain_supported(const CallDev * calls, const float * const * xq_x, const NextAct * next, int n);
