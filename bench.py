@@ -338,6 +338,31 @@ def cell_layer_norm(ctx, L=4, steps=96):
             "status_clean": ctx.be.device_status() == 0, "l2": f"{L} rotating weight sets", "clocks": clocks}
 
 
+def cell_lm_head(ctx, rows=152064, K=5120, iters=20):
+    """The LM head of a greedy decode step: Q6_K rows x K GEMV whose launch also leaves the argmax of
+    the logits, against the same GEMV followed by the argmax launch.  One weight copy: 639 MB, five
+    times the L2."""
+    torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
+    from sycl_infer_b200.backend import alloc_act, gemv_seg
+    w = torch.from_numpy(pkg.synth.make_weight(14, rows, K, 0xB209)).cuda()
+    x = torch.from_numpy(pkg.synth.make_activation(1, K, 0xB20A)).cuda()
+    x8, xm, xs = alloc_act(1, K)
+    out = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    idx, val = torch.zeros(1, dtype=torch.int32, device="cuda"), torch.zeros(1, device="cuda")
+    seg = gemv_seg(w=w, type=14, K=K, n_rows=rows, x=x, x_stride=K, out=out, out_stride=rows, x8=x8, xmeta=xm, xsumq=xs)
+    g1 = ctx.capture(lambda: [be.quant_gemv_ex([seg], 1, argmax=(idx, val)) for _ in range(iters)])
+    (ms1, clocks) = clocked(ctx, lambda: ctx.time_ms(lambda i: g1.replay(), 5))
+    fused_idx = int(idx.cpu()[0])
+    g2 = ctx.capture(lambda: [(be.quant_gemv_ex([seg], 1), be.mtp_argmax(out, rows, idx, val, 1)) for _ in range(iters)])
+    ms2 = ctx.time_ms(lambda i: g2.replay(), 5)
+    us1, us2 = 1e3 * ms1 / (5 * iters), 1e3 * ms2 / (5 * iters)
+    nbytes = w.numel() + 4 * K + 4 * rows
+    return {"cell": f"LM head: Q6_K {rows}x{K} GEMV + argmax in one launch, batch 1", "us": us1, "us_two_launches": us2,
+            "bytes": nbytes, "GB/s": nbytes / us1 / 1e3, "frac_of_measured_hbm": ctx.frac(nbytes / us1 / 1e3),
+            "same_token": fused_idx == int(idx.cpu()[0]) == int(out.argmax().cpu()), "launches_per_iter": 1,
+            "l2": "one 639 MB weight", "clocks": clocks}
+
+
 def cell_prefill(ctx, name, M, rows=17408, K=5120, iters=3):
     """Config 2: M tokens x (Q4_K weight of `rows` x K); quantizer + tensor-core GEMM per iteration."""
     torch, pkg, be = ctx.torch, ctx.pkg, ctx.be
@@ -545,6 +570,7 @@ def gpu_arm(args):
         if world == 1:
             safe(cells, cell_token, ctx, layers)
             safe(cells, cell_layer_norm, ctx)
+            safe(cells, cell_lm_head, ctx)
             safe(cells, cell_single_matrix, ctx, "config 0: Q4_K 4096x4096 GEMV, batch 1", 12, 4096, 4096)
             safe(cells, cell_layer, ctx, "config 1: dense layer Q4_K_M, batch 16", "Q4_K_M", 16)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=512 x 5120 x 17408 Q4_K", 512)
