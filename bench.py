@@ -564,7 +564,7 @@ def gpu_arm(args):
         ms_gemv = ctx.time_ms(lambda i: gemv_only(), reps)
     clocks = sampler.summary()
 
-    ctx.ceilings = measure_ceilings(ctx) if world == 1 else {}
+    ctx.ceilings = measure_ceilings(ctx) if world == 1 and not args.no_ceilings else {}
     cells = []
     if not args.no_cells:
         if world == 1:
@@ -640,6 +640,7 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: GEMV epilogue stores rows on every GPU (peer), or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels from the host instead of CUDA graphs")
+    ap.add_argument("--no-ceilings", action="store_true", help="skip the read-only HBM and int8 tensor-core probes")
     ap.add_argument("--step-graphs", action="store_true", help="one CUDA graph per layer step instead of one per L steps")
     args = ap.parse_args()
     if args.impl == "reference":
