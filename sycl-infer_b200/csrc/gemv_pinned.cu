@@ -39,6 +39,7 @@
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // B200Q_ETIMEOUT in a status word the host reads (b200q_device_status) and the role returns.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -183,7 +184,7 @@ __device__ __forceinline__ void pin_quantize(uint32_t pack, const CallDev & c, u
             if (task < n_tasks) {
                 const uint4 u = lds128(xraw + 16u * (uint32_t)task);
                 fb[i] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-                if (NORM) {
+                if (NORM && nw) {
                     const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw) + task);
                     fb[i].x = __fmul_rn(__fmul_rn(fb[i].x, nscale), wv.x);
                     fb[i].y = __fmul_rn(__fmul_rn(fb[i].y, nscale), wv.y);
@@ -625,7 +626,7 @@ __device__ __forceinline__ bool pin_activation(const PinArgs & a, const PinArgs 
     }
     if (a.xq_x) {
         float nscale = 1.0f;
-        if (NORM) {
+        if (NORM && a.norm.w) {
             // 1 / sqrt(sum(x^2) / K + eps), the sum in the order of the reference's widest host path
             // (sumsq_f32_avx512, common.cpp:278-290): sixteen accumulators acc[j] = fma(x, x, acc[j])
             // over i = 16k + j, halved 16 -> 8 -> 4, then (t0 + t2) + (t1 + t3)
@@ -1150,11 +1151,20 @@ cudaError_t launch_gemv_pinned(cudaStream_t s, const CallDev & c, const float * 
     trace_slot(a, true);
 #endif
     const size_t smem = (size_t)a.off_tiles + (size_t)a.stages * a.stage_bytes;
-    // the variants are kernel images of their own: the plain one carries neither option
+    // The variants are kernel images of their own: the plain one carries neither option.  Two large
+    // images taking turns in a stream run slower than either alone (a layer whose q|k|v and gate|up
+    // launches carry a norm and whose o and down launches do not: 76 us against 60), so once a
+    // call with a norm has been seen in this process every launch uses the image that can do it
+    // (0.35 us per layer step dearer than the plain one when no norm is given).
+    static std::atomic<bool> norm_image{false};
+    if (a.norm.w) {
+        norm_image.store(true, std::memory_order_relaxed);
+    }
+    const bool with_norm = norm_image.load(std::memory_order_relaxed);
     void (*kern)(PinArgs) = gemv_pinned_kernel<false, false>;
-    if (a.norm.w && a.am_idx) {
+    if (with_norm && a.am_idx) {
         kern = gemv_pinned_kernel<true, true>;
-    } else if (a.norm.w) {
+    } else if (with_norm) {
         kern = gemv_pinned_kernel<true, false>;
     } else if (a.am_idx) {
         kern = gemv_pinned_kernel<false, true>;
