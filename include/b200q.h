@@ -316,6 +316,46 @@ int b200q_device_status(int * status /*host*/, int clear);
  * they share device-side words. */
 int b200q_argmax(void * stream, const float * logits, int n, int32_t * out_idx, float * out_val /*may be NULL*/, int M);
 
+/* ---- GGUF files -> one device blob (the loader side of the path: src/model/gguf.{h,cpp} and the
+ * whole-file device blob of src/backend/weight_store.h:28-62 in the reference).  The raw block stream
+ * a tensor has on disk is what the kernels read, so loading is parsing the tensor table and copying
+ * the data section(s) into ONE device allocation the caller owns.  A tensor of dims [K][N] is N rows
+ * of K values: b200q_seg.w = blob + blob_offset, K = dims[0], n_rows = dims[1]; an expert bank
+ * [K][N][E] is E planes of N rows, plane e at blob_offset + e * N * row_bytes.  A split file
+ * ("...-00001-of-0000N.gguf", any shard may be named) is opened as a whole; every shard's data section
+ * gets its own 256-byte aligned place in the blob.  Files are treated as untrusted input. ---- */
+typedef struct b200q_gguf b200q_gguf;
+typedef struct b200q_gguf_tensor {
+    const char * name;       /* owned by the handle */
+    uint32_t type;           /* ggml type id (B200Q_Q4_K = 12, ...) */
+    uint32_t n_dims;         /* 1..4 */
+    uint64_t dims[4];        /* dims[0] = row length (values), unused dims are 1 */
+    uint64_t n_rows;         /* product of dims[1..] */
+    uint64_t row_bytes;
+    uint64_t nbytes;
+    uint64_t blob_offset;    /* where the tensor starts in the device blob */
+    int32_t shard;           /* which file of a split it comes from */
+    const void * host_data;  /* the tensor in the file mapping (valid until b200q_gguf_close) */
+} b200q_gguf_tensor;
+int b200q_gguf_open(const char * path, b200q_gguf ** out);
+void b200q_gguf_close(b200q_gguf * g);
+int b200q_gguf_n_tensors(const b200q_gguf * g);
+int b200q_gguf_n_shards(const b200q_gguf * g);
+uint32_t b200q_gguf_version(const b200q_gguf * g);
+int b200q_gguf_tensor_at(const b200q_gguf * g, int i, b200q_gguf_tensor * out);
+int b200q_gguf_find(const b200q_gguf * g, const char * name); /* index, -1 when absent */
+uint64_t b200q_gguf_blob_bytes(const b200q_gguf * g);          /* size of the device blob to allocate */
+/* copies every shard's data section to its place in `blob` (device, 256-byte aligned, blob_bytes large) */
+int b200q_gguf_upload(const b200q_gguf * g, void * blob, void * stream);
+/* metadata: GGUF value type of a key (0..12; 8 = string, 9 = array; -1 = absent), then the value */
+int b200q_gguf_meta_type(const b200q_gguf * g, const char * key);
+int b200q_gguf_meta_u64(const b200q_gguf * g, const char * key, uint64_t * out); /* integers, bool */
+int b200q_gguf_meta_f64(const b200q_gguf * g, const char * key, double * out);   /* numbers */
+const char * b200q_gguf_meta_str(const b200q_gguf * g, const char * key);        /* NULL unless a string */
+int b200q_gguf_meta_arr(const b200q_gguf * g, const char * key, uint32_t * elem_type, uint64_t * count);
+const char * b200q_gguf_meta_arr_str(const b200q_gguf * g, const char * key, uint64_t i);
+const void * b200q_gguf_meta_arr_data(const b200q_gguf * g, const char * key);   /* packed elements, not strings */
+
 /* Measurement instruments (no reference counterpart): the ceilings a benchmark reports the kernels
  * against.  The caller times them (events on `stream`).
  * b200q_probe_hbm_read: one pass of independent 16-byte loads over buf[0, bytes) - what a kernel

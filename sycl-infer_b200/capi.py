@@ -69,6 +69,13 @@ class ChainCall(C.Structure):
                 ("flags", C.c_uint32), ("next", C.POINTER(NextAct))]
 
 
+class GgufTensor(C.Structure):
+    """struct b200q_gguf_tensor."""
+    _fields_ = [("name", C.c_char_p), ("type", C.c_uint32), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4),
+                ("n_rows", C.c_uint64), ("row_bytes", C.c_uint64), ("nbytes", C.c_uint64), ("blob_offset", C.c_uint64),
+                ("shard", C.c_int32), ("host_data", _vp)]
+
+
 _SIGS = {
     "b200q_last_error": (C.c_char_p, []),
     "b200q_version": (C.c_int, []),
@@ -97,6 +104,22 @@ _SIGS = {
     "b200q_i8_block_dots": (C.c_int, [_vp, _vp, C.c_uint32, C.c_int, C.c_int, _vp, C.c_int, C.c_int, _vp]),
     "b200q_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "b200q_argmax": (C.c_int, [_vp, _vp, C.c_int, _vp, _vp, C.c_int]),
+    "b200q_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(_vp)]),
+    "b200q_gguf_close": (None, [_vp]),
+    "b200q_gguf_n_tensors": (C.c_int, [_vp]),
+    "b200q_gguf_n_shards": (C.c_int, [_vp]),
+    "b200q_gguf_version": (C.c_uint32, [_vp]),
+    "b200q_gguf_tensor_at": (C.c_int, [_vp, C.c_int, C.POINTER(GgufTensor)]),
+    "b200q_gguf_find": (C.c_int, [_vp, C.c_char_p]),
+    "b200q_gguf_blob_bytes": (C.c_uint64, [_vp]),
+    "b200q_gguf_upload": (C.c_int, [_vp, _vp, _vp]),
+    "b200q_gguf_meta_type": (C.c_int, [_vp, C.c_char_p]),
+    "b200q_gguf_meta_u64": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "b200q_gguf_meta_f64": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "b200q_gguf_meta_str": (C.c_char_p, [_vp, C.c_char_p]),
+    "b200q_gguf_meta_arr": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
+    "b200q_gguf_meta_arr_str": (C.c_char_p, [_vp, C.c_char_p, C.c_uint64]),
+    "b200q_gguf_meta_arr_data": (_vp, [_vp, C.c_char_p]),
     "b200q_probe_hbm_read": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "b200q_probe_i8_mma": (C.c_int, [_vp, C.c_int, _vp]),
     "b200q_synchronize": (C.c_int, [_vp]),
