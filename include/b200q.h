@@ -7,8 +7,12 @@
  * library allocates nothing and never falls back to the CPU: an unsupported
  * request is an error.  State the library keeps: a thread-local error string;
  * per GPU a few device words (the status words behind b200q_device_status, the
- * completion counter of b200q_moe_route_csr) and the 48 KB scratch array of
- * b200q_quant_gemv_static; per process a cache of per-device kernel attributes.
+ * completion counters of b200q_moe_route_csr and b200q_quant_gemv_chain, the
+ * keys and counters of b200q_argmax and of the argmax option) and the 48 KB
+ * scratch array of b200q_quant_gemv_static; per process a cache of per-device
+ * kernel attributes and one flag (a call with the norm option has been seen: from
+ * then on single-token launches use the kernel image that can apply a norm); per
+ * b200q_gguf handle the file mappings.
  *
  * Launch chaining.  GEMV launches use programmatic stream serialization: a kernel
  * may start streaming WEIGHTS while the previous kernel of the stream (when that
