@@ -1,0 +1,141 @@
+"""The caller's side of the GEMV path: a forward plan and its replay as one CUDA graph.
+
+The reference engine describes a forward pass as a `seg_plan` - a flat list of GEMV segments cut
+into calls, each call with the activation its quantizer reads (src/engine/engine_types.h:11-133) -
+and replays it with `record_forward` into a command graph per token (src/engine/engine.h:1269,
+src/engine/graph.cpp:145-429).  `SegPlan` mirrors that structure (begin_call / add / set_xq /
+finalize, same meaning) and adds what this library can do with it: `finalize()` lowers the calls to
+launches, pairing a gate|up call with the down call that consumes silu(gate)*up (the former emits
+the latter's quantized activation, the latter runs without a quantizer), folding a call's RMSNorm
+into its quantizer and hanging the argmax on the head call; `record()` captures the launches of a
+whole token into ONE CUDA graph and `replay()` runs it.
+"""
+from dataclasses import dataclass, field
+
+from .backend import gemv_seg
+
+MAX_SEGS = 8
+
+
+@dataclass
+class Call:
+    """One call of the plan: segments sharing one quantized activation (seg_plan::call_t)."""
+    tb: int
+    segs: list = field(default_factory=list)
+    x: object = None          # fp32 activation the call's quantizer reads (xq_t.x)
+    up: object = None         # non-None: the activation is silu(x) * up (xq_t.up)
+    norm: tuple = None        # (weight, eps): RMSNorm of x ahead of the quantizer
+    argmax: tuple = None      # (idx, val or None): argmax of the outputs (the head call)
+    # set by finalize()
+    prequantized: bool = False
+    next_act: tuple = None
+
+    @property
+    def total_rows(self):
+        return sum(s.n_rows for s in self.segs)
+
+
+def _same(a, b):
+    return a is not None and b is not None and a.data_ptr() == b.data_ptr()
+
+
+class SegPlan:
+    def __init__(self):
+        self.calls = []
+        self.lowered = None
+        self.graph = None
+
+    # ---- building (names and meaning of seg_plan's builders) ---------------------------------
+    def begin_call(self, tb=1):
+        self.calls.append(Call(tb=tb))
+        self.lowered = None
+
+    def add(self, seg: gemv_seg):
+        self.calls[-1].segs.append(seg)
+
+    def set_xq(self, x, up=None):
+        self.calls[-1].x, self.calls[-1].up = x, up
+
+    def set_norm(self, weight, eps):
+        self.calls[-1].norm = (weight, float(eps))
+
+    def set_argmax(self, idx, val=None):
+        self.calls[-1].argmax = (idx, val)
+
+    # ---- validation + lowering ------------------------------------------------------------------
+    def validate(self):
+        """Structural self-check (seg_plan::validate): raises ValueError naming the first violation."""
+        for ci, c in enumerate(self.calls):
+            if not 1 <= len(c.segs) <= MAX_SEGS:
+                raise ValueError(f"call {ci}: {len(c.segs)} segments (1..{MAX_SEGS})")
+            if c.x is None:
+                raise ValueError(f"call {ci}: no activation (set_xq)")
+            s0 = c.segs[0]
+            for si, s in enumerate(c.segs):
+                if s.K != s0.K or not _same(s.x8, s0.x8) or not _same(s.xmeta, s0.xmeta) or not _same(s.xsumq, s0.xsumq):
+                    raise ValueError(f"call {ci}: segment {si} does not share the call's K and activation scratch")
+                if s.n_rows < 1 or s.K % 256:
+                    raise ValueError(f"call {ci}: segment {si} has no rows or a K that is not a multiple of 256")
+            if c.tb < 1:
+                raise ValueError(f"call {ci}: tb < 1")
+            if c.tb != 1 and (c.norm or c.argmax):
+                raise ValueError(f"call {ci}: norm / argmax are single-token options")
+
+    def finalize(self):
+        """Validate, then decide the launches.  A single-token call whose activation is silu(g)*u of
+        the two segments of the call right before it (equal rows, a multiple of 32, one type) is
+        paired with it: no quantizer runs between them."""
+        self.validate()
+        for c in self.calls:
+            c.prequantized, c.next_act = False, None
+        for p, c in zip(self.calls, self.calls[1:]):
+            if (c.tb == 1 and p.tb == 1 and c.up is not None and c.norm is None and p.argmax is None and len(p.segs) == 2 and
+                    _same(p.segs[0].out, c.x) and _same(p.segs[1].out, c.up) and p.segs[0].type == p.segs[1].type and
+                    p.segs[0].n_rows == p.segs[1].n_rows and p.segs[0].n_rows % 32 == 0 and
+                    p.segs[0].n_rows == c.segs[0].K):
+                s0 = c.segs[0]
+                p.next_act, c.prequantized = (s0.x8, s0.xmeta, s0.xsumq), True
+        self.lowered = True
+        return self
+
+    def launches(self):
+        """Kernel launches of one replay (the single-token kernel quantizes plain activations itself;
+        silu(x)*up outside a pairing and several tokens take a quantizer launch)."""
+        assert self.lowered, "finalize() first"
+        n = 0
+        for c in self.calls:
+            n += 1 if c.prequantized or (c.tb == 1 and c.up is None) else 2
+        return n
+
+    # ---- execution ------------------------------------------------------------------------------
+    def run(self, be):
+        assert self.lowered, "finalize() first"
+        for c in self.calls:
+            segs = []
+            for s in c.segs:  # the segments carry the call's activation, as the C ABI wants it
+                s.x, s.act_up, s.x_stride = c.x, c.up, c.x.shape[-1]
+                segs.append(s)
+            if c.tb == 1:
+                be.quant_gemv_ex(segs, 1, prequantized=c.prequantized, next_act=c.next_act, norm=c.norm, argmax=c.argmax)
+            else:
+                be.quant_gemv(segs, c.tb)
+
+    def record(self, be, stream):
+        """Capture one pass over the plan into a CUDA graph on `stream` (record_forward)."""
+        import torch
+        prev = be._stream
+        be._stream = stream
+        try:
+            with torch.cuda.stream(stream):
+                self.run(be)  # warm-up: attributes, lazy state
+                stream.synchronize()
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=stream):
+                    self.run(be)
+        finally:
+            be._stream = prev
+        torch.cuda.synchronize()
+        return self.graph
+
+    def replay(self):
+        self.graph.replay()
