@@ -26,6 +26,8 @@ class Call:
     up: object = None         # non-None: the activation is silu(x) * up (xq_t.up)
     norm: tuple = None        # (weight, eps): RMSNorm of x ahead of the quantizer
     argmax: tuple = None      # (idx, val or None): argmax of the outputs (the head call)
+    # a routed-MoE call has no segments: it dispatches the MoE launch sequence (call_t::moe_routed)
+    moe: tuple = None         # (moe_t, MoeScratch, out): out[t] += sum_j w[t,j] * expert(x[t])
     # set by finalize()
     prequantized: bool = False
     next_act: tuple = None
@@ -62,10 +64,20 @@ class SegPlan:
     def set_argmax(self, idx, val=None):
         self.calls[-1].argmax = (idx, val)
 
+    def begin_moe_call(self, M, scratch, x, out, tb):
+        """A routed-MoE FFN in the call sequence (seg_plan::begin_moe_call): router, CSR, quantizers,
+        grouped gate|up and down, reduce - recorded into the same graph as the dense calls."""
+        self.calls.append(Call(tb=tb, x=x, moe=(M, scratch, out)))
+        self.lowered = None
+
     # ---- validation + lowering ------------------------------------------------------------------
     def validate(self):
         """Structural self-check (seg_plan::validate): raises ValueError naming the first violation."""
         for ci, c in enumerate(self.calls):
+            if c.moe is not None:
+                if c.segs or c.x is None or c.norm or c.argmax:
+                    raise ValueError(f"call {ci}: a MoE call has an activation and nothing else")
+                continue
             if not 1 <= len(c.segs) <= MAX_SEGS:
                 raise ValueError(f"call {ci}: {len(c.segs)} segments (1..{MAX_SEGS})")
             if c.x is None:
@@ -89,7 +101,7 @@ class SegPlan:
         for c in self.calls:
             c.prequantized, c.next_act = False, None
         for p, c in zip(self.calls, self.calls[1:]):
-            if (c.tb == 1 and p.tb == 1 and c.up is not None and c.norm is None and p.argmax is None and len(p.segs) == 2 and
+            if (p.moe is None and c.moe is None and c.tb == 1 and p.tb == 1 and c.up is not None and c.norm is None and p.argmax is None and len(p.segs) == 2 and
                     _same(p.segs[0].out, c.x) and _same(p.segs[1].out, c.up) and p.segs[0].type == p.segs[1].type and
                     p.segs[0].n_rows == p.segs[1].n_rows and p.segs[0].n_rows % 32 == 0 and
                     p.segs[0].n_rows == c.segs[0].K):
@@ -104,13 +116,21 @@ class SegPlan:
         assert self.lowered, "finalize() first"
         n = 0
         for c in self.calls:
-            n += 1 if c.prequantized or (c.tb == 1 and c.up is None) else 2
+            if c.moe is not None:
+                n += 7  # token quantizer, router logits, softmax/top-k + CSR, gate|up, quantizer of h, down, reduce
+            else:
+                n += 1 if c.prequantized or (c.tb == 1 and c.up is None) else 2
         return n
 
     # ---- execution ------------------------------------------------------------------------------
     def run(self, be):
         assert self.lowered, "finalize() first"
+        from .moe import moe_call
         for c in self.calls:
+            if c.moe is not None:
+                M, scratch, out = c.moe
+                moe_call(be, M, scratch, c.x, c.tb, out)
+                continue
             segs = []
             for s in c.segs:  # the segments carry the call's activation, as the C ABI wants it
                 s.x, s.act_up, s.x_stride = c.x, c.up, c.x.shape[-1]

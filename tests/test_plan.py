@@ -187,3 +187,46 @@ def be_xq(be, x, up):
           xs, None, 1, K)
     be.synchronize()
     return x8.cpu().numpy(), xm.cpu().numpy(), xs.cpu().numpy()
+
+
+@pytest.mark.gpu
+def test_moe_call_inside_a_plan(orc):
+    """A dense call and a routed-MoE call recorded into one graph: the replay gives what the same
+    launches give when made directly."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from sycl_infer_b200.moe import MoeScratch, make_synthetic_moe, moe_call
+    be = pkg.make_cuda_backend(0)
+    dev = torch.device("cuda")
+    n_tok, E, top_k, n_embd, n_ff = 4, 16, 2, 512, 256
+    _, M = make_synthetic_moe(E, top_k, n_embd, n_ff, (12, 12, 12), seed=3, with_router=True)
+    x = torch.from_numpy(pkg.synth.make_activation(n_tok, n_embd, 901)).cuda()
+    wq = torch.from_numpy(pkg.synth.make_weight(12, n_embd, n_embd, 902)).cuda()
+
+    def build(S, hbuf, out):
+        p = SegPlan()
+        p.begin_call(n_tok)
+        a8 = torch.zeros(n_tok * n_embd, dtype=torch.int8, device=dev)
+        am = torch.zeros(n_tok * n_embd // 16, dtype=torch.float32, device=dev)
+        asq = torch.zeros(n_tok * n_embd // 16, dtype=torch.int32, device=dev)
+        p.add(gemv_seg(w=wq, type=12, K=n_embd, n_rows=n_embd, out=hbuf.view(-1), out_stride=n_embd,
+                       alpha=1.0 / (3.0 * n_embd ** 0.5), x8=a8, xmeta=am, xsumq=asq))
+        p.set_xq(x)
+        p.begin_moe_call(M, S, hbuf, out, n_tok)
+        return p.finalize()
+
+    S1, h1, o1 = MoeScratch(M, n_tok), torch.zeros(n_tok, n_embd, device=dev), torch.zeros(n_tok, n_embd, device=dev)
+    plan = build(S1, h1, o1)
+    assert plan.launches() == 2 + 7
+    st = torch.cuda.Stream()
+    plan.record(be, st)
+    o1.zero_()
+    with torch.cuda.stream(st):
+        plan.replay()
+    st.synchronize()
+    S2, h2, o2 = MoeScratch(M, n_tok), torch.zeros(n_tok, n_embd, device=dev), torch.zeros(n_tok, n_embd, device=dev)
+    build(S2, h2, o2).run(be)
+    be.synchronize()
+    assert be.device_status() == 0
+    assert torch.equal(h1, h2) and torch.equal(o1, o2) and torch.equal(S1.ids, S2.ids)
+    assert float(o1.abs().max()) > 0
