@@ -244,13 +244,31 @@ int fail(b200q_gguf * g, int code, const char * fmt, const std::string & what) {
 
 extern "C" {
 
+static int gguf_open_impl(const char * path, b200q_gguf * g);
+
 int b200q_gguf_open(const char * path, b200q_gguf ** out) {
     if (!path || !out) {
         set_error("b200q_gguf_open: path and out must be non-null");
         return B200Q_EINVAL;
     }
     *out = nullptr;
-    b200q_gguf * g = new b200q_gguf();
+    b200q_gguf * g = nullptr;
+    try { // no exception may cross the C boundary (allocation failure on a hostile file)
+        g = new b200q_gguf();
+        const int rc = gguf_open_impl(path, g);
+        if (rc == B200Q_OK) {
+            *out = g;
+        }
+        return rc;
+    } catch (...) {
+        delete g;
+        set_error("b200q_gguf_open: out of memory while parsing %s", path);
+        return B200Q_EINVAL;
+    }
+}
+
+// parses into g; on failure g has been deleted
+static int gguf_open_impl(const char * path, b200q_gguf * g) {
     const std::vector<std::string> names = shard_names(path);
     for (size_t si = 0; si < names.size(); si++) {
         Shard sh;
@@ -364,7 +382,6 @@ int b200q_gguf_open(const char * path, b200q_gguf ** out) {
             t.blob_offset = s.slot + t.offset;
         }
     }
-    *out = g;
     return B200Q_OK;
 }
 
