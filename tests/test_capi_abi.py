@@ -29,6 +29,29 @@ def test_library_exports_every_declared_symbol(pkg):
     assert lib.dll.b200q_version() == 1
 
 
+def test_header_is_plain_c_and_structs_match_the_binding(tmp_path, pkg):
+    """include/b200q.h compiles as C11 (a host in C, cgo or any FFI generator reads it as such), and
+    the struct sizes a C compiler derives from it are the sizes of the ctypes mirrors."""
+    import shutil
+    import subprocess
+    from sycl_infer_b200 import capi
+    if not shutil.which("gcc"):
+        pytest.skip("no gcc")
+    names = [("b200q_seg", capi.Seg), ("b200q_peers", capi.Peers), ("b200q_next_act", capi.NextAct),
+             ("b200q_peer_sync", capi.PeerSync), ("b200q_norm", capi.Norm), ("b200q_argmax_out", capi.ArgmaxOut),
+             ("b200q_call_opts", capi.CallOpts), ("b200q_chain_call", capi.ChainCall), ("b200q_gguf_tensor", capi.GgufTensor)]
+    src = '#include <stdio.h>\n#include "b200q.h"\nint main(void) {\n'
+    src += "".join(f'  printf("%zu\\n", sizeof({n}));\n' for n, _ in names) + "  return 0;\n}\n"
+    c = tmp_path / "sizes.c"
+    c.write_text(src)
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"), str(c),
+                    "-o", str(exe)], check=True)
+    sizes = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    for (n, ct), sz in zip(names, sizes):
+        assert ctypes.sizeof(ct) == sz, f"{n}: C says {sz}, the ctypes mirror {ctypes.sizeof(ct)}"
+
+
 def test_row_bytes_table(pkg, po):
     # quant_row_bytes of the reference (src/common/quant.h:1177-1198; tests/model/test_quant_synth.cpp:106-111)
     lib = pkg.load_lib()
