@@ -52,6 +52,36 @@ def test_header_is_plain_c_and_structs_match_the_binding(tmp_path, pkg):
         assert ctypes.sizeof(ct) == sz, f"{n}: C says {sz}, the ctypes mirror {ctypes.sizeof(ct)}"
 
 
+def test_cpp_host_links_against_the_library(tmp_path, pkg):
+    """A host written in C++ (the reference's language) links libb200q.so through the header alone and
+    gets statuses and messages where the reference throws: no Python, no torch in between."""
+    import shutil
+    import subprocess
+    if not shutil.which("g++"):
+        pytest.skip("no g++")
+    lib_dir = os.path.dirname(pkg.load_lib().path)
+    src = tmp_path / "host.cpp"
+    src.write_text('''
+#include <cstdio>
+#include "b200q.h"
+int main() {
+    b200q_seg s{};
+    s.w = (const void *)0x1000; s.type = B200Q_Q4_K; s.K = 300; s.n_rows = 4; s.out = (float *)0x2000; s.out_stride = 4;
+    const int rc = b200q_i8_gemv(nullptr, &s, 1);
+    std::printf("%d|%s|%zu|%d\\n", rc, b200q_last_error(), b200q_row_bytes(B200Q_Q6_K, 4096), b200q_version());
+    b200q_gguf * g = nullptr;
+    std::printf("%d|%d\\n", b200q_gguf_open("/no/such/file.gguf", &g), g == nullptr);
+    return 0;
+}
+''')
+    exe = tmp_path / "host"
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-L", lib_dir,
+                    "-lb200q", f"-Wl,-rpath,{lib_dir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines()
+    assert out[0] == "1|K must be a positive multiple of 256 (got 300)|3360|1"
+    assert out[1] == "1|1"
+
+
 def test_row_bytes_table(pkg, po):
     # quant_row_bytes of the reference (src/common/quant.h:1177-1198; tests/model/test_quant_synth.cpp:106-111)
     lib = pkg.load_lib()
