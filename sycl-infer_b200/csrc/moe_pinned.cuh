@@ -117,11 +117,17 @@ __global__ void __launch_bounds__(kPinThreads, 1) moe_pinned_kernel(const __grid
     // the expert lists come from the router, the activation from the quantizer or from gate|up
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
+        // expert of every CSR position; a position no active expert claims (a pair whose id was not
+        // a valid expert: the CSR builder leaves it out) stays -1 and every role skips it
+        for (int q = threadIdx.x; q < a.n_pairs; q += blockDim.x) {
+            expert_of[q] = -1;
+        }
+        __syncthreads();
         const int n_act = min(*a.n_active, a.max_active);
-        for (int s = threadIdx.x; s < n_act; s += blockDim.x) { // expert of every CSR position
+        for (int s = threadIdx.x; s < n_act; s += blockDim.x) {
             const int e = a.active[s];
             const int q1 = min(a.off[e + 1], a.n_pairs);
-            for (int q = a.off[e]; q < q1; q++) {
+            for (int q = max(a.off[e], 0); q < q1; q++) {
                 expert_of[q] = e;
             }
         }
@@ -138,6 +144,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) moe_pinned_kernel(const __grid
         MoeWalk w = moe_walk_begin(a);
         while (moe_walk_next(a, w)) {
             const int e = expert_of[w.i];
+            if (e < 0) {
+                continue;
+            }
             const uint8_t * wa = a.bank_a + (size_t)e * a.plane_a;
             const uint8_t * wb = a.p.paired ? a.bank_b + (size_t)e * a.plane_b : wa;
             for (int r0 = w.lo; r0 < w.hi; r0 += step_rows) {
@@ -180,6 +189,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) moe_pinned_kernel(const __grid
         const int step_rows = a.p.paired ? H : R;
         MoeWalk w = moe_walk_begin(a);
         while (moe_walk_next(a, w)) {
+            if (expert_of[w.i] < 0) {
+                continue;
+            }
             const int pr = a.pair[w.i];
             float * orow = a.out + (size_t)pr * a.out_stride;
             for (int r0 = w.lo; r0 < w.hi; r0 += step_rows) {
@@ -247,6 +259,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) moe_pinned_kernel(const __grid
         MoeWalk w = moe_walk_begin(a);
         int s = 0, last = -1;
         while (moe_walk_next(a, w)) {
+            if (expert_of[w.i] < 0) {
+                continue;
+            }
             if (w.i != last && s < kMoePinSegs) {
                 const int pr = a.pair[w.i];
                 moe_pin_stage(packs + (uint32_t)(s * a.pack_bytes), a, a.top_k > 0 ? pr / a.top_k : pr, (int)threadIdx.x, 32 * W);
@@ -265,6 +280,9 @@ __global__ void __launch_bounds__(kPinThreads, 1) moe_pinned_kernel(const __grid
     MoeWalk w = moe_walk_begin(a);
     int s = -1, last = -1;
     while (moe_walk_next(a, w)) {
+        if (expert_of[w.i] < 0) {
+            continue;
+        }
         if (w.i != last) {
             last = w.i;
             s++;

@@ -193,3 +193,40 @@ def test_csr_separate_and_fused_agree(be, pkg, n_tok, E, top_k):
     assert na == len(np.unique(flat)) and np.array_equal(active, np.unique(flat))
     for e in range(E):
         assert np.array_equal(pair[off[e]:off[e + 1]], np.nonzero(flat == e)[0])
+
+
+def test_pairs_with_invalid_expert_ids_are_left_out(be, pkg):
+    """Expert ids outside 0..n_expert-1 (a caller's own router may emit -1 for "no expert"): the CSR
+    builder leaves those pairs out of every list, the expert kernels never touch their rows of h and
+    acc, and every other pair's rows are bit-identical to a run on the same lists with the bad pairs
+    routed to a valid expert."""
+    from sycl_infer_b200.moe import (MoeScratch, make_synthetic_moe, moe_actq_launch, moe_csr_launch,
+                                     moe_grp_down_launch, moe_grp_gate_up_launch)
+    E, top_k, n_embd, n_ff, n_tok = 8, 2, 512, 256, 6
+    _, dev = make_synthetic_moe(E, top_k, n_embd, n_ff, (12, 12, 14), 21)
+    x = torch.from_numpy(pkg.synth.make_activation(n_tok, n_embd, 77)).cuda()
+    n_pairs, n_act_max = n_tok * top_k, min(E, n_tok * top_k)
+    good = np.array([[0, 3], [3, 5], [7, 0], [2, 3], [5, 6], [1, 7]], np.int32)
+    bad = good.copy()
+    bad[1, 0], bad[3, 1], bad[5, 0] = -1, E, 1 << 20
+    res = []
+    for ids in (good, bad):
+        S = MoeScratch(dev, n_tok)
+        S.ids.copy_(torch.from_numpy(ids))
+        S.h.fill_(7.0)
+        S.acc.fill_(7.0)
+        moe_actq_launch(be, x, n_embd, n_tok, n_embd, *S.xq)
+        moe_csr_launch(be, S.ids, n_pairs, E, S.off, S.pair, S.active, S.n_active)
+        moe_grp_gate_up_launch(be, dev, S.off, S.pair, S.active, S.n_active, n_act_max, *S.xq, n_tok, S.h, n_ff)
+        moe_actq_launch(be, S.h, n_ff, n_pairs, n_ff, *S.hq)
+        moe_grp_down_launch(be, dev, S.off, S.pair, S.active, S.n_active, n_act_max, *S.hq, n_pairs, S.acc, n_embd)
+        be.synchronize()
+        assert be.device_status() == 0
+        res.append((S.off.cpu().numpy().copy(), S.h.cpu().numpy().copy(), S.acc.cpu().numpy().copy()))
+    (off_g, h_g, acc_g), (off_b, h_b, acc_b) = res
+    assert off_g[-1] == n_pairs and off_b[-1] == n_pairs - 3
+    left_out = np.nonzero((bad.reshape(-1) < 0) | (bad.reshape(-1) >= E))[0]
+    kept = np.setdiff1d(np.arange(n_pairs), left_out)
+    assert np.all(h_b[left_out] == 7.0) and np.all(acc_b[left_out] == 7.0)
+    assert np.array_equal(h_b[kept], h_g[kept]) and np.array_equal(acc_b[kept], acc_g[kept])
+    assert not np.any(h_g[left_out] == 7.0)
