@@ -21,6 +21,7 @@
 // acc_full (MMA -> epilogue) and acc_empty (epilogue -> MMA) per tensor-memory accumulator, of
 // which up to 16 form a ring.  All waits are bounded; TMEM is always released.
 #include <cstdlib>
+#include <cstring>
 
 #include "async.cuh"
 #include "decode.cuh"
@@ -51,8 +52,25 @@ template <int NT, int EW, int PG> struct Roles {
     static constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 1);
 };
 
+// Grouped form (routed MoE, more than a few tokens per expert): the row tiles of every active
+// expert's plane, each against the tokens routed to that expert (CSR lists), in one launch.  A tile
+// of the fused gate|up form interleaves 64 gate rows (even tensor-memory lanes) with the 64 up rows
+// of the same indices (odd lanes): the two values of h = silu(gate) * up meet in neighbouring lanes.
+struct GroupDev {
+    const uint8_t * bank_a, * bank_b; // expert planes (bank_b: the up planes of the fused form)
+    size_t plane_a, plane_b;          // bytes from one expert's plane to the next
+    const int32_t * off, * pair, * active, * n_active; // CSR lists of the routed pairs
+    int32_t max_active, n_pairs, top_k, fuse, n_rows, n_vec, tiles_per_expert, type;
+    float * out; // out[pair * out_stride + row]
+    int32_t out_stride;
+};
+struct TileG { // one grouped tile's tokens: CSR positions q0 .. q0 + ntok - 1 of expert e
+    int e, q0, ntok;
+};
+
 struct MmaArgs {
     CallDev c;
+    GroupDev g;
     int32_t tiles_m[B200Q_MAX_SEGS]; // exclusive prefix of 128-row tiles per segment
     int32_t n_tiles_m, n_tiles_t;
     int32_t raw_bytes; // per-thread staging bytes for one raw superblock (16-byte units)
@@ -284,17 +302,39 @@ __device__ __forceinline__ void unpack_slot(const uint8_t * sb, int h, int r, bo
 //     double buffered: the next superblock it needs is in flight while this one is unpacked),
 //   * copies the tokens' int8 groups straight into the slot's B buffers with cp.async,
 //   * unpacks the eight steps' codes into A and publishes the per-row and per-token factors.
-template <int TYPE, int NT, int PG>
-__device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                             uint32_t raw_all, int pt, const Bars & bars, uint32_t & gslot) {
+template <int TYPE, int NT, int PG, bool G>
+__device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, const TileG & tg,
+                                             uint32_t ring, uint32_t raw_all, int pt, const Bars & bars, uint32_t & gslot) {
     using F = StepFmt<TYPE>;
     constexpr int SB = Fmt<TYPE>::SB, SPS = F::NS / kSlotSteps; // slots per superblock
     constexpr int NB = F::NS == 16 ? 4 : 8;                     // activation groups per slot
     const int grp = pt >> 7, r = pt & 127;
-    const int nb = a.c.K >> 8, RB = a.raw_bytes, TB = a.c.TB;
+    const int nb = a.c.K >> 8, RB = a.raw_bytes;
     const uint32_t D = (uint32_t)bars.depth;
-    const bool row_ok = row0 + r < sg.n_rows;
-    const uint8_t * wrow = sg.w + (size_t)(row0 + r) * nb * SB;
+    bool row_ok;
+    const uint8_t * wrow;
+    // The token column this thread serves is the same in every round of the loops below (NT and 2*NT
+    // divide 128): column r % NT of the factor arrays, column (r % 2NT) / 2 of the int8 copies.  vf / vc:
+    // the activation vectors behind those columns (-1: beyond the tile's tokens); TB: vectors per group.
+    int vf, vc, TB;
+    if constexpr (G) {
+        const int rr = a.g.fuse ? row0 + (r >> 1) : row0 + r;
+        row_ok = rr < a.g.n_rows;
+        const uint8_t * plane = (a.g.fuse && (r & 1)) ? a.g.bank_b + (size_t)tg.e * a.g.plane_b : a.g.bank_a + (size_t)tg.e * a.g.plane_a;
+        wrow = plane + (size_t)rr * nb * SB;
+        const int tf = r & (NT - 1), tc = (r & (2 * NT - 1)) >> 1;
+        const int pf = tf < tg.ntok ? __ldg(a.g.pair + tg.q0 + tf) : -1, pc = tc < tg.ntok ? __ldg(a.g.pair + tg.q0 + tc) : -1;
+        vf = (pf >= 0 && a.g.top_k > 0) ? pf / a.g.top_k : pf;
+        vc = (pc >= 0 && a.g.top_k > 0) ? pc / a.g.top_k : pc;
+        TB = a.g.n_vec;
+    } else {
+        row_ok = row0 + r < sg.n_rows;
+        wrow = sg.w + (size_t)(row0 + r) * nb * SB;
+        TB = a.c.TB;
+        const int tf = t0 + (r & (NT - 1)), tc = t0 + ((r & (2 * NT - 1)) >> 1);
+        vf = tf < TB ? tf : -1;
+        vc = tc < TB ? tc : -1;
+    }
     // staging is buffer-major: thread pt's buffer `buf` sits at (buf * threads + pt) * RB, so the
     // threads of a warp are RB bytes apart (an odd number of 16-byte chunks: no bank conflicts)
     const int BS = 128 * PG * RB;
@@ -341,11 +381,11 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         int2 f_xs[NI];
 #pragma unroll
         for (int k = 0; k < NI; k++) {
-            const int c = r + 128 * k, st = c / NT, t = c - st * NT;
+            const int c = r + 128 * k, st = c / NT;
             f_sx[k] = 0.f;
             f_xs[k] = make_int2(0, 0);
-            if (kHoist && c < kSlotSteps * NT && t0 + t < TB) {
-                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
+            if (kHoist && c < kSlotSteps * NT && vf >= 0) {
+                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + vf;
                 f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
                 f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
             }
@@ -357,10 +397,10 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         // tokens: the int8 groups this slot's steps meet, straight into the B buffers
         for (int c = r; c < NB * NT * 2; c += 128) {
             const int gi = c / (2 * NT), rem = c - gi * 2 * NT, t = rem >> 1, hh = rem & 1;
-            const int G = 8 * b + (F::NS == 16 ? 4 * h + gi : gi);
+            const int grp8 = 8 * b + (F::NS == 16 ? 4 * h + gi : gi);
             const uint32_t dst = base + Slot<NT>::B + (uint32_t)(gi * NT * 32) + core_off(t, hh);
-            if (t0 + t < TB) {
-                cp_async16(dst, a.c.x8 + ((size_t)G * TB + t0 + t) * 32 + 16 * hh);
+            if (vc >= 0) {
+                cp_async16(dst, a.c.x8 + ((size_t)grp8 * TB + vc) * 32 + 16 * hh);
             } else {
                 sts128(dst, 0, 0, 0, 0);
             }
@@ -375,9 +415,9 @@ __device__ __forceinline__ bool produce_tile(const MmaArgs & a, const SegDev & s
         }
 #pragma unroll
         for (int k = 0; k < NI; k++) {
-            const int c = r + 128 * k, st = c / NT, t = c - st * NT;
-            if (!kHoist && c < kSlotSteps * NT && t0 + t < TB) {
-                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + t0 + t;
+            const int c = r + 128 * k, st = c / NT;
+            if (!kHoist && c < kSlotSteps * NT && vf >= 0) {
+                const size_t gi = (size_t)(8 * b + step_group<TYPE>(h, st)) * TB + vf;
                 f_sx[k] = __ldg(a.c.xmeta + 2 * gi);
                 f_xs[k] = __ldg(reinterpret_cast<const int2 *>(a.c.xsumq) + gi);
             }
@@ -463,9 +503,10 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 }
 
 // Epilogue: this thread owns weight row `row0 + 32*(warp%4) + lane` and NT/EW token columns.
-template <int TYPE, int NT, int EW>
-__device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                              uint32_t tmem, const Bars & bars, uint32_t & gslot, uint32_t & git) {
+template <int TYPE, int NT, int EW, bool G>
+__device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, const TileG & tg,
+                                              uint32_t ring, uint32_t tmem, const Bars & bars, uint32_t & gslot,
+                                              uint32_t & git) {
     using F = StepFmt<TYPE>;
     constexpr int NC = NT / EW; // token columns per thread
     constexpr uint32_t AR = acc_ring(NT);
@@ -576,6 +617,30 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
             mbar_arrive(bars.done + 8 * slot); // the operand slot and its factors may be refilled
         }
     }
+    if constexpr (G) {
+        // out[pair, row]: the tile's token column t is CSR position q0 + t.  Fused form: even lanes hold
+        // gate rows, odd lanes the up rows of the same index; the even lane stores silu(gate) * up.
+        if (__all_sync(0xFFFFFFFFu, ok)) {
+            const int rr = a.g.fuse ? row0 + (rl >> 1) : row0 + rl;
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                const int t = c0 + i;
+                const uint64_t pr2 = acc[i / 2];
+                const float v = __uint_as_float((uint32_t)((i & 1) ? pr2 >> 32 : pr2));
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                if (t < tg.ntok && rr < a.g.n_rows && !(a.g.fuse && (lane & 1))) {
+                    const int pi = __ldg(a.g.pair + tg.q0 + t);
+                    float h = v;
+                    if (a.g.fuse) { // x / (1 + expf(-x)) with the exponential rounded once, then one multiplication
+                        const float ex = (float)exp((double)(-v));
+                        h = __fmul_rn(__fdiv_rn(v, __fadd_rn(1.0f, ex)), other);
+                    }
+                    a.g.out[(size_t)pi * a.g.out_stride + rr] = h;
+                }
+            }
+        }
+        return ok;
+    }
     if (ok && !a.dump) {
         const int row = row0 + rl;
         if (row < sg.n_rows) {
@@ -597,17 +662,17 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
     return ok;
 }
 
-template <int TYPE, int NT, int EW, int PG>
-__device__ __forceinline__ bool run_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, uint32_t ring,
-                                         uint32_t tmem, const Bars & bars, uint32_t & gslot, uint32_t & git) {
+template <int TYPE, int NT, int EW, int PG, bool G>
+__device__ __forceinline__ bool run_tile(const MmaArgs & a, const SegDev & sg, int row0, int t0, const TileG & tg,
+                                         uint32_t ring, uint32_t tmem, const Bars & bars, uint32_t & gslot, uint32_t & git) {
     using R = Roles<NT, EW, PG>;
     const int warp = threadIdx.x >> 5;
     if (warp < R::kEpiWarps) {
-        return epilogue_tile<TYPE, NT, EW>(a, sg, row0, t0, ring, tmem, bars, gslot, git);
+        return epilogue_tile<TYPE, NT, EW, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
     }
     if (warp < R::kEpiWarps + R::kProdWarps) {
-        return produce_tile<TYPE, NT, PG>(a, sg, row0, t0, ring, ring + (uint32_t)bars.depth * Slot<NT>::BYTES,
-                                          (int)threadIdx.x - 32 * R::kEpiWarps, bars, gslot);
+        return produce_tile<TYPE, NT, PG, G>(a, sg, row0, t0, tg, ring, ring + (uint32_t)bars.depth * Slot<NT>::BYTES,
+                                             (int)threadIdx.x - 32 * R::kEpiWarps, bars, gslot);
     }
     if (threadIdx.x == 32 * (R::kEpiWarps + R::kProdWarps)) {
         return mma_tile<TYPE, NT, EW>(a, ring, tmem, bars, gslot, git);
@@ -615,7 +680,20 @@ __device__ __forceinline__ bool run_tile(const MmaArgs & a, const SegDev & sg, i
     return true; // idle lanes of the MMA warp
 }
 
-template <int NT, int EW, int PG>
+template <int NT, int EW, int PG, bool G>
+__device__ __forceinline__ bool run_tile_any(int type, const MmaArgs & a, const SegDev & sg, int row0, int t0,
+                                             const TileG & tg, uint32_t ring, uint32_t tmem, const Bars & bars,
+                                             uint32_t & gslot, uint32_t & git) {
+    switch (type) {
+    case kQ4_K: return run_tile<kQ4_K, NT, EW, PG, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
+    case kQ5_K: return run_tile<kQ5_K, NT, EW, PG, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
+    case kQ6_K: return run_tile<kQ6_K, NT, EW, PG, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
+    case kIQ4_XS: return run_tile<kIQ4_XS, NT, EW, PG, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
+    default: return run_tile<kQ8_0, NT, EW, PG, G>(a, sg, row0, t0, tg, ring, tmem, bars, gslot, git);
+    }
+}
+
+template <int NT, int EW, int PG, bool G>
 __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kernel(const __grid_constant__ MmaArgs a) {
     using R = Roles<NT, EW, PG>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -648,21 +726,32 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
 
     uint32_t gslot = 0, git = 0;
     bool ok = true;
-    const int n_tiles = a.n_tiles_m * a.n_tiles_t;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int tm = tile / a.n_tiles_t, tt = tile - tm * a.n_tiles_t; // token tiles innermost: weights stay in L2
-        int si = 0;
-        while (si + 1 < a.c.n_segs && tm >= a.tiles_m[si]) {
-            si++;
+    if constexpr (G) {
+        // every role walks the same list: (active expert, row tile) dealt to the CTAs in turn, row tiles of
+        // an expert on neighbouring CTAs (its tokens stay in L2); the expert's tokens NT at a time
+        const int tpe = a.g.tiles_per_expert, rows_per_tile = a.g.fuse ? kTileM / 2 : kTileM;
+        const int n_act = min(__ldg(a.g.n_active), a.g.max_active);
+        for (int tile = blockIdx.x; tile < n_act * tpe && ok; tile += gridDim.x) {
+            const int s = tile / tpe, tm = tile - s * tpe;
+            const int e = __ldg(a.g.active + s);
+            const int q0 = max(__ldg(a.g.off + e), 0), q1 = min(__ldg(a.g.off + e + 1), a.g.n_pairs);
+            for (int q = q0; q < q1 && ok; q += NT) {
+                const TileG tg{e, q, min(NT, q1 - q)};
+                ok = run_tile_any<NT, EW, PG, true>(a.g.type, a, a.c.seg[0], tm * rows_per_tile, 0, tg, ring, tmem, bars, gslot, git);
+            }
         }
-        const SegDev & sg = a.c.seg[si];
-        const int row0 = (tm - (si ? a.tiles_m[si - 1] : 0)) * kTileM, t0 = tt * NT;
-        switch (sg.type) {
-        case kQ4_K: ok = run_tile<kQ4_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
-        case kQ5_K: ok = run_tile<kQ5_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
-        case kQ6_K: ok = run_tile<kQ6_K, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
-        case kIQ4_XS: ok = run_tile<kIQ4_XS, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
-        default: ok = run_tile<kQ8_0, NT, EW, PG>(a, sg, row0, t0, ring, tmem, bars, gslot, git); break;
+    } else {
+        const int n_tiles = a.n_tiles_m * a.n_tiles_t;
+        const TileG none{0, 0, 0};
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int tm = tile / a.n_tiles_t, tt = tile - tm * a.n_tiles_t; // token tiles innermost: weights stay in L2
+            int si = 0;
+            while (si + 1 < a.c.n_segs && tm >= a.tiles_m[si]) {
+                si++;
+            }
+            const SegDev & sg = a.c.seg[si];
+            const int row0 = (tm - (si ? a.tiles_m[si - 1] : 0)) * kTileM, t0 = tt * NT;
+            ok = run_tile_any<NT, EW, PG, false>(sg.type, a, sg, row0, t0, none, ring, tmem, bars, gslot, git);
         }
     }
     // every role falls through to here, also after a wait that ran out: release tensor memory
@@ -674,7 +763,7 @@ __global__ void __launch_bounds__(Roles<NT, EW, PG>::kThreads, 1) gemm_mma_kerne
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, MmaArgs & a, bool pdl_secondary) {
+template <int NT, int EW, int PG, bool G = false> static cudaError_t launch_nt(cudaStream_t s, MmaArgs & a, bool pdl_secondary) {
     using R = Roles<NT, EW, PG>;
     const size_t raw = (size_t)32 * R::kProdWarps * 2 * a.raw_bytes, budget = 227 * 1024;
     if (kHdr + 2 * (size_t)Slot<NT>::BYTES + raw > budget) {
@@ -685,13 +774,13 @@ template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, M
     a.depth = depth;
     const size_t smem = kHdr + (size_t)depth * Slot<NT>::BYTES + raw;
     {
-        cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_mma_kernel<NT, EW, PG>), (int)smem);
+        cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_mma_kernel<NT, EW, PG, G>), (int)smem);
         if (e != cudaSuccess) {
             return e;
         }
     }
     a.n_tiles_t = (a.c.TB + NT - 1) / NT;
-    const int tiles = a.n_tiles_m * a.n_tiles_t;
+    const long long tiles = G ? (long long)a.g.max_active * a.g.tiles_per_expert : (long long)a.n_tiles_m * a.n_tiles_t;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles < kSMs ? tiles : kSMs));
     cfg.blockDim = dim3(R::kThreads);
@@ -702,11 +791,12 @@ template <int NT, int EW, int PG> static cudaError_t launch_nt(cudaStream_t s, M
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_secondary ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemm_mma_kernel<NT, EW, PG>, a);
+    return cudaLaunchKernelEx(&cfg, gemm_mma_kernel<NT, EW, PG, G>, a);
 }
 
 cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondary, int32_t * dump, int dump_t) {
     MmaArgs a;
+    memset(&a.g, 0, sizeof(a.g));
     a.c = c;
     a.dump = dump;
     a.dump_t = dump_t;
@@ -741,6 +831,72 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     }
     // prefill: the fp32 epilogue dominates; two epilogue warpgroups share the token columns
     return pg2 ? launch_nt<64, 2, 2>(s, a, pdl_secondary) : launch_nt<64, 2, 1>(s, a, pdl_secondary);
+}
+
+// ---- grouped form: the expert GEMMs of a routed-MoE call --------------------------------------------
+static int mma_raw_bytes(int type) {
+    // a superblock plus its misalignment, in whole 16-byte chunks (none when the size is a multiple
+    // of 16: planes and rows then keep the 16-byte alignment of the bank)
+    const int sbb = sb_bytes((uint32_t)type);
+    int n = sbb % 16 == 0 ? sbb : ((sbb + 30) / 16) * 16;
+    if (type == kQ8_0) {
+        n += 16; // the funnel-shifted 2-byte-aligned reads touch one word past the last block
+    }
+    return (n / 16) % 2 ? n : n + 16; // odd number of 16-byte chunks per thread: distinct banks
+}
+
+bool moe_mma_supported(int type_a, int type_b, int K, int n_rows, int fuse) {
+    return K >= 256 && (K & 255) == 0 && n_rows >= 1 && (!fuse || type_a == type_b);
+}
+
+cudaError_t launch_moe_mma(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
+                           size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
+                           const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                           const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
+                           float * out, int out_stride, int fuse) {
+    if (!moe_mma_supported(type_a, type_b, K, n_rows, fuse)) {
+        return cudaErrorInvalidConfiguration;
+    }
+    MmaArgs a;
+    memset(&a, 0, sizeof(a));
+    a.c.K = K;
+    a.c.TB = TB;
+    a.c.x8 = x8;
+    a.c.xmeta = xmeta;
+    a.c.xsumq = xsumq;
+    a.g.bank_a = static_cast<const uint8_t *>(bank_a);
+    a.g.bank_b = static_cast<const uint8_t *>(fuse ? bank_b : bank_a);
+    a.g.plane_a = plane_a;
+    a.g.plane_b = fuse ? plane_b : plane_a;
+    a.g.off = off;
+    a.g.pair = pair;
+    a.g.active = active;
+    a.g.n_active = n_active;
+    a.g.max_active = n_act_max;
+    const long long n_pairs = top_k > 0 ? (long long)TB * top_k : TB;
+    a.g.n_pairs = (int32_t)n_pairs;
+    a.g.top_k = top_k;
+    a.g.fuse = fuse;
+    a.g.n_rows = n_rows;
+    a.g.n_vec = TB;
+    const int rows_per_tile = fuse ? kTileM / 2 : kTileM;
+    a.g.tiles_per_expert = (n_rows + rows_per_tile - 1) / rows_per_tile;
+    a.g.type = type_a;
+    a.g.out = out;
+    a.g.out_stride = out_stride;
+    a.raw_bytes = mma_raw_bytes(type_a);
+    a.lbo = 128;
+    a.sbo = 256;
+    const bool pg2 = a.raw_bytes <= 240;
+    // token tile from the mean number of tokens per expert: an expert with more takes several tiles
+    const long long mean = (n_pairs + n_act_max - 1) / n_act_max;
+    if (mean <= 10) {
+        return pg2 ? launch_nt<16, 1, 2, true>(s, a, true) : launch_nt<16, 1, 1, true>(s, a, true);
+    }
+    if (mean <= 40) {
+        return pg2 ? launch_nt<32, 2, 2, true>(s, a, true) : launch_nt<32, 2, 1, true>(s, a, true);
+    }
+    return (pg2 && a.raw_bytes <= 192) ? launch_nt<64, 2, 2, true>(s, a, true) : launch_nt<64, 2, 1, true>(s, a, true);
 }
 
 cudaError_t read_mma_status(int * status, bool clear) {

@@ -69,6 +69,13 @@ cudaError_t launch_moe_pinned(cudaStream_t s, const void * bank_a, const void * 
                               const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                               const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
                               float * out, int out_stride, int fuse_silu, const NextAct * hq);
+// grouped expert GEMMs on the tensor cores (gemm_mma.cu): more than a few routed tokens per expert
+bool moe_mma_supported(int type_a, int type_b, int K, int n_rows, int fuse_silu);
+cudaError_t launch_moe_mma(cudaStream_t s, const void * bank_a, const void * bank_b, int type_a, int type_b,
+                           size_t plane_a, size_t plane_b, const int32_t * off, const int32_t * pair,
+                           const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
+                           const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
+                           float * out, int out_stride, int fuse_silu);
 // which kernel launch_moe_rows picks for a shape: true = the pinned one (which can emit hq itself)
 bool moe_rows_takes_pinned(int type_a, int type_b, int K, int n_rows, int fuse_silu, int TB, int top_k, int n_act_max,
                            bool want_hq = false);

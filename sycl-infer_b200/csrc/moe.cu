@@ -532,6 +532,18 @@ cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int
                           in_smem);
 }
 
+static bool moe_force_rows() { // A/B builds only: B200Q_MOE_KERNEL=rows keeps the warp-per-row kernel
+#ifdef B200Q_TUNING
+    static const bool on = [] {
+        const char * e = getenv("B200Q_MOE_KERNEL");
+        return e && strcmp(e, "rows") == 0;
+    }();
+    return on;
+#else
+    return false;
+#endif
+}
+
 bool moe_rows_takes_pinned(int type_a, int type_b, int K, int n_rows, int fuse_silu, int TB, int top_k, int n_act_max,
                            bool want_hq) {
 #ifdef B200Q_TUNING
@@ -561,6 +573,11 @@ cudaError_t launch_moe_rows(cudaStream_t s, const void * bank_a, const void * ba
     }
     if (hq) { // only the pinned kernel quantizes h itself; callers ask moe_rows_takes_pinned first
         return cudaErrorInvalidConfiguration;
+    }
+    // more than four routed tokens per expert on average (prefill): the expert GEMMs as tensor-core tiles
+    if (n_pairs > 4LL * n_act_max && !moe_force_rows() && moe_mma_supported(type_a, type_b, K, n_rows, fuse_silu)) {
+        return launch_moe_mma(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max, x8,
+                              xmeta, xsumq, TB, top_k, K, n_rows, out, out_stride, fuse_silu);
     }
     if (n_pairs <= 4LL * n_act_max && n_act_max <= 1023 && moe_stream_supported(type_a, type_b, K, n_rows, fuse_silu)) {
         return launch_moe_stream(s, bank_a, bank_b, type_a, type_b, plane_a, plane_b, off, pair, active, n_active, n_act_max,

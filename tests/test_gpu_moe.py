@@ -106,8 +106,29 @@ def test_moe_small(be, orc, pkg, types):
 
 
 def test_moe_many_tokens_per_expert(be, orc, pkg):
-    """More than four routed tokens per expert on average: the warp-per-row expert kernel."""
+    """More than four routed tokens per expert on average: the grouped tensor-core expert kernel
+    (10 tokens per expert: 16-token tiles, the busier experts take two)."""
     _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=40, types=(12, 12, 12), seed=7)
+
+
+@pytest.mark.parametrize("n_tok,types", [(40, (13, 13, 14)), (100, (12, 12, 12)), (100, (14, 14, 8)), (100, (23, 23, 13)),
+                                         (300, (12, 12, 14)), (300, (8, 8, 23))])
+def test_moe_grouped_tensor_core_tiles(be, orc, pkg, n_tok, types):
+    """Prefill-sized calls on the grouped tcgen05 kernel: 16-, 32- and 64-token tiles (10, 25 and 75
+    routed tokens per expert on average), every block format on either side."""
+    _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=n_tok, types=types, seed=31 + n_tok)
+
+
+def test_moe_many_tokens_mixed_gate_up_types(be, orc, pkg):
+    """gate and up planes of different types with many tokens per expert: the grouped kernel pairs
+    gate and up rows of one format only, this shape stays on the warp-per-row kernel."""
+    _run_moe(be, orc, pkg, E=8, top_k=2, n_embd=512, n_ff=256, n_tok=40, types=(12, 14, 12), seed=8)
+
+
+def test_moe_config3_prefill_512_tokens(be, orc, pkg):
+    """Configuration 3 with 512 tokens (16 routed tokens per expert on average)."""
+    n = _run_moe(be, orc, pkg, E=256, top_k=8, n_embd=2048, n_ff=512, n_tok=512, types=(12, 12, 12), seed=0xC3)
+    assert n >= 250
 
 
 @pytest.mark.parametrize("types", [(12, 14, 12), (14, 14, 14)])
