@@ -628,12 +628,13 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
                 const uint64_t pr2 = acc[i / 2];
                 const float v = __uint_as_float((uint32_t)((i & 1) ? pr2 >> 32 : pr2));
                 const float other = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-                if (t < tg.ntok && rr < a.g.n_rows && !(a.g.fuse && (lane & 1))) {
+                // both lanes of a pair now hold gate and up: the even lane finishes the even columns, the odd one the odd
+                if (t < tg.ntok && rr < a.g.n_rows && (!a.g.fuse || (i & 1) == (lane & 1))) {
                     const int pi = __ldg(a.g.pair + tg.q0 + t);
                     float h = v;
-                    if (a.g.fuse) { // x / (1 + expf(-x)) with the exponential rounded once, then one multiplication
-                        const float ex = (float)exp((double)(-v));
-                        h = __fmul_rn(__fdiv_rn(v, __fadd_rn(1.0f, ex)), other);
+                    if (a.g.fuse) { // x / (1 + expf(-x)) * up, as the single-token expert kernel forms it
+                        const float gv = (lane & 1) ? other : v, uv = (lane & 1) ? v : other;
+                        h = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
                     }
                     a.g.out[(size_t)pi * a.g.out_stride + rr] = h;
                 }
@@ -887,9 +888,19 @@ cudaError_t launch_moe_mma(cudaStream_t s, const void * bank_a, const void * ban
     a.raw_bytes = mma_raw_bytes(type_a);
     a.lbo = 128;
     a.sbo = 256;
-    const bool pg2 = a.raw_bytes <= 240;
+    // one producer group: the second one's 96-register limit makes this form spill (A/B at 512 tokens of
+    // 256 experts top-8: 828 against 952 microseconds per call)
+    bool pg2 = false;
     // token tile from the mean number of tokens per expert: an expert with more takes several tiles
-    const long long mean = (n_pairs + n_act_max - 1) / n_act_max;
+    long long mean = (n_pairs + n_act_max - 1) / n_act_max;
+#ifdef B200Q_TUNING
+    if (const char * e = getenv("B200Q_MOE_NT")) { // A/B builds only: force the token tile and the producer groups
+        mean = atoi(e) <= 16 ? 1 : (atoi(e) <= 32 ? 20 : 100);
+    }
+    if (const char * e = getenv("B200Q_MOE_PG")) {
+        pg2 = a.raw_bytes <= 240 && atoi(e) == 2;
+    }
+#endif
     if (mean <= 10) {
         return pg2 ? launch_nt<16, 1, 2, true>(s, a, true) : launch_nt<16, 1, 1, true>(s, a, true);
     }

@@ -108,10 +108,92 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
     }
 }
 
+// The same logits for many tokens (prefill): a 32-token x 32-expert tile per CTA, K in chunks of 32
+// through shared memory, so that an activation row is read once per 32 experts instead of once per
+// CTA of two.  Every output is one thread's fp64 sum of the exact products (even and odd k apart).
+// float -> double conversions run at a quarter of the fp64 FMA rate on this GPU: a value is converted
+// once, by the thread that stages it, and the tiles lie in shared memory as doubles, k-major, so that a
+// thread's two tokens (two experts) come with one 16-byte load.
+constexpr int kLogitTile = 32;
+// Column of token (expert) r in row k of a tile: pairs (2i, 2i + 1) stay together, and the 32 values a
+// warp stores for one r (k = 0..31) spread over all banks.
+__device__ __forceinline__ int logit_col(int k, int r) {
+    return r ^ (2 * (k & 15));
+}
+__global__ void __launch_bounds__(256) moe_logits_tiled_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
+                                                               int x_stride, int n_tok, int n_embd, int n_expert,
+                                                               float * __restrict__ logits) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // two chunks of [k][token] and [k][expert] doubles: one is summed while the next is stored
+    __shared__ __align__(16) double xs[2][kLogitTile][kLogitTile], ws[2][kLogitTile][kLogitTile];
+    const int e0 = blockIdx.x * kLogitTile, t0 = blockIdx.y * kLogitTile;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4; // experts 2tx, 2tx + 1; tokens 2ty, 2ty + 1
+    // two sums per output (even and odd k), added at the end: twice as many independent fp64 chains in
+    // flight, which this tile size needs to keep the fp64 pipe busy
+    double a00[2] = {0.0, 0.0}, a01[2] = {0.0, 0.0}, a10[2] = {0.0, 0.0}, a11[2] = {0.0, 0.0};
+    float px[4], pw[4]; // a chunk's values of this thread, in flight while an earlier chunk is summed
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int idx = (int)threadIdx.x + 256 * j, r = idx >> 5, k = idx & 31;
+            const bool kin = k0 + k < n_embd;
+            px[j] = (kin && t0 + r < n_tok) ? __ldg(x + (size_t)(t0 + r) * x_stride + k0 + k) : 0.0f;
+            pw[j] = (kin && e0 + r < n_expert) ? __ldg(gate_inp + (size_t)(e0 + r) * n_embd + k0 + k) : 0.0f;
+        }
+    };
+    auto store = [&](int b) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int idx = (int)threadIdx.x + 256 * j, r = idx >> 5, k = idx & 31;
+            xs[b][k][logit_col(k, r)] = (double)px[j];
+            ws[b][k][logit_col(k, r)] = (double)pw[j];
+        }
+    };
+    fetch(0);
+    store(0);
+    if (kLogitTile < n_embd) {
+        fetch(kLogitTile);
+    }
+    int b = 0;
+    for (int k0 = 0; k0 < n_embd; k0 += kLogitTile, b ^= 1) {
+        __syncthreads(); // chunk k0 is stored; the other buffer's readers (chunk k0 - 32) are done
+        if (k0 + kLogitTile < n_embd) {
+            store(b ^ 1);
+            if (k0 + 2 * kLogitTile < n_embd) {
+                fetch(k0 + 2 * kLogitTile);
+            }
+        }
+#pragma unroll 8
+        for (int k = 0; k < kLogitTile; k++) {
+            const double2 xv = *reinterpret_cast<const double2 *>(&xs[b][k][logit_col(k, 2 * ty)]);
+            const double2 wv = *reinterpret_cast<const double2 *>(&ws[b][k][logit_col(k, 2 * tx)]);
+            a00[k & 1] += xv.x * wv.x;
+            a01[k & 1] += xv.x * wv.y;
+            a10[k & 1] += xv.y * wv.x;
+            a11[k & 1] += xv.y * wv.y;
+        }
+    }
+    const int ta = t0 + 2 * ty, ea = e0 + 2 * tx;
+    if (ta < n_tok && ea < n_expert) {
+        logits[(size_t)ta * n_expert + ea] = (float)(a00[0] + a00[1]);
+    }
+    if (ta < n_tok && ea + 1 < n_expert) {
+        logits[(size_t)ta * n_expert + ea + 1] = (float)(a01[0] + a01[1]);
+    }
+    if (ta + 1 < n_tok && ea < n_expert) {
+        logits[(size_t)(ta + 1) * n_expert + ea] = (float)(a10[0] + a10[1]);
+    }
+    if (ta + 1 < n_tok && ea + 1 < n_expert) {
+        logits[(size_t)(ta + 1) * n_expert + ea + 1] = (float)(a11[0] + a11[1]);
+    }
+}
+
 // ---- token -> expert CSR (one CTA) -----------------------------------------------------------
 // off[e]..off[e+1] index `pair`, which lists the (token, slot) pair ids routed to expert e in
 // increasing pair order; active[0..n_active) lists the experts with at least one pair.
-// cnt: shared memory, 2 * (n_expert + 1) words (+ n_pairs when ids_in_smem): n_expert + 1 counts ->
+// cnt: shared memory, 2 * (n_expert + 1) words (+ n_pairs when ids_in_smem, + a cursor per warp and
+// expert for lists of more than 1024 pairs): n_expert + 1 counts ->
 // their prefix; then the active flags' prefix; then the ids.
 __device__ __forceinline__ void csr_build(const int32_t * ids, int n_pairs, int n_expert, int32_t * off, int32_t * pair,
                                           int32_t * active, int32_t * n_active, int ids_in_smem, int32_t * cnt) {
@@ -186,13 +268,47 @@ __device__ __forceinline__ void csr_build(const int32_t * ids, int n_pairs, int 
         }
         return;
     }
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
-        int o = cnt[e];
-        const int end = cnt[e + 1];
-        for (int i = 0; i < n_pairs && o < end; i++) { // deterministic fill in pair order
-            if (idv[i] == e) {
-                pair[o++] = i;
+    // long lists: every warp takes a contiguous range of the pairs.  Pass 1 counts the range's pairs
+    // per expert, a prefix over the warps turns the counts into each warp's first free place in every
+    // expert's list, pass 2 fills; lanes with the same expert in one step of 32 pairs are ranked by lane.
+    // Lower ranges come first and a warp walks its range upwards: the lists stay in pair order.
+    const int nw = (int)blockDim.x >> 5, warp = (int)threadIdx.x >> 5, lane = (int)threadIdx.x & 31;
+    int32_t * wc = sid + (ids_in_smem ? n_pairs : 0); // [nw][n_expert]
+    const int span = ((n_pairs + nw - 1) / nw + 31) & ~31;
+    const int lo = min(warp * span, n_pairs), hi = min(lo + span, n_pairs);
+    for (int e = threadIdx.x; e < nw * n_expert; e += blockDim.x) {
+        wc[e] = 0;
+    }
+    __syncthreads();
+    for (int pass = 0; pass < 2; pass++) {
+        int32_t * mine = wc + warp * n_expert;
+        for (int i0 = lo; i0 < hi; i0 += 32) {
+            const int i = i0 + lane;
+            int e = i < hi ? (ids_in_smem ? sid[i] : __ldcg(ids + i)) : -1; // other CTAs of this launch wrote the ids
+            e = (e >= 0 && e < n_expert) ? e : -1;
+            const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+            const int rank = __popc(same & ((1u << lane) - 1u));
+            const int base = e >= 0 ? mine[e] : 0;
+            __syncwarp();
+            if (e >= 0 && rank == 0) {
+                mine[e] = base + __popc(same);
             }
+            __syncwarp();
+            if (pass == 1 && e >= 0) {
+                pair[base + rank] = i;
+            }
+        }
+        __syncthreads();
+        if (pass == 0) {
+            for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+                int run = cnt[e];
+                for (int w = 0; w < nw; w++) {
+                    const int c = wc[w * n_expert + e];
+                    wc[w * n_expert + e] = run;
+                    run += c;
+                }
+            }
+            __syncthreads();
         }
     }
 }
@@ -493,7 +609,8 @@ static cudaError_t launch_chained(cudaStream_t s, void (*k)(KArgs...), dim3 grid
 
 static size_t csr_smem(int n_pairs, int n_expert, int & in_smem) {
     in_smem = n_pairs <= 8192 ? 1 : 0;
-    return (size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) * sizeof(int32_t);
+    const size_t per_warp = n_pairs > 1024 ? (size_t)8 * n_expert : 0; // the long-list fill's cursors (256 threads)
+    return ((size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) + per_warp) * sizeof(int32_t);
 }
 
 // off != nullptr: the CSR is built by the router's last CTA
@@ -501,8 +618,12 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
                              int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts,
                              int32_t * off, int32_t * pair, int32_t * active, int32_t * n_active) {
     if (gate_inp) {
-        cudaError_t e = launch_chained(s, moe_logits_kernel, dim3((unsigned)((n_expert + kRouteExp - 1) / kRouteExp)), dim3(256), 0, gate_inp, x, x_stride, n_tok,
-                                       n_embd, n_expert, logits);
+        cudaError_t e = n_tok >= kLogitTile
+                            ? launch_chained(s, moe_logits_tiled_kernel,
+                                             dim3((unsigned)((n_expert + kLogitTile - 1) / kLogitTile), (unsigned)((n_tok + kLogitTile - 1) / kLogitTile)),
+                                             dim3(256), 0, gate_inp, x, x_stride, n_tok, n_embd, n_expert, logits)
+                            : launch_chained(s, moe_logits_kernel, dim3((unsigned)((n_expert + kRouteExp - 1) / kRouteExp)),
+                                             dim3(256), 0, gate_inp, x, x_stride, n_tok, n_embd, n_expert, logits);
         if (e != cudaSuccess) {
             return e;
         }

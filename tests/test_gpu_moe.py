@@ -182,7 +182,29 @@ def test_moe_config3_full_size(be, orc, pkg):
     assert 60 <= n <= 128
 
 
-@pytest.mark.parametrize("n_tok,E,top_k", [(16, 256, 8), (3, 32, 4)])
+@pytest.mark.parametrize("n_tok,E,n_embd", [(100, 40, 520), (32, 256, 2048), (257, 33, 96)])
+def test_router_logits_many_tokens(be, orc, pkg, n_tok, E, n_embd):
+    """32 tokens and more take the tiled logits kernel (ragged token, expert and K tiles included):
+    logits within 1e-6 of the oracle's fp64 sums, same ids."""
+    from sycl_infer_b200.moe import moe_router_launch
+    rng = np.random.default_rng(n_tok + E)
+    x = pkg.synth.make_activation(n_tok, n_embd, 900 + n_tok)
+    gate = (rng.standard_normal((E, n_embd)) / np.sqrt(n_embd)).astype(np.float32)
+    top_k = 4
+    lg_o, ids_o, wts_o = orc.moe_route(x, gate, top_k)
+    logits = torch.zeros(n_tok, E, device="cuda")
+    ids = torch.zeros(n_tok, top_k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n_tok, top_k, device="cuda")
+    moe_router_launch(be, torch.from_numpy(gate).cuda(), 0, torch.from_numpy(x).cuda(), n_embd, n_tok, n_embd, E, top_k,
+                      logits, ids, wts)
+    be.synchronize()
+    assert be.device_status() == 0
+    assert np.max(np.abs(logits.cpu().numpy() - lg_o)) <= 1e-6 * max(1.0, np.max(np.abs(lg_o)))
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    assert np.max(np.abs(wts.cpu().numpy() - wts_o)) <= 1e-6
+
+
+@pytest.mark.parametrize("n_tok,E,top_k", [(16, 256, 8), (3, 32, 4), (600, 64, 4), (2100, 8, 4)])
 def test_csr_separate_and_fused_agree(be, pkg, n_tok, E, top_k):
     """Router + CSR as two entry points and as the fused one (the router's last CTA builds the
     lists): identical ids, offsets, pair lists and active experts; the lists are checked against a
