@@ -398,8 +398,14 @@ def cell_moe(ctx, name, tokens=16, experts=256, topk=8, embd=2048, ff=512, copie
     per_expert = sum(int(pkg.synth.row_bytes(12, K)) * r for r, K in ((ff, embd), (ff, embd), (embd, ff)))
     nbytes = n_active * per_expert
     gbs = nbytes / us / 1e3
-    return {"cell": name, "us": us, "bytes": nbytes, "active_experts": n_active, "GB/s": gbs,
+    cell = {"cell": name, "us": us, "bytes": nbytes, "active_experts": n_active, "GB/s": gbs,
             "frac_of_measured_hbm": ctx.frac(gbs), "l2": f"{copies} rotating expert banks", "clocks": clocks}
+    if tokens * topk > 4 * min(experts, tokens * topk):  # the grouped tensor-core form: arithmetic, not the weight stream
+        tops = 2.0 * tokens * topk * 3 * embd * ff / us / 1e6
+        cell["T_int8_op/s"] = tops
+        if ctx.ceilings.get("i8_mma_tops"):
+            cell["frac_of_i8_mma_peak"] = tops / ctx.ceilings["i8_mma_tops"]
+    return cell
 
 
 # ------------------------------------------------------------------------ cells, several GPUs
@@ -576,6 +582,7 @@ def gpu_arm(args):
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=2048 x 5120 x 17408 Q4_K", 2048)
             safe(cells, cell_prefill, ctx, "config 2: prefill GEMM M=8192 x 5120 x 17408 Q4_K", 8192, iters=2)
             safe(cells, cell_moe, ctx, "config 3: routed MoE, 256 experts top-8, 16 tokens, Q4_K")
+            safe(cells, cell_moe, ctx, "config 3 (prefill): routed MoE, 256 experts top-8, 512 tokens, Q4_K", tokens=512, iters=4)
             safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer IQ4_XS, batch 1", "IQ4_XS", 1)
             safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer Q5_K, batch 1", "Q5_K", 1)
             safe(cells, cell_layer, ctx, "config 4 (1 GPU): dense layer Q4_K_M, batch 32", "Q4_K_M", 32)

@@ -520,6 +520,8 @@ __device__ __forceinline__ bool epilogue_tile(const MmaArgs & a, const SegDev & 
         acc[i] = 0ull;
     }
     const uint64_t kNegMagic = pack2(-12582912.0f, -12582912.0f);
+    // (grouped form: token columns beyond a tile's tokens are folded like the rest - leaving them out
+    // by a branch per group of four columns made the fold slower, 451 against 349 microseconds)
     bool ok = true;
     // Steps are taken in batches: wait for the batch's MMAs, start all their tensor-memory reads,
     // wait once, hand the accumulators back, then fold.  The wait -> read -> fold -> release chain

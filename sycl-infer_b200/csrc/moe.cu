@@ -114,11 +114,19 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
 // float -> double conversions run at a quarter of the fp64 FMA rate on this GPU: a value is converted
 // once, by the thread that stages it, and the tiles lie in shared memory as doubles, k-major, so that a
 // thread's two tokens (two experts) come with one 16-byte load.
-constexpr int kLogitTile = 32;
-// Column of token (expert) r in row k of a tile: pairs (2i, 2i + 1) stay together, and the 32 values a
-// warp stores for one r (k = 0..31) spread over all banks.
-__device__ __forceinline__ int logit_col(int k, int r) {
-    return r ^ (2 * (k & 15));
+constexpr int kLogitTile = 32, kLogitPitch = kLogitTile + 2; // the pad spreads a warp's 32 stores of one column
+// one chunk: 32 steps of k on the doubles in shared memory, every address a constant offset
+__device__ __forceinline__ void logits_chunk(const double (*xs)[kLogitPitch], const double (*ws)[kLogitPitch], int ty, int tx,
+                                             double (&a00)[2], double (&a01)[2], double (&a10)[2], double (&a11)[2]) {
+#pragma unroll
+    for (int k = 0; k < kLogitTile; k++) {
+        const double2 xv = *reinterpret_cast<const double2 *>(&xs[k][2 * ty]);
+        const double2 wv = *reinterpret_cast<const double2 *>(&ws[k][2 * tx]);
+        a00[k & 1] += xv.x * wv.x;
+        a01[k & 1] += xv.x * wv.y;
+        a10[k & 1] += xv.y * wv.x;
+        a11[k & 1] += xv.y * wv.y;
+    }
 }
 __global__ void __launch_bounds__(256) moe_logits_tiled_kernel(const float * __restrict__ gate_inp, const float * __restrict__ x,
                                                                int x_stride, int n_tok, int n_embd, int n_expert,
@@ -126,11 +134,10 @@ __global__ void __launch_bounds__(256) moe_logits_tiled_kernel(const float * __r
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // two chunks of [k][token] and [k][expert] doubles: one is summed while the next is stored
-    __shared__ __align__(16) double xs[2][kLogitTile][kLogitTile], ws[2][kLogitTile][kLogitTile];
+    __shared__ __align__(16) double xs[2][kLogitTile][kLogitPitch], ws[2][kLogitTile][kLogitPitch];
     const int e0 = blockIdx.x * kLogitTile, t0 = blockIdx.y * kLogitTile;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4; // experts 2tx, 2tx + 1; tokens 2ty, 2ty + 1
-    // two sums per output (even and odd k), added at the end: twice as many independent fp64 chains in
-    // flight, which this tile size needs to keep the fp64 pipe busy
+    // two sums per output (even and odd k), added at the end: twice as many independent fp64 chains
     double a00[2] = {0.0, 0.0}, a01[2] = {0.0, 0.0}, a10[2] = {0.0, 0.0}, a11[2] = {0.0, 0.0};
     float px[4], pw[4]; // a chunk's values of this thread, in flight while an earlier chunk is summed
     auto fetch = [&](int k0) {
@@ -146,8 +153,8 @@ __global__ void __launch_bounds__(256) moe_logits_tiled_kernel(const float * __r
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int idx = (int)threadIdx.x + 256 * j, r = idx >> 5, k = idx & 31;
-            xs[b][k][logit_col(k, r)] = (double)px[j];
-            ws[b][k][logit_col(k, r)] = (double)pw[j];
+            xs[b][k][r] = (double)px[j];
+            ws[b][k][r] = (double)pw[j];
         }
     };
     fetch(0);
@@ -155,24 +162,26 @@ __global__ void __launch_bounds__(256) moe_logits_tiled_kernel(const float * __r
     if (kLogitTile < n_embd) {
         fetch(kLogitTile);
     }
-    int b = 0;
-    for (int k0 = 0; k0 < n_embd; k0 += kLogitTile, b ^= 1) {
-        __syncthreads(); // chunk k0 is stored; the other buffer's readers (chunk k0 - 32) are done
+    for (int k0 = 0; k0 < n_embd; k0 += 2 * kLogitTile) { // two chunks per round: the buffer is a constant
+        __syncthreads(); // chunk k0 is stored; buffer 1's readers are done
         if (k0 + kLogitTile < n_embd) {
-            store(b ^ 1);
+            store(1);
             if (k0 + 2 * kLogitTile < n_embd) {
                 fetch(k0 + 2 * kLogitTile);
             }
         }
-#pragma unroll 8
-        for (int k = 0; k < kLogitTile; k++) {
-            const double2 xv = *reinterpret_cast<const double2 *>(&xs[b][k][logit_col(k, 2 * ty)]);
-            const double2 wv = *reinterpret_cast<const double2 *>(&ws[b][k][logit_col(k, 2 * tx)]);
-            a00[k & 1] += xv.x * wv.x;
-            a01[k & 1] += xv.x * wv.y;
-            a10[k & 1] += xv.y * wv.x;
-            a11[k & 1] += xv.y * wv.y;
+        logits_chunk(xs[0], ws[0], ty, tx, a00, a01, a10, a11);
+        if (k0 + kLogitTile >= n_embd) {
+            break;
         }
+        __syncthreads(); // chunk k0 + 32 is stored; buffer 0's readers are done
+        if (k0 + 2 * kLogitTile < n_embd) {
+            store(0);
+            if (k0 + 3 * kLogitTile < n_embd) {
+                fetch(k0 + 3 * kLogitTile);
+            }
+        }
+        logits_chunk(xs[1], ws[1], ty, tx, a00, a01, a10, a11);
     }
     const int ta = t0 + 2 * ty, ea = e0 + 2 * tx;
     if (ta < n_tok && ea < n_expert) {
