@@ -251,7 +251,10 @@ int b200q_moe_csr(void * stream, const int32_t * ids, int n_pairs, int n_expert,
 
 /* moe_grp_gate_up_launch (kernels.h:638-642): h[p*h_stride + i] = silu(gate_e[i].x_t) * (up_e[i].x_t) for
  * every pair, on the tokens' quantized activation (x8/xmeta/xsumq with TB = n_tok, from b200q_xq).
- * n_act_max bounds the number of active experts (grid size; n_expert is always safe). */
+ * n_act_max bounds the number of active experts (grid size; n_expert is always safe).  Up to four routed
+ * tokens per expert on average (n_tok * top_k <= 4 * n_act_max) every routed pair runs as a single-token
+ * GEMV; more (prefill) run as grouped tensor-core tiles over (expert, row tile).  The same holds for
+ * b200q_moe_down. */
 int b200q_moe_gate_up(void * stream, const void * gbank, const void * ubank, uint32_t gtype, uint32_t utype,
                       size_t slot_gb, size_t slot_ub, const int32_t * off, const int32_t * pair,
                       const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,

@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const float * __restric
 // float -> double conversions run at a quarter of the fp64 FMA rate on this GPU: a value is converted
 // once, by the thread that stages it, and the tiles lie in shared memory as doubles, k-major, so that a
 // thread's two tokens (two experts) come with one 16-byte load.
+constexpr int kLogitTiledFrom = 256; // tokens from which the tiled kernel is used
 constexpr int kLogitTile = 32, kLogitPitch = kLogitTile + 2; // the pad spreads a warp's 32 stores of one column
 // one chunk: 32 steps of k on the doubles in shared memory, every address a constant offset
 __device__ __forceinline__ void logits_chunk(const double (*xs)[kLogitPitch], const double (*ws)[kLogitPitch], int ty, int tx,
@@ -627,7 +628,9 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
                              int n_embd, int n_expert, int top_k, float * logits, int32_t * ids, float * wts,
                              int32_t * off, int32_t * pair, int32_t * active, int32_t * n_active) {
     if (gate_inp) {
-        cudaError_t e = n_tok >= kLogitTile
+        // the tiled kernel's grid is (experts / 32) x (tokens / 32) CTAs, each walking all of K: below 256
+        // tokens that is too few CTAs (64 tokens: 16), and the kernel of two experts per CTA is faster
+        cudaError_t e = n_tok >= kLogitTiledFrom
                             ? launch_chained(s, moe_logits_tiled_kernel,
                                              dim3((unsigned)((n_expert + kLogitTile - 1) / kLogitTile), (unsigned)((n_tok + kLogitTile - 1) / kLogitTile)),
                                              dim3(256), 0, gate_inp, x, x_stride, n_tok, n_embd, n_expert, logits)

@@ -182,10 +182,11 @@ def test_moe_config3_full_size(be, orc, pkg):
     assert 60 <= n <= 128
 
 
-@pytest.mark.parametrize("n_tok,E,n_embd", [(100, 40, 520), (32, 256, 2048), (257, 33, 96)])
+@pytest.mark.parametrize("n_tok,E,n_embd", [(100, 40, 520), (300, 40, 520), (256, 256, 2048), (257, 33, 96)])
 def test_router_logits_many_tokens(be, orc, pkg, n_tok, E, n_embd):
-    """32 tokens and more take the tiled logits kernel (ragged token, expert and K tiles included):
-    logits within 1e-6 of the oracle's fp64 sums, same ids."""
+    """256 tokens and more take the tiled logits kernel (ragged token, expert and K tiles included),
+    fewer the kernel of two experts per CTA in several passes of 16 tokens: logits within 1e-6 of the
+    oracle's fp64 sums, same ids."""
     from sycl_infer_b200.moe import moe_router_launch
     rng = np.random.default_rng(n_tok + E)
     x = pkg.synth.make_activation(n_tok, n_embd, 900 + n_tok)
