@@ -821,7 +821,12 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     a.raw_bytes = (need / 16) % 2 ? need : need + 16;
     a.lbo = 128;
     a.sbo = 256;
-    const bool pg2 = a.raw_bytes <= (c.TB <= 32 ? 240 : 192); // a second producer group where its staging fits
+    bool pg2 = a.raw_bytes <= 240; // up to 32 tokens unpacking dominates: a second producer group where its staging fits
+#ifdef B200Q_TUNING
+    if (const char * e = getenv("B200Q_MMA_PG")) { // A/B builds only
+        pg2 = pg2 && atoi(e) == 2;
+    }
+#endif
     // token tile: the fp32 epilogue costs in proportion to its width, so it is as narrow as the call allows
     if (c.TB <= 8) {
         return pg2 ? launch_nt<8, 1, 2>(s, a, pdl_secondary) : launch_nt<8, 1, 1>(s, a, pdl_secondary);
@@ -833,7 +838,10 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
         return pg2 ? launch_nt<32, 2, 2>(s, a, pdl_secondary) : launch_nt<32, 2, 1>(s, a, pdl_secondary);
     }
     // prefill: the fp32 epilogue dominates; two epilogue warpgroups share the token columns
-    return pg2 ? launch_nt<64, 2, 2>(s, a, pdl_secondary) : launch_nt<64, 2, 1>(s, a, pdl_secondary);
+    // One producer group: the epilogue is the bound, a second group only costs registers (A/B on
+    // 17408 x 5120 Q4_K: 741 -> 716 us at 512 tokens, 2717 -> 2653 us at 2048).  Four epilogue warpgroups
+    // instead of two (21 warps: 80 registers, spills) were slower: 761 us.
+    return launch_nt<64, 2, 1>(s, a, pdl_secondary);
 }
 
 // ---- grouped form: the expert GEMMs of a routed-MoE call --------------------------------------------
