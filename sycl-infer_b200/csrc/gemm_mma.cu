@@ -865,7 +865,8 @@ cudaError_t launch_moe_mma(cudaStream_t s, const void * bank_a, const void * ban
                            const int32_t * active, const int32_t * n_active, int n_act_max, const int8_t * x8,
                            const float * xmeta, const int32_t * xsumq, int TB, int top_k, int K, int n_rows,
                            float * out, int out_stride, int fuse) {
-    if (!moe_mma_supported(type_a, type_b, K, n_rows, fuse)) {
+    if (!moe_mma_supported(type_a, type_b, K, n_rows, fuse) || n_act_max < 1 || TB < 1 ||
+        (top_k > 0 ? (long long)TB * top_k : (long long)TB) > 0x7FFFFFFFLL) {
         return cudaErrorInvalidConfiguration;
     }
     MmaArgs a;

@@ -274,3 +274,63 @@ def test_pairs_with_invalid_expert_ids_are_left_out(be, pkg):
     assert np.all(h_b[left_out] == 7.0) and np.all(acc_b[left_out] == 7.0)
     assert np.array_equal(h_b[kept], h_g[kept]) and np.array_equal(acc_b[kept], acc_g[kept])
     assert not np.any(h_g[left_out] == 7.0)
+
+
+@pytest.mark.parametrize("t", [12, 14])
+def test_grouped_expert_tiles_with_ragged_rows(be, orc, pkg, t):
+    """The grouped tensor-core kernel on planes whose row count is not a multiple of its tiles (200 rows:
+    64-pair tiles of gate|up, 128-row tiles of down), experts with more tokens than one 32-token tile,
+    called through b200q_moe_gate_up / b200q_moe_down directly; every pair against the oracle's rows."""
+    from sycl_infer_b200.backend import alloc_act
+    from sycl_infer_b200.moe import (moe_actq_launch, moe_csr_launch, moe_grp_down_launch, moe_grp_gate_up_launch,
+                                     moe_t)
+    E, top_k, K, rows, n_tok = 4, 2, 512, 200, 48
+    n_pairs = n_tok * top_k
+    rng = np.random.default_rng(5 + t)
+    ids = rng.integers(0, E, (n_tok, top_k)).astype(np.int32)
+    ids[:40, 0] = 1  # expert 1 gets more than 32 tokens: two tiles of tokens
+    i32 = dict(dtype=torch.int32, device="cuda")
+    off, pair = torch.zeros(E + 1, **i32), torch.zeros(n_pairs, **i32)
+    active, n_active = torch.zeros(E, **i32), torch.zeros(1, **i32)
+    moe_csr_launch(be, torch.from_numpy(ids).cuda(), n_pairs, E, off, pair, active, n_active)
+    flat = ids.reshape(-1)
+
+    # gate|up: h[p] = silu(gate_e . x_t) * (up_e . x_t)
+    gate = [pkg.synth.make_weight(t, rows, K, 100 + e) for e in range(E)]
+    up = [pkg.synth.make_weight(t, rows, K, 200 + e) for e in range(E)]
+    M = moe_t(gate_exps=torch.from_numpy(np.concatenate(gate)).cuda(), up_exps=torch.from_numpy(np.concatenate(up)).cuda(),
+              down_exps=None, gate_type=t, up_type=t, down_type=t, n_expert=E, top_k=top_k, n_embd=K, n_ff_exp=rows)
+    x = pkg.synth.make_activation(n_tok, K, 61)
+    xq = alloc_act(n_tok, K)
+    moe_actq_launch(be, torch.from_numpy(x).cuda(), K, n_tok, K, *xq)
+    h = torch.full((n_pairs, rows), 7.0, device="cuda")
+    moe_grp_gate_up_launch(be, M, off, pair, active, n_active, E, *xq, n_tok, h, rows)
+    be.synchronize()
+    assert be.device_status() == 0
+    got = h.cpu().numpy()
+    for p in range(n_pairs):
+        e, one = flat[p], orc.xq(x[p // top_k])
+        g = orc.gemm(t, gate[e], K, rows, one)[0]
+        u = orc.gemm(t, up[e], K, rows, one)[0]
+        with np.errstate(over="ignore"):  # exp(-g) may overflow to inf: silu is then -0, on both sides
+            ref = (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
+        assert np.max(np.abs(got[p] - ref)) <= 2e-5 * (np.max(np.abs(ref)) + 1e-30), p
+
+    # down: acc[p] = down_e . h_p, 200 output rows, K = 256
+    Kd = 256
+    down = [pkg.synth.make_weight(t, rows, Kd, 300 + e) for e in range(E)]
+    D = moe_t(gate_exps=None, up_exps=None, down_exps=torch.from_numpy(np.concatenate(down)).cuda(), gate_type=t, up_type=t,
+              down_type=t, n_expert=E, top_k=top_k, n_embd=rows, n_ff_exp=Kd)
+    hv = pkg.synth.make_activation(n_pairs, Kd, 62)
+    hq = alloc_act(n_pairs, Kd)
+    moe_actq_launch(be, torch.from_numpy(hv).cuda(), Kd, n_pairs, Kd, *hq)
+    acc = torch.full((n_pairs, rows), 7.0, device="cuda")
+    moe_grp_down_launch(be, D, off, pair, active, n_active, E, *hq, n_pairs, acc, rows)
+    be.synchronize()
+    assert be.device_status() == 0
+    got = acc.cpu().numpy()
+    for p in range(n_pairs):
+        e, one = flat[p], orc.xq(hv[p])
+        ref = orc.gemm(t, down[e], Kd, rows, one)[0]
+        ab = orc.gemm_abs(t, down[e], Kd, rows, one)[0]
+        assert np.max(np.abs(got[p] - ref) / np.maximum(ab, 1e-30)) <= TOL, p
