@@ -797,6 +797,18 @@ template <int NT, int EW, int PG, bool G = false> static cudaError_t launch_nt(c
     return cudaLaunchKernelEx(&cfg, gemm_mma_kernel<NT, EW, PG, G>, a);
 }
 
+// Per-thread staging bytes for one raw superblock of `type`: the superblock plus its misalignment in
+// whole 16-byte chunks (none when the size is a multiple of 16: tensor bases, planes and rows then keep
+// the 16-byte alignment), made an odd number of chunks so that the threads' 16-byte reads hit distinct banks.
+static int mma_raw_bytes(int type) {
+    const int sbb = sb_bytes((uint32_t)type);
+    int n = sbb % 16 == 0 ? sbb : ((sbb + 30) / 16) * 16;
+    if (type == kQ8_0) {
+        n += 16; // the funnel-shifted 2-byte-aligned reads touch one word past the last block
+    }
+    return (n / 16) % 2 ? n : n + 16;
+}
+
 cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondary, int32_t * dump, int dump_t) {
     MmaArgs a;
     memset(&a.g, 0, sizeof(a.g));
@@ -807,18 +819,11 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
     for (int i = 0; i < c.n_segs; i++) {
         tiles += (c.seg[i].n_rows + kTileM - 1) / kTileM;
         a.tiles_m[i] = tiles;
-        // a superblock plus its misalignment, in whole 16-byte chunks (none when the size is a
-        // multiple of 16: tensor bases are 16-byte aligned)
-        const int sbb = sb_bytes(c.seg[i].type);
-        int n = sbb % 16 == 0 ? sbb : ((sbb + 30) / 16) * 16;
-        if (c.seg[i].type == kQ8_0) {
-            n += 16; // the funnel-shifted 2-byte-aligned reads touch one word past the last block
-        }
+        const int n = mma_raw_bytes((int)c.seg[i].type);
         need = need > n ? need : n;
     }
     a.n_tiles_m = tiles;
-    // odd number of 16-byte chunks per thread: the threads' 16-byte reads then hit distinct banks
-    a.raw_bytes = (need / 16) % 2 ? need : need + 16;
+    a.raw_bytes = need;
     a.lbo = 128;
     a.sbo = 256;
     bool pg2 = a.raw_bytes <= 240; // up to 32 tokens unpacking dominates: a second producer group where its staging fits
@@ -845,17 +850,6 @@ cudaError_t launch_gemm_mma(cudaStream_t s, const CallDev & c, bool pdl_secondar
 }
 
 // ---- grouped form: the expert GEMMs of a routed-MoE call --------------------------------------------
-static int mma_raw_bytes(int type) {
-    // a superblock plus its misalignment, in whole 16-byte chunks (none when the size is a multiple
-    // of 16: planes and rows then keep the 16-byte alignment of the bank)
-    const int sbb = sb_bytes((uint32_t)type);
-    int n = sbb % 16 == 0 ? sbb : ((sbb + 30) / 16) * 16;
-    if (type == kQ8_0) {
-        n += 16; // the funnel-shifted 2-byte-aligned reads touch one word past the last block
-    }
-    return (n / 16) % 2 ? n : n + 16; // odd number of 16-byte chunks per thread: distinct banks
-}
-
 bool moe_mma_supported(int type_a, int type_b, int K, int n_rows, int fuse) {
     return K >= 256 && (K & 255) == 0 && n_rows >= 1 && (!fuse || type_a == type_b);
 }
