@@ -7,6 +7,11 @@
 // (:72-137); experts = int8 gate/up rows on the token's quantized activation, h = silu(g)*u,
 // h re-quantized per 32 values, down rows on that (:476-559); reduce = out[t] += sum_j w*acc
 // with a double accumulator (:562-574).  Expert e's plane starts at bank + e*plane_bytes.
+//
+// Expert kernels by regime (launch_moe_rows): up to four routed tokens per expert on average, every
+// routed pair as a single-token GEMV (moe_pinned.cuh; moe_stream.cu for shapes it does not take);
+// more, grouped tensor-core tiles over (expert, row tile) (gemm_mma.cu); the warp-per-row kernel
+// below serves what neither takes (gate and up planes of different types with many tokens).
 #include "decode.cuh"
 #include "launch.h"
 

@@ -13,8 +13,9 @@
 //     (up to kMoeTok tokens at a time) whenever the CTA moves to another expert;
 //   * the down projection has a short K (the expert's FFN width): lanes then cover
 //     (row, unit) pairs - several rows per pass - instead of one row's units.
-// Rows must be 16-byte multiples (the copies then need no realignment); other shapes and the
-// prefill regime (many tokens per expert) stay on the warp-per-row kernel.
+// Rows must be 16-byte multiples (the copies then need no realignment); other shapes stay on the
+// warp-per-row kernel, the prefill regime (many tokens per expert) runs as grouped tensor-core tiles
+// (gemm_mma.cu).
 #include <cstdlib>
 #include <cstring>
 
