@@ -9,6 +9,11 @@ launches, pairing a gate|up call with the down call that consumes silu(gate)*up 
 the latter's quantized activation, the latter runs without a quantizer), folding a call's RMSNorm
 into its quantizer and hanging the argmax on the head call; `record()` captures the launches of a
 whole token into ONE CUDA graph and `replay()` runs it.
+
+`PlanBuckets` mirrors the engine's decode buckets (src/engine/engine.h:770-782, src/engine/graph.cpp:
+2824-2835 and 3146-3194): one plan per row count 1..max_rows, so that a decode step of n sequences runs
+exactly n rows, with a recorded graph for the coarse row counts only and direct replay of the plan for
+the others.
 """
 from dataclasses import dataclass, field
 
@@ -132,8 +137,11 @@ class SegPlan:
                 moe_call(be, M, scratch, c.x, c.tb, out)
                 continue
             segs = []
-            for s in c.segs:  # the segments carry the call's activation, as the C ABI wants it
-                s.x, s.act_up, s.x_stride = c.x, c.up, c.x.shape[-1]
+            # the segments carry the call's activation, as the C ABI wants it; a 2-D activation may be a
+            # column slice of a wider buffer: its row stride, not its width, separates the rows
+            x_stride = c.x.stride(0) if c.x.dim() > 1 else c.x.shape[-1]
+            for s in c.segs:
+                s.x, s.act_up, s.x_stride = c.x, c.up, x_stride
                 segs.append(s)
             if c.tb == 1:
                 be.quant_gemv_ex(segs, 1, prequantized=c.prequantized, next_act=c.next_act, norm=c.norm, argmax=c.argmax)
@@ -159,3 +167,52 @@ class SegPlan:
 
     def replay(self):
         self.graph.replay()
+
+
+class PlanBuckets:
+    """Decode plans by row count.  `build(tb)` returns the (unfinalized or finalized) SegPlan of a step
+    with tb rows; plans are built on first use (`build_all()` builds every one up front, as the engine
+    does).  `run(be, n_rows, stream)` replays the bucket's CUDA graph when n_rows is one of the graphed
+    row counts (1, 2, 4, 8, 16 and max_rows: dec_graph_rows) and a stream is given, else it issues the
+    plan's launches directly."""
+
+    def __init__(self, build, max_rows):
+        if max_rows < 1:
+            raise ValueError("max_rows < 1")
+        self.build, self.max_rows = build, int(max_rows)
+        self.plans = {}
+
+    def graph_rows(self, tb):
+        return tb in (1, 2, 4, 8, 16, self.max_rows)
+
+    def bucket(self, n_rows):
+        if not 1 <= n_rows <= self.max_rows:
+            raise ValueError(f"{n_rows} rows: buckets cover 1..{self.max_rows}")
+        p = self.plans.get(n_rows)
+        if p is None:
+            p = self.build(n_rows)
+            for ci, c in enumerate(p.calls):
+                if c.tb != n_rows:
+                    raise ValueError(f"bucket {n_rows}: call {ci} was built for {c.tb} rows")
+            if not p.lowered:
+                p.finalize()
+            self.plans[n_rows] = p
+        return p
+
+    def build_all(self):
+        for tb in range(1, self.max_rows + 1):
+            self.bucket(tb)
+        return self
+
+    def launches(self, n_rows):
+        return self.bucket(n_rows).launches()
+
+    def run(self, be, n_rows, stream=None):
+        p = self.bucket(n_rows)
+        if stream is not None and self.graph_rows(n_rows):
+            if p.graph is None:
+                p.record(be, stream)
+            p.replay()
+        else:
+            p.run(be)
+        return p

@@ -10,7 +10,7 @@ pkg = graft.load_package()
 torch = pytest.importorskip("torch")
 from sycl_infer_b200 import gguf as G  # noqa: E402
 from sycl_infer_b200.backend import gemv_seg  # noqa: E402
-from sycl_infer_b200.plan import SegPlan  # noqa: E402
+from sycl_infer_b200.plan import PlanBuckets, SegPlan  # noqa: E402
 
 H, QD, KD, FF, V, L = 512, 512, 128, 1024, 1024, 2
 EPS = 1e-6
@@ -230,3 +230,95 @@ def test_moe_call_inside_a_plan(orc):
     assert be.device_status() == 0
     assert torch.equal(h1, h2) and torch.equal(o1, o2) and torch.equal(S1.ids, S2.ids)
     assert float(o1.abs().max()) > 0
+
+
+# ---- decode buckets: a plan per row count ------------------------------------------------------------
+def _two_call_plan(w_qkv, w_o, x, mid, out, act_h, act_q, tb):
+    """q|k|v-like call (two segments) and an o-like call with a residual, tb rows each."""
+    p = SegPlan()
+    p.begin_call(tb)
+    p.add(gemv_seg(w=w_qkv[0], type=12, K=H, n_rows=QD, out=mid.view(-1), out_stride=mid.shape[-1], x8=act_h[0],
+                   xmeta=act_h[1], xsumq=act_h[2]))
+    p.add(gemv_seg(w=w_qkv[1], type=14, K=H, n_rows=KD, out=mid.view(-1)[QD:], out_stride=mid.shape[-1], x8=act_h[0],
+                   xmeta=act_h[1], xsumq=act_h[2]))
+    p.set_xq(x[:tb])
+    p.begin_call(tb)
+    p.add(gemv_seg(w=w_o, type=12, K=QD, n_rows=H, out=out.view(-1), out_stride=H, residual=x.view(-1), x8=act_q[0],
+                   xmeta=act_q[1], xsumq=act_q[2]))
+    p.set_xq(mid[:tb, :QD])
+    return p
+
+
+class _CountingBackend:
+    def __init__(self):
+        self.calls = []
+
+    def quant_gemv_ex(self, segs, tb, **kw):
+        self.calls.append(("ex", tb, len(segs)))
+
+    def quant_gemv(self, segs, tb):
+        self.calls.append(("gemv", tb, len(segs)))
+
+
+def test_buckets_build_one_plan_per_row_count():
+    dev = "cpu"
+    x, mid, out = torch.zeros(6, H), torch.zeros(6, QD + KD), torch.zeros(6, H)
+    dummy = torch.zeros(16, dtype=torch.uint8)
+    built = []
+
+    def build(tb):
+        built.append(tb)
+        return _two_call_plan((dummy, dummy), dummy, x, mid, out, _act(H * 6, dev), _act(QD * 6, dev), tb)
+
+    B = PlanBuckets(build, 6)
+    assert [B.graph_rows(t) for t in range(1, 7)] == [True, True, False, True, False, True]
+    be = _CountingBackend()
+    B.run(be, 3)
+    B.run(be, 3)
+    B.run(be, 1)
+    assert built == [3, 1]  # built on first use, once
+    assert be.calls == [("gemv", 3, 2), ("gemv", 3, 1)] * 2 + [("ex", 1, 2), ("ex", 1, 1)]
+    assert B.launches(3) == 4 and B.launches(1) == 2  # several rows take a quantizer launch per call
+    with pytest.raises(ValueError):
+        B.run(be, 7)
+    with pytest.raises(ValueError):
+        PlanBuckets(lambda tb: _two_call_plan((dummy, dummy), dummy, x, mid, out, _act(H, dev), _act(QD, dev), 1), 4).run(be, 2)
+    assert sorted(PlanBuckets(build, 6).build_all().plans) == [1, 2, 3, 4, 5, 6]
+
+
+@pytest.mark.gpu
+def test_buckets_graph_and_direct_replay_agree_with_plain_calls():
+    """Row counts 1..5 through the buckets (graphs for 1, 2, 4 and 5 = max, direct replay for 3) against
+    the same calls issued one by one: identical outputs."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    be = pkg.make_cuda_backend(0)
+    dev, R = "cuda", 5
+    w_qkv = (torch.from_numpy(pkg.synth.make_weight(12, QD, H, 1)).cuda(), torch.from_numpy(pkg.synth.make_weight(14, KD, H, 2)).cuda())
+    w_o = torch.from_numpy(pkg.synth.make_weight(12, H, QD, 3)).cuda()
+    x = torch.from_numpy(pkg.synth.make_activation(R, H, 4)).cuda()
+    mid, out = torch.zeros(R, QD + KD, device=dev), torch.zeros(R, H, device=dev)
+    from sycl_infer_b200.backend import alloc_act
+    acts = {}
+
+    def build(tb):
+        acts[tb] = (alloc_act(tb, H), alloc_act(tb, QD))
+        return _two_call_plan(w_qkv, w_o, x, mid, out, acts[tb][0], acts[tb][1], tb)
+
+    B = PlanBuckets(build, R)
+    st = torch.cuda.Stream()
+    for n in (1, 2, 3, 4, 5, 3, 1):
+        mid.zero_()
+        out.zero_()
+        torch.cuda.synchronize()
+        p = B.run(be, n, st)
+        st.synchronize()
+        assert (p.graph is not None) == (n != 3)
+        got_mid, got_out = mid.clone(), out.clone()
+        mid.zero_()
+        out.zero_()
+        _two_call_plan(w_qkv, w_o, x, mid, out, acts[n][0], acts[n][1], n).finalize().run(be)
+        be.synchronize()
+        assert be.device_status() == 0
+        assert torch.equal(got_mid, mid) and torch.equal(got_out, out)
+        assert torch.count_nonzero(out[:n]).item() > 0 and torch.count_nonzero(out[n:]).item() == 0
