@@ -622,10 +622,19 @@ static cudaError_t launch_chained(cudaStream_t s, void (*k)(KArgs...), dim3 grid
     return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
 }
 
+// Shared memory of csr_build.  Lists of up to 1024 pairs are filled by a thread per pair, which needs the
+// ids in shared memory; longer lists by the warp-parallel fill (a cursor per warp and expert), with the
+// ids in shared memory while that stays within the 48 KB every launch may have (beyond that - many
+// experts - the ids are read from global memory; the launchers raise the kernel's limit when even the
+// cursors need more).
+constexpr size_t kCsrPlainSmem = 48 * 1024;
 static size_t csr_smem(int n_pairs, int n_expert, int & in_smem) {
+    const size_t fixed = (size_t)2 * (n_expert + 1) + (n_pairs > 1024 ? (size_t)8 * n_expert : 0);
     in_smem = n_pairs <= 8192 ? 1 : 0;
-    const size_t per_warp = n_pairs > 1024 ? (size_t)8 * n_expert : 0; // the long-list fill's cursors (256 threads)
-    return ((size_t)(2 * (n_expert + 1) + (in_smem ? n_pairs : 0)) + per_warp) * sizeof(int32_t);
+    if (n_pairs > 1024 && (fixed + n_pairs) * sizeof(int32_t) > kCsrPlainSmem) {
+        in_smem = 0;
+    }
+    return (fixed + (in_smem ? n_pairs : 0)) * sizeof(int32_t);
 }
 
 // off != nullptr: the CSR is built by the router's last CTA
@@ -658,6 +667,12 @@ cudaError_t launch_moe_route(cudaStream_t s, const float * gate_inp, const float
         const size_t c = csr_smem(n_tok * top_k, n_expert, in_smem);
         smem = smem > c ? smem : c;
     }
+    if (smem > kCsrPlainSmem) {
+        const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(moe_route_kernel), (int)smem);
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
     return launch_chained(s, moe_route_kernel, dim3((unsigned)n_tok), dim3(256), smem, x, x_stride, n_embd, n_expert, top_k,
                           logits, ids, wts, off, pair, active, n_active, in_smem);
 }
@@ -666,6 +681,12 @@ cudaError_t launch_moe_csr(cudaStream_t s, const int32_t * ids, int n_pairs, int
                            int32_t * pair, int32_t * active, int32_t * n_active) {
     int in_smem = 0;
     const size_t smem = csr_smem(n_pairs, n_expert, in_smem);
+    if (smem > kCsrPlainSmem) {
+        const cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(moe_csr_kernel), (int)smem);
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
     return launch_chained(s, moe_csr_kernel, dim3(1), dim3(256), smem, ids, n_pairs, n_expert, off, pair, active, n_active,
                           in_smem);
 }

@@ -205,7 +205,8 @@ def test_router_logits_many_tokens(be, orc, pkg, n_tok, E, n_embd):
     assert np.max(np.abs(wts.cpu().numpy() - wts_o)) <= 1e-6
 
 
-@pytest.mark.parametrize("n_tok,E,top_k", [(16, 256, 8), (3, 32, 4), (600, 64, 4), (2100, 8, 4)])
+@pytest.mark.parametrize("n_tok,E,top_k", [(16, 256, 8), (3, 32, 4), (600, 64, 4), (2100, 8, 4), (2048, 512, 4),
+                                           (1024, 2048, 4)])
 def test_csr_separate_and_fused_agree(be, pkg, n_tok, E, top_k):
     """Router + CSR as two entry points and as the fused one (the router's last CTA builds the
     lists): identical ids, offsets, pair lists and active experts; the lists are checked against a
