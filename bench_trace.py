@@ -27,8 +27,7 @@ sys.path.insert(0, ROOT)
 spec = importlib.util.spec_from_file_location("b200q_build", os.path.join(ROOT, "sycl-infer_b200", "build.py"))
 build = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(build)
-os.environ["B200Q_LIB"] = build.build_native(extra=["-DB200Q_TUNING"],
-                                             out=os.path.join(ROOT, "sycl-infer_b200", "libb200q_tuning.so"))
+os.environ["B200Q_LIB"] = build.build_tuning()
 import torch  # noqa: E402
 
 if len(sys.argv) > 1 and sys.argv[1] == "router":

@@ -52,7 +52,19 @@ def build_native(force=False, verbose=False, extra=(), out=None):
     return lib
 
 
+TUNING_LIB = os.path.join(HERE, "libb200q_tuning.so")
+
+
+def build_tuning(force=False, verbose=False):
+    """The A/B variant (-DB200Q_TUNING: timeline stamps and kernel-selection knobs read from the
+    environment) beside the product library; select it with B200Q_LIB=<path>."""
+    return build_native(force=force, verbose=verbose, extra=["-DB200Q_TUNING"], out=TUNING_LIB)
+
+
 if __name__ == "__main__":
     import sys
-    build_native(force="--force" in sys.argv, verbose=True,
-                 extra=["-Xptxas", "-v"] if "--ptxas" in sys.argv else [])
+    if "--tuning" in sys.argv:
+        print(build_tuning(force="--force" in sys.argv, verbose=True))
+    else:
+        build_native(force="--force" in sys.argv, verbose=True,
+                     extra=["-Xptxas", "-v"] if "--ptxas" in sys.argv else [])
